@@ -1,0 +1,133 @@
+"""The Python entry point: a model folder in, tokens out.
+
+The reference has no `Model::from_dir`; each of its examples loads by hand
+(crates/janus-engine/examples/inference.rs:199-309: config, safetensors, blocks,
+sampler, `Model::new`, `generate`).  `load` does the same steps here, choosing
+the model class by config.json's `architectures`.
+"""
+from __future__ import annotations
+
+from typing import Callable, List, Optional, Sequence, Tuple
+
+import torch
+
+from .cache import PAGE_SIZE
+from .config import read_config_json, resolve_architecture
+from .engine.generate import GenerationStats, run_generation
+from .engine.step import Engine, EngineOptions, StepEntry
+from .sampling import DeviceSampler, SamplerConfig
+from .weights import FolderCheckpoint, RandomCheckpoint, parse_dtype
+
+
+class _EngineBackend:
+    """Drives the engine's step function and the device sampler for the
+    generation loop."""
+
+    def __init__(self, engine: Engine, sampler: DeviceSampler):
+        self.engine, self.sampler = engine, sampler
+        self.device = engine.device
+
+    def alloc_slot(self) -> int:
+        slot = self.engine.alloc_slot()
+        self.sampler.reset_row(slot)
+        return slot
+
+    def free_slot(self, slot: int) -> None:
+        self.engine.free_slot(slot)
+
+    def synchronize(self) -> None:
+        torch.cuda.synchronize(self.device)
+
+    def _sample(self, logits: torch.Tensor, slots, requests, steps) -> List[int]:
+        meta = torch.tensor([list(requests), list(steps), list(slots)], dtype=torch.int32).to(self.device)
+        ids = self.sampler.sample(logits, meta[0], meta[1], meta[2])
+        return ids.cpu().tolist()
+
+    def prefill(self, slots, prompts, requests) -> List[int]:
+        logits = self.engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
+        return self._sample(logits, slots, requests, [0] * len(slots))
+
+    def decode(self, slots, last_tokens, requests, steps) -> List[int]:
+        logits = self.engine.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, last_tokens)])
+        return self._sample(logits, slots, requests, steps)
+
+
+class Model:
+    """A loaded model with its cache and step function."""
+
+    def __init__(self, config, engine: Engine):
+        self.config = config
+        self.engine = engine
+        self.device = engine.device
+        self.dtype = engine.dtype
+
+    # -- the step function, for callers that schedule themselves ---------------
+    def alloc_slot(self) -> int:
+        return self.engine.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.engine.free_slot(slot)
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        return self.engine.step(entries)
+
+    # -- generation ------------------------------------------------------------
+    def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 128, temperature: float = 0.0,
+                 top_k: int = 0, top_p: float = 1.0, repetition_penalty: float = 1.0, seed: int = 0,
+                 stop_token_ids: Optional[Sequence[int]] = None, ignore_eos: bool = False,
+                 batch_size: Optional[int] = None,
+                 callback: Optional[Callable[[int, int], bool]] = None,
+                 return_reasons: bool = False):
+        """Generate up to `max_tokens` new tokens for each prompt (lists of token
+        ids).  Stop tokens are config.json's `eos_token_id` plus
+        `stop_token_ids`, unless `ignore_eos`.  Returns (tokens, stats), or
+        (tokens, reasons, stats) with `return_reasons`."""
+        sc = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p,
+                           repetition_penalty=repetition_penalty, max_tokens=max_tokens)
+        cache = self.engine.cache
+        sampler = DeviceSampler(sc, self.engine.model.vocab_size, cache.n_slots, seed, self.device)
+        stop = [] if ignore_eos else list(getattr(self.config, "eos_token_id", ()) or ())
+        stop += list(stop_token_ids or ())
+        outputs, reasons, stats = run_generation(
+            _EngineBackend(self.engine, sampler), [list(map(int, p)) for p in prompts], max_tokens, stop,
+            batch_size or cache.n_slots, cache.n_pages * PAGE_SIZE, self.engine.max_seq_len,
+            cache.n_free_slots, PAGE_SIZE, callback)
+        if return_reasons:
+            return outputs, reasons, stats
+        return outputs, stats
+
+
+def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_seq_len: Optional[int],
+           max_slots: Optional[int], device, use_graphs: bool) -> Model:
+    if not torch.cuda.is_available():
+        raise RuntimeError("janus_b200 needs a CUDA device (sm_100a); there is no CPU path")
+    device = torch.device(device)
+    torch_dtype = parse_dtype(dtype)
+    arch = resolve_architecture(config_dict)
+    config = arch.config_class.from_dict(config_dict)
+    with torch.cuda.device(device):
+        model = arch.build(config, torch_dtype, device)
+        model.load(checkpoint_factory(arch, config))
+        engine = Engine(model, EngineOptions(max_tokens=max_tokens, max_seq_len=max_seq_len,
+                                             max_slots=max_slots, use_graphs=use_graphs))
+    return Model(config, engine)
+
+
+def load(model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_seq_len: Optional[int] = None,
+         max_slots: Optional[int] = None, device="cuda:0", use_graphs: bool = True) -> Model:
+    """Load `model_dir` (config.json + model.safetensors).  `dtype` is the engine
+    dtype: "bfloat16" (tensor-core kernels) or "float32" (true 32-bit path).
+    `max_tokens` sizes the cache: the most tokens live sequences hold at any
+    time, each sequence rounded up to a multiple of 64."""
+    return _build(read_config_json(model_dir), lambda arch, config: FolderCheckpoint(model_dir), dtype,
+                  max_tokens, max_seq_len, max_slots, device, use_graphs)
+
+
+def load_random(config_dict: dict, seed: int, dtype="bfloat16", max_tokens: int = 8192,
+                max_seq_len: Optional[int] = None, max_slots: Optional[int] = None, device="cuda:0",
+                std: float = 0.02, norm_std: float = 0.0, use_graphs: bool = True) -> Model:
+    """A model with seeded random weights made on the device, without a folder."""
+    def factory(arch, config):
+        return RandomCheckpoint(arch.weight_specs(config), seed, dtype=dtype, std=std, norm_std=norm_std,
+                                device=device)
+    return _build(config_dict, factory, dtype, max_tokens, max_seq_len, max_slots, device, use_graphs)

@@ -1,0 +1,156 @@
+"""The generation loop: batches of unequal prompts, one prefill step per batch,
+then one token per live sequence per step; sequences that meet a stop token or
+their budget leave the batch at once and give their slot back; batches follow
+one another until every request is served.
+
+The loop's decisions are plain Python over a small backend interface, so they
+can be tested without a device.  Compared with the reference's `generate_batch`
+(crates/janus-engine/src/model/transformer/generation.rs:673-876): prompts are
+not padded (728-738), finished rows do not stay in the batch (810-832), and the
+stop token is not part of the output (as in `generate`, 241-263).  Finish
+reasons are "stop" and "length" (generation.rs:421-427).
+"""
+from __future__ import annotations
+
+import time
+from dataclasses import dataclass, field
+from typing import Callable, List, Optional, Protocol, Sequence, Tuple
+
+
+class GenerationBackend(Protocol):
+    def alloc_slot(self) -> int: ...
+    def free_slot(self, slot: int) -> None: ...
+    def prefill(self, slots: Sequence[int], prompts: Sequence[Sequence[int]],
+                requests: Sequence[int]) -> List[int]:
+        """Run whole prompts in one step; return the first new token of each."""
+    def decode(self, slots: Sequence[int], last_tokens: Sequence[int], requests: Sequence[int],
+               steps: Sequence[int]) -> List[int]:
+        """Run one token per sequence; return the next token of each.
+        `steps[i]` is the number of tokens request i has produced so far."""
+    def synchronize(self) -> None: ...
+
+
+@dataclass
+class GenerationStats:
+    requests: int = 0
+    batches: int = 0
+    prefill_tokens: int = 0
+    prefill_ms: float = 0.0
+    decode_steps: int = 0
+    decode_tokens: int = 0
+    decode_ms: float = 0.0
+
+    @property
+    def prefill_tokens_per_s(self) -> float:
+        return self.prefill_tokens / (self.prefill_ms / 1e3) if self.prefill_ms > 0 else 0.0
+
+    @property
+    def decode_tokens_per_s(self) -> float:
+        return self.decode_tokens / (self.decode_ms / 1e3) if self.decode_ms > 0 else 0.0
+
+
+def tokens_held(prompt_len: int, max_new_tokens: int, page_size: int) -> int:
+    """Cache tokens a request holds at most, rounded up to whole pages.  The
+    last generated token is never fed back, so it needs no room."""
+    n = prompt_len + max(0, max_new_tokens - 1)
+    return (n + page_size - 1) // page_size * page_size
+
+
+def plan_batch(pending: Sequence[int], prompt_lens: Sequence[int], max_new_tokens: int, batch_size: int,
+               capacity_tokens: int, free_slots: int, page_size: int) -> List[int]:
+    """The next batch: requests in order, as many as the batch size, the free
+    slots and the cache's capacity allow.  At least one, or an error that names
+    the request that can never fit."""
+    chosen: List[int] = []
+    used = 0
+    for r in pending:
+        if len(chosen) >= min(batch_size, free_slots):
+            break
+        need = tokens_held(prompt_lens[r], max_new_tokens, page_size)
+        if used + need > capacity_tokens:
+            break
+        chosen.append(r)
+        used += need
+    if not chosen and pending:
+        r = pending[0]
+        raise ValueError(
+            f"request {r} needs room for {tokens_held(prompt_lens[r], max_new_tokens, page_size)} tokens "
+            f"but the cache holds {capacity_tokens} (free slots: {free_slots})")
+    return chosen
+
+
+def run_generation(backend: GenerationBackend, prompts: Sequence[Sequence[int]], max_new_tokens: int,
+                   stop_token_ids: Sequence[int], batch_size: int, capacity_tokens: int, max_seq_len: int,
+                   free_slots: int, page_size: int,
+                   callback: Optional[Callable[[int, int], bool]] = None
+                   ) -> Tuple[List[List[int]], List[str], GenerationStats]:
+    """Returns (generated tokens per request, finish reason per request, stats).
+    `callback(request, token)` is called for every accepted token; returning
+    False ends that request (reason "stop")."""
+    n = len(prompts)
+    for i, p in enumerate(prompts):
+        if len(p) == 0:
+            raise ValueError(f"prompt {i} is empty")
+        if len(p) > max_seq_len:
+            raise ValueError(f"prompt {i} has {len(p)} tokens, the longest sequence allowed is {max_seq_len}")
+    stop = set(int(t) for t in stop_token_ids)
+    outputs: List[List[int]] = [[] for _ in range(n)]
+    reasons: List[str] = ["length"] * n
+    stats = GenerationStats(requests=n)
+    if max_new_tokens <= 0:
+        return outputs, reasons, stats
+    pending = list(range(n))
+    prompt_lens = [len(p) for p in prompts]
+
+    def accept(r: int, token: int) -> bool:
+        """Record a sampled token; True if the request goes on."""
+        if token in stop:
+            reasons[r] = "stop"
+            return False
+        outputs[r].append(token)
+        if callback is not None and callback(r, token) is False:
+            reasons[r] = "stop"
+            return False
+        if len(outputs[r]) >= max_new_tokens:
+            reasons[r] = "length"
+            return False
+        if prompt_lens[r] + len(outputs[r]) > max_seq_len:
+            # feeding this token would pass the longest length (generation.rs:208-212)
+            reasons[r] = "length"
+            return False
+        return True
+
+    while pending:
+        batch = plan_batch(pending, prompt_lens, max_new_tokens, batch_size, capacity_tokens, free_slots,
+                           page_size)
+        pending = pending[len(batch):]
+        stats.batches += 1
+        slots = {r: backend.alloc_slot() for r in batch}
+        backend.synchronize()
+        t0 = time.perf_counter()
+        first = backend.prefill([slots[r] for r in batch], [prompts[r] for r in batch], batch)
+        backend.synchronize()
+        stats.prefill_ms += (time.perf_counter() - t0) * 1e3
+        stats.prefill_tokens += sum(prompt_lens[r] for r in batch)
+        live: List[int] = []
+        for r, tok in zip(batch, first):
+            if accept(r, int(tok)):
+                live.append(r)
+            else:
+                backend.free_slot(slots.pop(r))
+        t0 = time.perf_counter()
+        while live:
+            toks = backend.decode([slots[r] for r in live], [outputs[r][-1] for r in live], live,
+                                  [len(outputs[r]) for r in live])
+            stats.decode_steps += 1
+            stats.decode_tokens += len(live)
+            still: List[int] = []
+            for r, tok in zip(live, toks):
+                if accept(r, int(tok)):
+                    still.append(r)
+                else:
+                    backend.free_slot(slots.pop(r))
+            live = still
+        backend.synchronize()
+        stats.decode_ms += (time.perf_counter() - t0) * 1e3
+    return outputs, reasons, stats

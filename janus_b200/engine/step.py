@@ -1,0 +1,230 @@
+"""The step function: run the tokens a batch of sequences brings, from the
+cache that earlier steps left, and return the logits at the wanted places.
+
+A step's sequences either all bring their prompts (unequal lengths, packed
+without padding) or all bring one token; both go through the same code with
+per-token positions, so the logits at a position do not depend on how the
+tokens were cut into steps or on what else is in the batch.  (The reference runs
+one token per row per call with one shared position,
+crates/janus-engine/src/model/transformer/forward.rs:25,139-141.)
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Dict, List, Optional, Sequence, Tuple
+
+import numpy as np
+import torch
+
+from ..cache import PAGE_SIZE, CacheFull, CacheView, GroupStepView, SequenceCache
+from .model import DecoderModel
+from .workspace import Workspace
+
+
+class StepError(ValueError):
+    """A step that cannot run: a dead slot, a token outside the vocabulary, a
+    sequence past its longest length.  Raised before anything is launched."""
+
+
+@dataclass
+class EngineOptions:
+    max_tokens: int = 4096            # tokens the live sequences hold at most (each rounded up to a page)
+    max_seq_len: Optional[int] = None  # longest sequence; default: the model's max positions
+    max_slots: Optional[int] = None    # live sequences at most; default: one per page, at most 1024
+    use_graphs: bool = True            # replay decode steps from CUDA graphs
+
+
+@dataclass
+class StepEntry:
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()           # places among `tokens` whose logits are wanted
+
+
+class StepContext:
+    """What a step hands the parts (all tensors int32 on the device)."""
+
+    def __init__(self):
+        self.n_tokens = 0
+        self.n_seqs = 0
+        self.is_decode = False
+        self.max_q_len = 0
+        self.max_kv_len_bound = 0        # host upper bound of the longest sequence after this step
+        self.token_ids: torch.Tensor = None
+        self.positions: torch.Tensor = None
+        self.token_seq: torch.Tensor = None   # index of each token's sequence within the step
+        self.q_start: torch.Tensor = None     # [n_seqs + 1] offsets of each sequence's tokens
+        self.kv_len: torch.Tensor = None      # [n_seqs] length of each sequence after this step
+        self.seq_slot: torch.Tensor = None    # [n_seqs] cache slot of each sequence
+        self.groups: List[GroupStepView] = []
+        self.workspace: Workspace = None
+        self.cache: SequenceCache = None
+        self.dtype: torch.dtype = None
+
+    def cache_view(self, place: int) -> CacheView:
+        cache = self.cache
+        gi = cache.group_of_place.get(place)
+        if gi is not None:
+            g = cache.groups[gi]
+            return CacheView(k=g.k[place], v=g.v[place], group=self.groups[gi])
+        if place in cache.states:
+            return CacheView(state=cache.states[place])
+        return CacheView()
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
+
+
+class Engine:
+    def __init__(self, model: DecoderModel, options: Optional[EngineOptions] = None):
+        self.model = model
+        self.options = options or EngineOptions()
+        self.device, self.dtype = model.device, model.dtype
+        if self.device.type != "cuda":
+            raise RuntimeError("the engine runs on a CUDA device only; there is no CPU path")
+        o = self.options
+        self.max_seq_len = min(o.max_seq_len or model.spec.max_positions, model.spec.max_positions)
+        n_pages = max(1, (o.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE)
+        n_slots = o.max_slots or min(n_pages, 1024)
+        self.cache = SequenceCache(model.place_cache_specs(), o.max_tokens, n_slots, self.dtype, self.device)
+        self.workspace = Workspace(self.device)
+        self._pinned: Optional[torch.Tensor] = None
+        self._graphs: Dict[Tuple, object] = {}
+
+    # -- slots -----------------------------------------------------------------
+    def alloc_slot(self) -> int:
+        return self.cache.alloc_slot()
+
+    def free_slot(self, slot: int) -> None:
+        self.cache.free_slot(slot)
+
+    # -- the step --------------------------------------------------------------
+    def _validate(self, entries: Sequence[StepEntry]) -> None:
+        if not entries:
+            raise StepError("a step needs at least one sequence")
+        seen = set()
+        V = self.model.vocab_size
+        for e in entries:
+            if not self.cache.is_live(e.slot):
+                raise StepError(f"slot {e.slot} is not held by a live sequence")
+            if e.slot in seen:
+                raise StepError(f"slot {e.slot} appears twice in one step")
+            seen.add(e.slot)
+            n = len(e.tokens)
+            if n == 0:
+                raise StepError(f"slot {e.slot} brings no tokens")
+            bad = [t for t in e.tokens if not 0 <= int(t) < V]
+            if bad:
+                raise StepError(f"token id {bad[0]} is outside the vocabulary of {V}")
+            if self.cache.lengths[e.slot] + n > self.max_seq_len:
+                raise StepError(
+                    f"slot {e.slot} would reach {self.cache.lengths[e.slot] + n} tokens, the longest "
+                    f"sequence allowed is {self.max_seq_len}")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise StepError(f"wanted place {w} is outside the {n} tokens that slot {e.slot} brings")
+
+    def _reserve(self, entries: Sequence[StepEntry]) -> None:
+        done = []
+        try:
+            for e in entries:
+                self.cache.reserve(e.slot, len(e.tokens))
+                done.append(e)
+        except CacheFull:
+            for e in done:
+                for g in self.cache.groups:
+                    need = (self.cache.lengths[e.slot] + PAGE_SIZE - 1) // PAGE_SIZE
+                    while len(g.pages[e.slot]) > need:
+                        g.pool.give_back(g.pages[e.slot].pop())
+            raise
+
+    def build_context(self, entries: Sequence[StepEntry], pages_capacity: Optional[int] = None,
+                      into: Optional[torch.Tensor] = None):
+        """Pack the step's index arrays into one int32 buffer, copy it to the
+        device once, and hand out views.  Returns (ctx, want_rows)."""
+        cache = self.cache
+        S = len(entries)
+        lens = [len(e.tokens) for e in entries]
+        starts = [cache.lengths[e.slot] for e in entries]
+        T = sum(lens)
+        after = [s + n for s, n in zip(starts, lens)]
+        P = max((a + PAGE_SIZE - 1) // PAGE_SIZE for a in after)
+        if pages_capacity is not None:
+            if P > pages_capacity:
+                raise StepError("a sequence outgrew the page capacity this step was laid out for")
+            P = pages_capacity
+        wants: List[int] = []
+        q_start = [0]
+        for e, n in zip(entries, lens):
+            wants.extend(q_start[-1] + int(w) for w in e.want)
+            q_start.append(q_start[-1] + n)
+        W = len(wants)
+        G = len(cache.groups)
+        sizes = [T, T, T, S + 1, S, S, W] + [T, S * P] * G
+        offsets = [0]
+        for s in sizes:
+            offsets.append(offsets[-1] + _pad4(s))
+        host = np.zeros(offsets[-1], dtype=np.int32)
+        o = offsets
+        host[o[0]:o[0] + T] = np.concatenate([np.asarray(e.tokens, dtype=np.int32) for e in entries])
+        host[o[1]:o[1] + T] = np.concatenate([np.arange(s, s + n, dtype=np.int32) for s, n in zip(starts, lens)])
+        host[o[2]:o[2] + T] = np.repeat(np.arange(S, dtype=np.int32), lens)
+        host[o[3]:o[3] + S + 1] = q_start
+        host[o[4]:o[4] + S] = after
+        host[o[5]:o[5] + S] = [e.slot for e in entries]
+        host[o[6]:o[6] + W] = wants
+        for gi, g in enumerate(cache.groups):
+            base = 7 + 2 * gi
+            host[o[base]:o[base] + T] = np.concatenate(
+                [g.dest_rows(e.slot, s, n) for e, s, n in zip(entries, starts, lens)])
+            bt = np.full((S, P), -1, dtype=np.int32)
+            for i, e in enumerate(entries):
+                pages = g.pages[e.slot]
+                bt[i, :len(pages)] = pages
+            host[o[base + 1]:o[base + 1] + S * P] = bt.reshape(-1)
+        total = offsets[-1]
+        if self._pinned is None or self._pinned.numel() < total:
+            self._pinned = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
+        self._pinned[:total].numpy()[:] = host
+        if into is None:
+            dev = self._pinned[:total].to(self.device, non_blocking=True)
+        else:
+            if into.numel() < total:
+                raise StepError("the step's index buffer is smaller than this step needs")
+            into[:total].copy_(self._pinned[:total], non_blocking=True)
+            dev = into
+        # The pinned buffer is reused by the next step: wait until this copy has left it.
+        copied = torch.cuda.Event()
+        copied.record()
+        self._copy_done = copied
+
+        def seg(i: int, n: int) -> torch.Tensor:
+            return dev[offsets[i]:offsets[i] + n]
+
+        ctx = StepContext()
+        ctx.n_tokens, ctx.n_seqs = T, S
+        ctx.is_decode = all(n == 1 for n in lens)
+        ctx.max_q_len = max(lens)
+        ctx.max_kv_len_bound = P * PAGE_SIZE
+        ctx.token_ids, ctx.positions, ctx.token_seq = seg(0, T), seg(1, T), seg(2, T)
+        ctx.q_start, ctx.kv_len, ctx.seq_slot = seg(3, S + 1), seg(4, S), seg(5, S)
+        ctx.groups = [GroupStepView(seg(7 + 2 * gi, T), seg(8 + 2 * gi, S * P).view(S, P), PAGE_SIZE)
+                      for gi in range(G)]
+        ctx.workspace, ctx.cache, ctx.dtype = self.workspace, cache, self.dtype
+        return ctx, seg(6, W), total
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Run one step; returns float32 logits [number of wanted places, vocab]
+        on the device, in the order of the entries and of their `want`."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        self._validate(entries)
+        self._reserve(entries)
+        if getattr(self, "_copy_done", None) is not None:
+            self._copy_done.synchronize()
+        ctx, want_rows, _ = self.build_context(entries)
+        logits = torch.empty((want_rows.shape[0], self.model.vocab_size), dtype=torch.float32, device=self.device)
+        self.model.forward(ctx, want_rows, logits)
+        for e in entries:
+            self.cache.advance(e.slot, len(e.tokens))
+        return logits

@@ -1,0 +1,180 @@
+"""Python faces of the CUDA kernels: each function checks its tensors, passes
+raw pointers and the current stream to the exported C function, and raises on
+a non-zero return.  Nothing here computes; there is no other code path.
+"""
+from __future__ import annotations
+
+import ctypes
+from typing import Optional
+
+import torch
+
+from .build import library
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor must be on a CUDA device (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
+
+
+def _check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code >= 10000:
+        names = {10001: "size not supported (see stderr)", 10002: "dtype not supported",
+                 10003: "tensor map could not be encoded"}
+        raise KernelError(f"{what}: {names.get(code, 'error')} (code {code})")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+# -- embedding, norm, elementwise ---------------------------------------------
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, :] = float32(table[ids[t], :])"""
+    T, H = out.shape
+    _need(table, "embed table")
+    _need(ids, "token ids", torch.int32, (T,))
+    _need(out, "embed out", torch.float32)
+    if table.shape[1] != H:
+        raise KernelError(f"embed: table width {table.shape[1]} != output width {H}")
+    _check(library("elementwise").jb_embed_gather(
+        _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), T, H, _stream()), "embed_gather")
+
+
+def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, out: torch.Tensor,
+            row_index: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[row_index[r] or r] / sqrt(mean(x^2) + eps) * gamma"""
+    rows, H = out.shape
+    _need(x, "rmsnorm x", torch.float32)
+    _need(gamma, "rmsnorm gamma", None, (H,))
+    _need(out, "rmsnorm out")
+    if x.shape[1] != H:
+        raise KernelError(f"rmsnorm: input width {x.shape[1]} != output width {H}")
+    if row_index is not None:
+        _need(row_index, "rmsnorm row_index", torch.int32, (rows,))
+    elif x.shape[0] < rows:
+        raise KernelError("rmsnorm: fewer input rows than output rows")
+    _check(library("elementwise").jb_rmsnorm(
+        _ptr(x), _ptr(row_index), _ptr(gamma), dtype_code(gamma.dtype), ctypes.c_float(eps), _ptr(out),
+        dtype_code(out.dtype), rows, H, _stream()), "rmsnorm")
+
+
+def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
+    """residual += float32(delta), elementwise, in place"""
+    _need(residual, "residual", torch.float32)
+    _need(delta, "delta", None, residual.shape)
+    _check(library("elementwise").jb_residual_add(
+        _ptr(residual), _ptr(delta), dtype_code(delta.dtype), ctypes.c_longlong(residual.numel()), _stream()),
+        "residual_add")
+
+
+def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, I + c]"""
+    T, I = out.shape
+    _need(gate_up, "swiglu input", out.dtype, (T, 2 * I))
+    _need(out, "swiglu out")
+    _check(library("elementwise").jb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()),
+           "swiglu")
+
+
+# -- rotary positions + cache append --------------------------------------------
+def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[torch.Tensor],
+                     positions: torch.Tensor, dest: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
+                     v_cache: Optional[torch.Tensor], nh: int, nkv: int, hd: int, page_size: int,
+                     write_kv: bool = True) -> None:
+    T = q_out.shape[0]
+    width = (nh + 2 * nkv) * hd if write_kv else nh * hd
+    _need(qkv, "qkv", q_out.dtype)
+    if qkv.shape[0] != T or qkv.shape[1] < width:
+        raise KernelError(f"rope: qkv shape {tuple(qkv.shape)} does not hold {T} rows of width {width}")
+    _need(q_out, "q_out", None, (T, nh * hd))
+    _need(positions, "positions", torch.int32, (T,))
+    rotate = cos_sin is not None
+    if rotate:
+        _need(cos_sin, "rope table", torch.float32)
+        if cos_sin.shape[1:] != (hd // 2, 2):
+            raise KernelError(f"rope: table shape {tuple(cos_sin.shape)} does not fit head_dim {hd}")
+    if write_kv:
+        _need(dest, "cache rows", torch.int32, (T,))
+        _need(k_cache, "k cache", q_out.dtype)
+        _need(v_cache, "v cache", q_out.dtype)
+    _check(library("rope_cache").jb_rope_cache_write(
+        _ptr(qkv), qkv.shape[1], _ptr(q_out), dtype_code(q_out.dtype), _ptr(cos_sin),
+        cos_sin.shape[0] if rotate else 0, _ptr(positions), _ptr(dest), _ptr(k_cache), _ptr(v_cache),
+        T, nh, nkv, hd, page_size, int(rotate), int(write_kv), _stream()), "rope_cache_write")
+
+
+# -- float32 matrix product and attention ------------------------------------------
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool = False) -> None:
+    """y[T, N] (+)= x[T, K] . w[N, K]^T in true float32"""
+    T, K = x.shape
+    N = w.shape[0]
+    _need(x, "gemm x", torch.float32)
+    _need(w, "gemm w", torch.float32, (N, K))
+    _need(y, "gemm y", torch.float32, (T, N))
+    _check(library("gemm_f32").jb_gemm_f32(_ptr(x), _ptr(w), _ptr(y), T, N, K, K, N, int(accumulate), _stream()),
+           "gemm_f32")
+
+
+def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                  block_table: torch.Tensor, token_slot: torch.Tensor, positions: torch.Tensor,
+                  nh: int, nkv: int, hd: int, page_size: int, window: int, scale: float) -> None:
+    T = q.shape[0]
+    _need(q, "attention q", torch.float32, (T, nh * hd))
+    _need(out, "attention out", torch.float32, (T, nh * hd))
+    _need(k_cache, "k cache", torch.float32)
+    _need(v_cache, "v cache", torch.float32)
+    _need(block_table, "block table", torch.int32)
+    _need(token_slot, "token slots", torch.int32, (T,))
+    _need(positions, "positions", torch.int32, (T,))
+    _check(library("attention_f32").jb_attention_f32(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(token_slot), _ptr(positions),
+        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale), _stream()),
+        "attention_f32")
+
+
+# -- sampling -----------------------------------------------------------------------
+def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_k: int, top_p: float,
+           repetition_penalty: float, counts: Optional[torch.Tensor], count_rows: Optional[torch.Tensor],
+           seed: int, seq_ids: torch.Tensor, steps: torch.Tensor) -> None:
+    B, V = logits.shape
+    _need(logits, "logits", torch.float32)
+    _need(out_ids, "sampled ids", torch.int32, (B,))
+    _need(seq_ids, "sequence ids", torch.int32, (B,))
+    _need(steps, "step counters", torch.int32, (B,))
+    if counts is not None:
+        _need(counts, "token counts", torch.int32)
+        _need(count_rows, "count rows", torch.int32, (B,))
+        if counts.shape[1] != V:
+            raise KernelError("sample: counts width differs from the vocabulary")
+    _check(library("sampling").jb_sample(
+        _ptr(logits), B, V, _ptr(out_ids), ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p),
+        ctypes.c_float(repetition_penalty), _ptr(counts), _ptr(count_rows),
+        ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(seq_ids), _ptr(steps), _stream()), "sample")

@@ -1,0 +1,87 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v projections as one stacked product; rotary positions on q and k fused
+with the append of k (rotated) and v to the cache; causal attention of every
+new token over its sequence's cached keys (optionally only the last `window`);
+output projection added into the residual stream.  Formulas:
+crates/janus-engine/src/model/block.rs:239-363 and
+crates/janus-engine/src/compute/shaders/attention.wgsl:96-115,170-185
+(kv head of query head h is floor(h*nkv/nh); score = dot * 1/sqrt(head_dim)).
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional
+
+import torch
+
+from ..kernels import ops
+from .base import KVSpec, Mixer, PartSpec, make_part, register_part
+from .linear import Linear
+
+
+class GQAttention(Mixer):
+    def __init__(self, hidden_size: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: Optional[PartSpec] = None, window: int = 0,
+                 dtype: torch.dtype = torch.bfloat16, device: torch.device = torch.device("cuda")):
+        if num_heads % num_kv_heads:
+            raise ValueError(f"{num_heads} heads are not a multiple of {num_kv_heads} key/value heads")
+        self.hidden_size, self.nh, self.nkv, self.hd = hidden_size, num_heads, num_kv_heads, head_dim
+        self.window = int(window)
+        self.dtype, self.device = dtype, device
+        self.scale = 1.0 / math.sqrt(head_dim)          # crates/janus-engine/src/compute/ops/attention.rs:98
+        self.position = make_part("position", position, dtype, device) if position is not None else None
+        self.q_width, self.kv_width = num_heads * head_dim, num_kv_heads * head_dim
+        self.qkv = Linear(hidden_size, self.q_width + 2 * self.kv_width, dtype, device)
+        self.q_only: Optional[Linear] = None             # view of the q rows, for layers that read another cache
+        self.o = Linear(self.q_width, hidden_size, dtype, device)
+
+    def cache_spec(self) -> KVSpec:
+        return KVSpec(self.nkv, self.hd, self.window)
+
+    def weight_shapes(self):
+        return {"q": ((self.q_width, self.hidden_size), "normal"),
+                "k": ((self.kv_width, self.hidden_size), "normal"),
+                "v": ((self.kv_width, self.hidden_size), "normal"),
+                "o": ((self.hidden_size, self.q_width), "normal")}
+
+    def load(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor) -> None:
+        self.qkv.load([q, k, v])
+        self.o.load([o])
+        self.q_only = Linear(self.hidden_size, self.q_width, self.dtype, self.device)
+        self.q_only.weight = self.qkv.weight[: self.q_width]
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+        T = x.shape[0]
+        ws = ctx.workspace
+        proj = self.qkv if writes_cache else self.q_only
+        qkv = ws.get("qkv", (T, proj.out_features), self.dtype)
+        proj.forward(x, qkv)
+        q = ws.get("q_rot", (T, self.q_width), self.dtype)
+        table = self.position.fused_rotary_table() if self.position is not None else None
+        if self.position is not None and table is None:
+            self.position.apply(qkv[:, : self.q_width], self.nh, self.hd, ctx.positions)
+            if writes_cache:
+                self.position.apply(qkv[:, self.q_width: self.q_width + self.kv_width], self.nkv, self.hd,
+                                    ctx.positions)
+        group = cache_view.group
+        ops.rope_cache_write(qkv, q, table, ctx.positions, group.dest_rows if writes_cache else None,
+                             cache_view.k if writes_cache else None, cache_view.v if writes_cache else None,
+                             self.nh, self.nkv, self.hd, group.page_size, write_kv=writes_cache)
+        attn = ws.get("attn_out", (T, self.q_width), self.dtype)
+        if self.dtype == torch.float32:
+            ops.attention_f32(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.token_seq,
+                              ctx.positions, self.nh, self.nkv, self.hd, group.page_size, self.window,
+                              self.scale)
+        elif ctx.is_decode:
+            ops.attention_bf16_decode(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.kv_len,
+                                      self.nh, self.nkv, self.hd, group.page_size, self.window, self.scale,
+                                      ctx.workspace, ctx.max_kv_len_bound)
+        else:
+            ops.attention_bf16_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start,
+                                       ctx.kv_len, ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, self.hd,
+                                       group.page_size, self.window, self.scale)
+        self.o.forward_add(attn, residual)
+
+
+register_part("mixer", "gqa_attention", GQAttention)

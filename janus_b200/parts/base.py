@@ -1,0 +1,157 @@
+"""Interfaces of the parts a decoder is put together from, their registries,
+and the data that describes a model (`ModelSpec`).
+
+A model is data: for each layer a mixer, a feed-forward, norms and their
+arrangement, each named by a registered kind with its sizes and constants as
+parameters and the checkpoint names of its weights; plus the order in which
+layers run.  No part knows which model it is in.
+
+Interfaces
+----------
+Norm          load(gamma); forward(x_f32[rows,H] , out[rows,H], row_index=None)
+Position      fused_rotary_table() -> [positions, head_dim/2, 2] float32 or None;
+              apply(x[T, heads*head_dim], heads, head_dim, positions) in place (only if no table)
+Mixer         cache_spec() -> KVSpec | StateSpec | None
+              forward(x[T,H], residual_f32[T,H], ctx, cache_view, writes_cache): adds its output into residual
+FeedForward   forward(x[T,H], residual_f32[T,H], ctx): adds its output into residual
+all parts     weight_shapes() -> {parameter: (shape, init)};  load(**tensors)
+
+The residual stream is float32 in both engine dtypes, so the residual sum is
+always made in 32 bits; `x` is the normed layer input in the engine dtype.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable, Dict, List, Optional, Tuple, Union
+
+import torch
+
+
+# --------------------------------------------------------------------------
+# what a mixer needs from the cache
+# --------------------------------------------------------------------------
+@dataclass(frozen=True)
+class KVSpec:
+    """Keys and values per token.  window = 0 keeps every key; window = w keeps
+    the last w keys (the query's own position included)."""
+    n_kv_heads: int
+    head_dim: int
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateSpec:
+    """Per-sequence state of fixed size, float32, zeroed when a slot is taken."""
+    shape: Tuple[int, ...]
+
+
+CacheSpec = Union[KVSpec, StateSpec, None]
+
+
+# --------------------------------------------------------------------------
+# model description
+# --------------------------------------------------------------------------
+@dataclass(frozen=True)
+class PartSpec:
+    kind: str                                   # a registered kind
+    params: Dict[str, Any] = field(default_factory=dict)
+    weights: Dict[str, str] = field(default_factory=dict)   # part parameter -> checkpoint tensor name
+
+
+@dataclass(frozen=True)
+class LayerSpec:
+    mixer: PartSpec
+    feed_forward: PartSpec
+    mixer_norm: PartSpec
+    feed_forward_norm: PartSpec
+    arrangement: str = "pre_norm"
+
+
+@dataclass(frozen=True)
+class ScheduleEntry:
+    """One place in the order of execution: which layer runs, and whose cache it
+    reads (None = its own, written at this place; an earlier place's index = it
+    reads that place's keys and values and writes none)."""
+    layer: int
+    reads_cache_of: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class ModelSpec:
+    hidden_size: int
+    vocab_size: int
+    layers: Tuple[LayerSpec, ...]
+    schedule: Tuple[ScheduleEntry, ...]
+    final_norm: PartSpec
+    embedding_weight: str
+    head_weight: Optional[str]                  # None = tied to the embedding
+    max_positions: int
+    ignorable_weights: Tuple[str, ...] = ()
+
+
+# --------------------------------------------------------------------------
+# registries
+# --------------------------------------------------------------------------
+_REGISTRIES: Dict[str, Dict[str, Callable[..., Any]]] = {
+    "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "arrangement": {},
+}
+
+
+def register_part(family: str, kind: str, factory: Callable[..., Any]) -> None:
+    """`factory(**params, dtype=..., device=...)` builds the part.  `family` is
+    one of mixer, feed_forward, norm, position, arrangement."""
+    if family not in _REGISTRIES:
+        raise KeyError(f"unknown family '{family}' (have {sorted(_REGISTRIES)})")
+    _REGISTRIES[family][kind] = factory
+
+
+def make_part(family: str, spec: PartSpec, dtype: torch.dtype, device: torch.device):
+    try:
+        factory = _REGISTRIES[family][spec.kind]
+    except KeyError:
+        raise KeyError(f"no {family} of kind '{spec.kind}' is registered "
+                       f"(have {sorted(_REGISTRIES[family])})") from None
+    return factory(**spec.params, dtype=dtype, device=device)
+
+
+def registered_parts(family: str) -> List[str]:
+    return sorted(_REGISTRIES[family])
+
+
+# --------------------------------------------------------------------------
+# base classes (documentation of the interfaces; parts need not inherit)
+# --------------------------------------------------------------------------
+class Part:
+    def weight_shapes(self) -> Dict[str, Tuple[Tuple[int, ...], str]]:
+        """{parameter: (shape, init)} with init "normal" or "ones"."""
+        return {}
+
+    def load(self, **tensors: torch.Tensor) -> None:
+        if tensors:
+            raise TypeError(f"{type(self).__name__} takes no weights, got {sorted(tensors)}")
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def fused_rotary_table(self) -> Optional[torch.Tensor]:
+        return None
+
+    def apply(self, x: torch.Tensor, heads: int, head_dim: int, positions: torch.Tensor) -> None:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_spec(self) -> CacheSpec:
+        return None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx) -> None:
+        raise NotImplementedError

@@ -1,0 +1,26 @@
+"""Arrangement of a layer's parts.  Pre-norm, as the reference's block:
+h1 = x + mixer(norm1(x)); out = h1 + feed_forward(norm2(h1))
+(crates/janus-engine/src/model/block.rs:223-233,355-380,447-455).  The parts
+add into the float32 residual stream themselves."""
+from __future__ import annotations
+
+import torch
+
+from .base import register_part
+
+
+class PreNormBlock:
+    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, hidden_size: int, dtype: torch.dtype):
+        self.mixer_norm, self.mixer = mixer_norm, mixer
+        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+        self.hidden_size, self.dtype = hidden_size, dtype
+
+    def forward(self, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+        x = ctx.workspace.get("normed", (residual.shape[0], self.hidden_size), self.dtype)
+        self.mixer_norm.forward(residual, x)
+        self.mixer.forward(x, residual, ctx, cache_view, writes_cache)
+        self.feed_forward_norm.forward(residual, x)
+        self.feed_forward.forward(x, residual, ctx)
+
+
+register_part("arrangement", "pre_norm", PreNormBlock)

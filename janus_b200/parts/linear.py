@@ -1,0 +1,80 @@
+"""Matrix products y = x W^T with W stored [out, in] (no bias anywhere in the
+architecture: crates/janus-engine/src/model/block.rs:239-276 looks none up).
+
+The engine dtype picks the kernel: float32 runs the CUDA-core product (true
+32-bit), bfloat16 runs the tcgen05 tensor-core product with float32
+accumulation.  Three epilogues: store, add into the float32 residual stream,
+and SiLU-gate (for a stacked gate/up weight).
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from ..kernels import ops
+
+
+def _to_engine(w: torch.Tensor, dtype: torch.dtype, device: torch.device) -> torch.Tensor:
+    return w.to(device=device, dtype=dtype).contiguous()
+
+
+class Linear:
+    """One weight matrix, possibly the row-wise stack of several tensors of the
+    checkpoint (q, k, v stacked so that one product serves all three)."""
+
+    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device):
+        self.in_features, self.out_features = in_features, out_features
+        self.dtype, self.device = dtype, device
+        self.weight: Optional[torch.Tensor] = None
+
+    def load(self, tensors: Sequence[torch.Tensor]) -> None:
+        parts = [_to_engine(t, self.dtype, self.device) for t in tensors]
+        w = parts[0] if len(parts) == 1 else torch.cat(parts, dim=0)
+        if tuple(w.shape) != (self.out_features, self.in_features):
+            raise ValueError(f"weight of shape {tuple(w.shape)} does not fit "
+                             f"({self.out_features}, {self.in_features})")
+        self.weight = w
+
+    def share(self, other: "Linear") -> None:
+        """Use another product's storage (a head tied to the embedding)."""
+        self.weight = other.weight
+
+    # y = x W^T, stored in y's dtype (engine dtype, or float32 for logits)
+    def forward(self, x: torch.Tensor, y: torch.Tensor) -> None:
+        if self.dtype == torch.float32:
+            ops.gemm_f32(x, self.weight, y, accumulate=False)
+        else:
+            ops.gemm_bf16(x, self.weight, y, mode="store")
+
+    # residual += x W^T, the sum made in float32
+    def forward_add(self, x: torch.Tensor, residual: torch.Tensor) -> None:
+        if self.dtype == torch.float32:
+            ops.gemm_f32(x, self.weight, residual, accumulate=True)
+        else:
+            ops.gemm_bf16(x, self.weight, residual, mode="add")
+
+
+class GatedLinear:
+    """out = silu(x Wg^T) * (x Wu^T) with Wg stacked over Wu
+    (crates/janus-engine/src/model/block.rs:383-430)."""
+
+    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device):
+        self.in_features, self.out_features = in_features, out_features
+        self.dtype, self.device = dtype, device
+        self.weight: Optional[torch.Tensor] = None   # [2 * out, in]
+
+    def load(self, gate: torch.Tensor, up: torch.Tensor) -> None:
+        w = torch.cat([_to_engine(gate, self.dtype, self.device), _to_engine(up, self.dtype, self.device)], dim=0)
+        if tuple(w.shape) != (2 * self.out_features, self.in_features):
+            raise ValueError(f"gate/up weights of shape {tuple(w.shape)} do not fit "
+                             f"(2*{self.out_features}, {self.in_features})")
+        self.weight = w
+
+    def forward(self, x: torch.Tensor, out: torch.Tensor, ctx) -> None:
+        if self.dtype == torch.float32:
+            gu = ctx.workspace.get("gate_up", (x.shape[0], 2 * self.out_features), torch.float32)
+            ops.gemm_f32(x, self.weight, gu, accumulate=False)
+            ops.swiglu(gu, out)
+        else:
+            ops.gemm_bf16(x, self.weight, out, mode="swiglu")
