@@ -11,15 +11,15 @@
 
 namespace {
 
-template <typename TT>
-__global__ void rope_cache_kernel(const TT* __restrict__ qkv, int qkv_stride, TT* __restrict__ q_out,
+template <typename TI, typename TT>
+__global__ void rope_cache_kernel(const TI* __restrict__ qkv, int qkv_stride, TT* __restrict__ q_out,
                                   const float* __restrict__ cos_sin, const int* __restrict__ positions,
                                   const int* __restrict__ dest, TT* __restrict__ k_cache,
                                   TT* __restrict__ v_cache, int nh, int nkv, int hd, int page_size,
                                   int rotate, int write_kv) {
   const int t = blockIdx.x;
   const int half = hd >> 1;
-  const TT* row = qkv + (size_t)t * qkv_stride;
+  const TI* row = qkv + (size_t)t * qkv_stride;
   const int pos = positions[t];
   const float* cs = cos_sin + (size_t)pos * half * 2;
   const int n_rot_heads = write_kv ? nh + nkv : nh;
@@ -51,10 +51,10 @@ __global__ void rope_cache_kernel(const TT* __restrict__ qkv, int qkv_stride, TT
     }
   }
   if (write_kv) {
-    const TT* vrow = row + (size_t)(nh + nkv) * hd;
+    const TI* vrow = row + (size_t)(nh + nkv) * hd;
     for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
       const int kvh = idx / hd, d = idx % hd;
-      v_cache[kv_base + (size_t)kvh * page_size * hd + d] = vrow[idx];
+      v_cache[kv_base + (size_t)kvh * page_size * hd + d] = jb::from_f32<TT>(jb::to_f32(vrow[idx]));
     }
   }
 }
@@ -63,25 +63,25 @@ __global__ void rope_cache_kernel(const TT* __restrict__ qkv, int qkv_stride, TT
 
 // rotate = 0 leaves q and k unrotated (a mixer without rotary positions);
 // write_kv = 0 rotates q only (a layer that reads another layer's cache).
-JB_EXPORT int jb_rope_cache_write(const void* qkv, int qkv_stride, void* q_out, int dtype, const float* cos_sin,
-                                  int table_positions, const int* positions, const int* dest, void* k_cache,
+// in_dtype is the dtype of qkv (float32 accumulators of the projection, or the
+// engine dtype), out_dtype that of q_out and of the cache.
+JB_EXPORT int jb_rope_cache_write(const void* qkv, int qkv_stride, int in_dtype, void* q_out, int out_dtype,
+                                  const float* cos_sin, const int* positions, const int* dest, void* k_cache,
                                   void* v_cache, int T, int nh, int nkv, int hd, int page_size, int rotate,
                                   int write_kv, cudaStream_t stream) {
   if (T <= 0) return 0;
   JB_REFUSE(hd % 2 != 0, "rope: head_dim %d must be even", hd);
-  (void)table_positions;
   const int work = (nh + nkv) * (hd / 2);
   const int threads = work >= 1024 ? 256 : 128;
-  if (dtype == JB_F32)
-    rope_cache_kernel<float><<<T, threads, 0, stream>>>((const float*)qkv, qkv_stride, (float*)q_out, cos_sin,
-                                                        positions, dest, (float*)k_cache, (float*)v_cache, nh,
-                                                        nkv, hd, page_size, rotate, write_kv);
-  else if (dtype == JB_BF16)
-    rope_cache_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>(
-        (const __nv_bfloat16*)qkv, qkv_stride, (__nv_bfloat16*)q_out, cos_sin, positions, dest,
-        (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, nh, nkv, hd, page_size, rotate, write_kv);
-  else
-    return JB_ERR_BAD_DTYPE;
+#define JB_LAUNCH_ROPE(TI, TT)                                                                                  \
+  rope_cache_kernel<TI, TT><<<T, threads, 0, stream>>>((const TI*)qkv, qkv_stride, (TT*)q_out, cos_sin, positions, \
+                                                       dest, (TT*)k_cache, (TT*)v_cache, nh, nkv, hd, page_size,  \
+                                                       rotate, write_kv)
+  if (in_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_ROPE(float, float);
+  else if (in_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_ROPE(float, __nv_bfloat16);
+  else if (in_dtype == JB_BF16 && out_dtype == JB_BF16) JB_LAUNCH_ROPE(__nv_bfloat16, __nv_bfloat16);
+  else return JB_ERR_BAD_DTYPE;
+#undef JB_LAUNCH_ROPE
   JB_CHECK_LAUNCH();
   return 0;
 }

@@ -111,7 +111,7 @@ def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[t
                      write_kv: bool = True) -> None:
     T = q_out.shape[0]
     width = (nh + 2 * nkv) * hd if write_kv else nh * hd
-    _need(qkv, "qkv", q_out.dtype)
+    _need(qkv, "qkv")
     if qkv.shape[0] != T or qkv.shape[1] < width:
         raise KernelError(f"rope: qkv shape {tuple(qkv.shape)} does not hold {T} rows of width {width}")
     _need(q_out, "q_out", None, (T, nh * hd))
@@ -126,8 +126,8 @@ def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[t
         _need(k_cache, "k cache", q_out.dtype)
         _need(v_cache, "v cache", q_out.dtype)
     _check(library("rope_cache").jb_rope_cache_write(
-        _ptr(qkv), qkv.shape[1], _ptr(q_out), dtype_code(q_out.dtype), _ptr(cos_sin),
-        cos_sin.shape[0] if rotate else 0, _ptr(positions), _ptr(dest), _ptr(k_cache), _ptr(v_cache),
+        _ptr(qkv), qkv.shape[1], dtype_code(qkv.dtype), _ptr(q_out), dtype_code(q_out.dtype), _ptr(cos_sin),
+        _ptr(positions), _ptr(dest), _ptr(k_cache), _ptr(v_cache),
         T, nh, nkv, hd, page_size, int(rotate), int(write_kv), _stream()), "rope_cache_write")
 
 
@@ -160,6 +160,73 @@ def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
         "attention_f32")
 
 
+# -- bfloat16 tensor-core matrix product --------------------------------------------
+_GEMM_MODES = {"store": None, "add": 2, "swiglu": 3}
+_status = {}
+SM_COUNT_TARGET = 296      # CTAs wanted in flight for a weight-streaming product (two per SM)
+
+
+def kernel_status(device: torch.device) -> torch.Tensor:
+    """Device int that a kernel sets when one of its bounded waits ran out."""
+    key = str(device)
+    if key not in _status:
+        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _status[key]
+
+
+def check_kernel_status(device: torch.device) -> None:
+    """Synchronises; raises if a tensor-core kernel gave up on a wait."""
+    code = int(kernel_status(device).item())
+    if code != 0:
+        kernel_status(device).zero_()
+        who = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, "?")
+        raise KernelError(f"a tensor-core kernel timed out waiting on an mbarrier ({who}, code {code})")
+
+
+def split_k_for(T: int, N: int, K: int) -> int:
+    """How many slices of K a weight-streaming product (few tokens) is cut into
+    so that enough CTAs are in flight; 1 for prefill-sized T."""
+    if T > 64:
+        return 1
+    tiles = (N + 127) // 128
+    k_tiles = (K + 63) // 64
+    return max(1, min(SM_COUNT_TARGET // max(tiles, 1), k_tiles // 4))
+
+
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "store",
+              split_k: Optional[int] = None) -> None:
+    """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation.
+    mode "store": y[T, N] = result (bf16 or float32 by y's dtype);
+    mode "add":   y[T, N] += result, y float32 (K may be split, sums meet by atomic adds);
+    mode "swiglu": w = [2N, K] (gate rows over up rows), y[T, N] = silu(gate) * up in bf16."""
+    T, K = x.shape
+    _need(x, "gemm x", torch.bfloat16)
+    _need(w, "gemm w", torch.bfloat16)
+    _need(y, "gemm y")
+    if mode == "swiglu":
+        N = w.shape[0] // 2
+        code, want = 3, torch.bfloat16
+        if w.shape != (2 * N, K):
+            raise KernelError(f"gemm swiglu: weight {tuple(w.shape)} is not [2N, {K}]")
+    else:
+        N = w.shape[0]
+        if w.shape != (N, K):
+            raise KernelError(f"gemm: weight {tuple(w.shape)} does not fit K = {K}")
+        if mode == "add":
+            code, want = 2, torch.float32
+        elif mode == "store":
+            code, want = (1, torch.float32) if y.dtype == torch.float32 else (0, torch.bfloat16)
+        else:
+            raise KernelError(f"gemm: unknown mode {mode!r}")
+    if y.dtype != want or tuple(y.shape) != (T, N):
+        raise KernelError(f"gemm {mode}: output must be {want} [{T}, {N}], got {y.dtype} {tuple(y.shape)}")
+    if split_k is None:
+        split_k = split_k_for(T, N, K) if code == 2 else 1
+    _check(library("gemm_bf16_tc").jb_gemm_bf16(
+        _ptr(x), _ptr(w), _ptr(y), T, N, K, N, code, int(split_k), _ptr(kernel_status(x.device)), _stream()),
+        "gemm_bf16")
+
+
 # -- sampling -----------------------------------------------------------------------
 def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_k: int, top_p: float,
            repetition_penalty: float, counts: Optional[torch.Tensor], count_rows: Optional[torch.Tensor],
@@ -178,3 +245,62 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_
         _ptr(logits), B, V, _ptr(out_ids), ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p),
         ctypes.c_float(repetition_penalty), _ptr(counts), _ptr(count_rows),
         ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(seq_ids), _ptr(steps), _stream()), "sample")
+
+
+# -- bfloat16 attention (one library per head size) -----------------------------------
+def _attention_lib(hd: int):
+    if hd % 8 or not 8 <= hd <= 256:
+        raise KernelError(f"attention_bf16: head_dim {hd} is not a multiple of 8 in [8, 256]")
+    return library("attention_bf16", {"JB_HEAD_DIM": int(hd)})
+
+
+def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                           block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
+                           n_seqs: int, max_q_len: int, nh: int, nkv: int, hd: int, page_size: int,
+                           window: int, scale: float) -> None:
+    """Causal attention of each sequence's new tokens (the last q_len positions of
+    its kv_len) over its cached keys."""
+    T = q.shape[0]
+    _need(q, "attention q", torch.bfloat16, (T, nh * hd))
+    _need(out, "attention out", torch.bfloat16, (T, nh * hd))
+    _need(k_cache, "k cache", torch.bfloat16)
+    _need(v_cache, "v cache", torch.bfloat16)
+    _need(block_table, "block table", torch.int32)
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(kv_len, "kv_len", torch.int32, (n_seqs,))
+    _check(_attention_lib(hd).jb_attention_bf16_prefill(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
+        n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
+        _stream()), "attention_bf16_prefill")
+
+
+def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: int) -> int:
+    """Splits of the key range per (sequence, kv head) so that about two CTAs
+    per SM are in flight, at most one split per page."""
+    pages = max(1, (max_kv_len + page_size - 1) // page_size)
+    return max(1, min(pages, SM_COUNT_TARGET // max(1, n_seqs * nkv_blocks)))
+
+
+def attention_bf16_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                          block_table: torch.Tensor, kv_len: torch.Tensor, nh: int, nkv: int, hd: int,
+                          page_size: int, window: int, scale: float, workspace, max_kv_len: int,
+                          n_splits: Optional[int] = None) -> None:
+    """One new token per sequence (its last position) over its cached keys."""
+    B = q.shape[0]
+    _need(q, "attention q", torch.bfloat16, (B, nh * hd))
+    _need(out, "attention out", torch.bfloat16, (B, nh * hd))
+    _need(k_cache, "k cache", torch.bfloat16)
+    _need(v_cache, "v cache", torch.bfloat16)
+    _need(block_table, "block table", torch.int32)
+    _need(kv_len, "kv_len", torch.int32, (B,))
+    n_rb = (nh // nkv + 15) // 16
+    if n_splits is None:
+        n_splits = decode_splits_for(B, nkv * n_rb, max_kv_len, page_size)
+    part_o = part_ml = None
+    if n_splits > 1:
+        part_o = workspace.get("attn_part_o", (B * nh * n_splits * hd,), torch.float32)
+        part_ml = workspace.get("attn_part_ml", (B * nh * n_splits * 2,), torch.float32)
+    _check(_attention_lib(hd).jb_attention_bf16_decode(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
+        _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
+        int(n_splits), _stream()), "attention_bf16_decode")

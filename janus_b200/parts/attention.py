@@ -55,7 +55,8 @@ class GQAttention(Mixer):
         T = x.shape[0]
         ws = ctx.workspace
         proj = self.qkv if writes_cache else self.q_only
-        qkv = ws.get("qkv", (T, proj.out_features), self.dtype)
+        # the projection's float32 accumulators go straight into the rotation
+        qkv = ws.get("qkv", (T, proj.out_features), torch.float32)
         proj.forward(x, qkv)
         q = ws.get("q_rot", (T, self.q_width), self.dtype)
         table = self.position.fused_rotary_table() if self.position is not None else None

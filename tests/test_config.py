@@ -1,0 +1,85 @@
+"""Configuration and registry (mirrors the reference's own config tests,
+crates/janus-engine/src/model/config.rs:447-552 and tests/error_handling.rs)."""
+import json
+
+import pytest
+
+from helpers import TINY_A, TINY_B
+from janus_b200.config import (ConfigError, LlamaConfig, read_config_json, registered_architectures,
+                               resolve_architecture)
+
+
+def test_parse_tiny_configs():
+    a = LlamaConfig.from_dict(TINY_A)
+    assert (a.hidden_size, a.num_hidden_layers, a.num_attention_heads, a.num_key_value_heads) == (64, 2, 4, 2)
+    assert a.head_dim == 16 and a.rope_scaling is None and a.eos_token_id == (250, 251)
+    b = LlamaConfig.from_dict(TINY_B)
+    assert b.head_dim == 40 and b.tie_word_embeddings and b.rms_norm_eps == 1e-6
+    assert b.rope_scaling.factor == 4.0 and b.rope_scaling.original_max_position_embeddings == 32
+    assert b.eos_token_id == (383,)
+
+
+def test_defaults_follow_the_reference():
+    c = LlamaConfig.from_dict(dict(hidden_size=128, num_hidden_layers=1, num_attention_heads=8, vocab_size=50))
+    assert c.num_key_value_heads == 8           # config.rs:235-241
+    assert c.head_dim == 16                      # config.rs:246-248
+    assert c.intermediate_size == 512            # config.rs:254-260
+    assert c.max_position_embeddings == 2048     # config.rs:265-271
+    assert c.rms_norm_eps == 1e-5                # config.rs:96-98
+    assert c.rope_theta == 10000.0               # config.rs:299
+    assert c.architectures == ("LlamaForCausalLM",)
+
+
+def test_round_trip_through_dict():
+    for cfg in (TINY_A, TINY_B):
+        c = LlamaConfig.from_dict(cfg)
+        assert LlamaConfig.from_dict(json.loads(json.dumps(c.to_dict()))) == c
+
+
+@pytest.mark.parametrize("patch, word", [
+    (dict(hidden_size=None), "hidden_size"),
+    (dict(vocab_size=0), "vocab_size"),
+    (dict(num_attention_heads=5, head_dim=None), "divisible"),
+    (dict(num_key_value_heads=3), "num_key_value_heads"),
+    (dict(head_dim=15), "head_dim"),
+    (dict(hidden_size=40000, head_dim=16), "hidden_size"),
+    (dict(num_hidden_layers=300), "num_hidden_layers"),
+    (dict(vocab_size=2_000_000), "vocab_size"),
+    (dict(rms_norm_eps="tiny"), "rms_norm_eps"),
+    (dict(rope_scaling=dict(rope_type="yarn", factor=2.0)), "rope_scaling"),
+    (dict(rope_scaling=dict(rope_type="llama3", factor=2.0, low_freq_factor=4.0, high_freq_factor=1.0,
+                            original_max_position_embeddings=32)), "low_freq_factor"),
+    (dict(rope_scaling=dict(rope_type="llama3", factor=2.0)), "low_freq_factor"),
+    (dict(eos_token_id=9999), "eos_token_id"),
+    (dict(tie_word_embeddings="yes"), "tie_word_embeddings"),
+])
+def test_errors_name_the_key(patch, word):
+    cfg = dict(TINY_A)
+    for k, v in patch.items():
+        if v is None:
+            cfg.pop(k, None)
+        else:
+            cfg[k] = v
+    with pytest.raises(ConfigError) as e:
+        LlamaConfig.from_dict(cfg)
+    assert word in str(e.value)
+
+
+def test_registry_resolves_and_refuses():
+    assert "LlamaForCausalLM" in registered_architectures()
+    assert resolve_architecture(TINY_A).config_class is LlamaConfig
+    assert resolve_architecture({k: v for k, v in TINY_A.items() if k != "architectures"}).name == "LlamaForCausalLM"
+    with pytest.raises(ConfigError) as e:
+        resolve_architecture(dict(TINY_A, architectures=["MambaForCausalLM"]))
+    assert "MambaForCausalLM" in str(e.value) and "LlamaForCausalLM" in str(e.value)
+
+
+def test_read_config_json_errors(tmp_path):
+    with pytest.raises(ConfigError):
+        read_config_json(str(tmp_path))                      # folder without config.json
+    (tmp_path / "config.json").write_text("{not json")
+    with pytest.raises(ConfigError):
+        read_config_json(str(tmp_path))
+    (tmp_path / "config.json").write_text(json.dumps(TINY_B))
+    assert read_config_json(str(tmp_path))["hidden_size"] == 96
+    assert read_config_json(str(tmp_path / "config.json"))["hidden_size"] == 96

@@ -1,0 +1,115 @@
+"""The generation loop's decisions, with a scripted backend instead of a device."""
+import pytest
+
+from janus_b200.engine.generate import plan_batch, run_generation, tokens_held
+from janus_b200.sampling import SamplerConfig
+
+
+class ScriptedBackend:
+    """Next token of request r after k generated tokens is script[r][k]."""
+
+    def __init__(self, script, n_slots):
+        self.script, self.free = script, list(range(n_slots))
+        self.held, self.log, self.max_live = {}, [], 0
+
+    def alloc_slot(self):
+        s = self.free.pop()
+        assert s not in self.held
+        self.held[s] = 0
+        self.max_live = max(self.max_live, len(self.held))
+        return s
+
+    def free_slot(self, s):
+        assert s in self.held, "slot freed twice"
+        del self.held[s]
+        self.free.append(s)
+
+    def synchronize(self):
+        pass
+
+    def prefill(self, slots, prompts, requests):
+        self.log.append(("prefill", list(requests), [len(p) for p in prompts]))
+        for s, p in zip(slots, prompts):
+            assert self.held[s] == 0
+            self.held[s] = len(p)
+        return [self.script[r][0] for r in requests]
+
+    def decode(self, slots, last, requests, steps):
+        self.log.append(("decode", list(requests), list(steps)))
+        for s, r, t, k in zip(slots, requests, last, steps):
+            assert t == self.script[r][k - 1]            # the token fed is the one just produced
+            self.held[s] += 1
+        return [self.script[r][k] for r, k in zip(requests, steps)]
+
+
+def run(script, prompts, max_new, stop=(), batch=8, cap=10_000, max_seq=1000, slots=8, cb=None):
+    b = ScriptedBackend(script, slots)
+    out = run_generation(b, prompts, max_new, stop, batch, cap, max_seq, slots, 64, cb)
+    assert not b.held, "a slot was never given back"
+    return b, out
+
+
+def test_unequal_prompts_stop_tokens_and_early_finish():
+    script = {0: [5, 6, 99, 1], 1: [99, 1, 1, 1], 2: [7, 8, 9, 10]}
+    b, (toks, reasons, stats) = run(script, [[1] * 3, [1] * 10, [1] * 5], 4, stop=[99])
+    assert toks == [[5, 6], [], [7, 8, 9, 10]]            # the stop token is not part of the output
+    assert reasons == ["stop", "stop", "length"]
+    assert b.log[0] == ("prefill", [0, 1, 2], [3, 10, 5])
+    assert [e[1] for e in b.log[1:]] == [[0, 2], [0, 2], [2]]   # finished sequences leave the batch
+    assert stats.decode_steps == 3 and stats.decode_tokens == 5 and stats.prefill_tokens == 18
+    assert stats.batches == 1
+
+
+def test_batches_follow_one_another():
+    script = {r: [r + 1] * 10 for r in range(5)}
+    b, (toks, reasons, stats) = run(script, [[1, 2]] * 5, 3, batch=2)
+    assert stats.batches == 3 and b.max_live == 2
+    assert toks == [[r + 1] * 3 for r in range(5)] and reasons == ["length"] * 5
+    assert [e[1] for e in b.log if e[0] == "prefill"] == [[0, 1], [2, 3], [4]]
+
+
+def test_capacity_limits_the_batch_and_errors_when_nothing_fits():
+    # each request holds 64 * ceil((60 + 9) / 64) = 128 tokens
+    assert tokens_held(60, 10, 64) == 128
+    assert plan_batch([0, 1, 2], [60, 60, 60], 10, 8, 256, 8, 64) == [0, 1]
+    assert plan_batch([0, 1, 2], [60, 60, 60], 10, 8, 10_000, 1, 64) == [0]
+    with pytest.raises(ValueError, match="request 0"):
+        plan_batch([0], [60], 10, 8, 64, 8, 64)
+
+
+def test_budgets():
+    script = {0: list(range(10, 30))}
+    _, (toks, reasons, _) = run(script, [[1, 2, 3]], 0)
+    assert toks == [[]]
+    _, (toks, reasons, _) = run(script, [[1, 2, 3]], 1)
+    assert toks == [[10]] and reasons == ["length"]
+    # the longest sequence ends generation: 3 prompt tokens, room for 5 positions
+    b, (toks, reasons, _) = run(script, [[1, 2, 3]], 20, max_seq=5)
+    assert toks == [[10, 11, 12]] and reasons == ["length"]
+    assert max(b.log[-1][2]) == 2                          # the last token produced is never fed
+    with pytest.raises(ValueError, match="empty"):
+        run(script, [[]], 3)
+    with pytest.raises(ValueError, match="longest"):
+        run(script, [[1] * 9], 3, max_seq=5)
+
+
+def test_callback_can_end_a_request():
+    script = {0: [1, 2, 3, 4], 1: [5, 6, 7, 8]}
+    seen = []
+
+    def cb(r, t):
+        seen.append((r, t))
+        return not (r == 0 and t == 2)
+
+    _, (toks, reasons, _) = run(script, [[9], [9]], 4, cb=cb)
+    assert toks == [[1, 2], [5, 6, 7, 8]] and reasons == ["stop", "length"]
+    assert (0, 3) not in seen
+
+
+def test_sampler_config_names_and_checks():
+    c = SamplerConfig()
+    assert (c.temperature, c.top_k, c.top_p, c.beam_width, c.max_tokens) == (0.0, 0, 1.0, 1, 128)
+    for bad in (dict(temperature=-1.0), dict(top_k=-1), dict(top_p=0.0), dict(top_p=1.5),
+                dict(repetition_penalty=0.0), dict(beam_width=4), dict(max_tokens=-1)):
+        with pytest.raises(ValueError):
+            SamplerConfig(**bad).validate()

@@ -1,0 +1,323 @@
+"""Each CUDA kernel alone against a plain float32/float64 computation of the
+same op, at sizes other than the tiny models': widths and vocabularies that are
+no power of two, head sizes in steps of 8, any number of heads and groups."""
+import math
+
+import pytest
+import torch
+
+import plain_llama as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = 64
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from janus_b200.kernels import ops as o
+    return o
+
+
+def close(got, ref, tol):
+    got, ref = got.double().cpu(), ref.double().cpu()
+    assert torch.isfinite(got).all()
+    err = float((got - ref).abs().max() / (ref.abs().max() + 1e-12))
+    assert err < tol, f"relative error {err:.3e} >= {tol}"
+
+
+# ---------------------------------------------------------------- elementwise
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed_gather(ops, dtype):
+    V, H, T = 301, 200, 37
+    table = torch.randn(V, H, device=DEV).to(dtype)
+    ids = torch.randint(0, V, (T,), device=DEV, dtype=torch.int32)
+    out = torch.empty(T, H, device=DEV)
+    ops.embed_gather(table, ids, out)
+    assert torch.equal(out.cpu(), P.embed(table.float().cpu(), ids.cpu()))
+
+
+@pytest.mark.parametrize("H", [200, 4100])
+@pytest.mark.parametrize("gdt, odt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                      (torch.bfloat16, torch.bfloat16)])
+def test_rmsnorm(ops, H, gdt, odt):
+    T = 19
+    x = torch.randn(T, H, device=DEV) * 3
+    gamma = (1 + 0.1 * torch.randn(H, device=DEV)).to(gdt)
+    out = torch.empty(T, H, device=DEV, dtype=odt)
+    ops.rmsnorm(x, gamma, 1e-6, out)
+    ref = P.rms_norm(x.cpu(), gamma.float().cpu(), 1e-6)
+    close(out, ref, 2e-6 if odt == torch.float32 else 5e-3)
+    rows = torch.tensor([18, 0, 7], device=DEV, dtype=torch.int32)
+    out2 = torch.empty(3, H, device=DEV, dtype=odt)
+    ops.rmsnorm(x, gamma, 1e-6, out2, rows)
+    assert torch.equal(out2, out[rows.long()])
+
+
+def test_residual_add_and_swiglu(ops):
+    T, I = 13, 330
+    r = torch.randn(T, I, device=DEV)
+    d = torch.randn(T, I, device=DEV).to(torch.bfloat16)
+    want = r.cpu() + d.float().cpu()
+    ops.residual_add(r, d)
+    assert torch.equal(r.cpu(), want)
+    gu = torch.randn(T, 2 * I, device=DEV) * 2
+    out = torch.empty(T, I, device=DEV)
+    ops.swiglu(gu, out)
+    close(out, P.silu(gu[:, :I].cpu()) * gu[:, I:].cpu(), 2e-6)
+
+
+# ---------------------------------------------------------------- rope + cache
+@pytest.mark.parametrize("in_dt, out_dt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
+                                           (torch.bfloat16, torch.bfloat16)])
+def test_rope_cache_write(ops, in_dt, out_dt):
+    nh, nkv, hd, T, n_pages = 6, 3, 24, 29, 7
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV).to(in_dt)
+    positions = torch.randint(0, 300, (T,), device=DEV, dtype=torch.int32)
+    dest = torch.randperm(n_pages * PAGE, device=DEV)[:T].to(torch.int32)
+    inv = P.rope_inv_freq(hd, 12345.0, None)
+    cos, sin = P.rope_cos_sin(torch.arange(300), inv)
+    table = torch.stack([cos, sin], -1).contiguous().to(DEV)
+    kc = torch.zeros(n_pages, nkv, PAGE, hd, device=DEV, dtype=out_dt)
+    vc = torch.zeros_like(kc)
+    q = torch.empty(T, nh * hd, device=DEV, dtype=out_dt)
+    ops.rope_cache_write(qkv, q, table, positions, dest, kc, vc, nh, nkv, hd, PAGE)
+    x = qkv.float().cpu()
+    c, s = P.rope_cos_sin(positions.cpu(), inv)
+    q_ref = P.apply_rope(x[:, :nh * hd].view(T, nh, hd), c, s).reshape(T, -1)
+    k_ref = P.apply_rope(x[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), c, s)
+    v_ref = x[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    tol = 2e-6 if out_dt == torch.float32 else 5e-3
+    close(q, q_ref, tol)
+    page, row = (dest.cpu() // PAGE).long(), (dest.cpu() % PAGE).long()
+    close(kc.cpu()[page, :, row, :], k_ref, tol)
+    close(vc.cpu()[page, :, row, :], v_ref, tol)
+    untouched = torch.ones(n_pages * PAGE, dtype=torch.bool)
+    untouched[dest.cpu().long()] = False
+    assert float(kc.cpu().permute(0, 2, 1, 3).reshape(n_pages * PAGE, -1)[untouched].abs().sum()) == 0.0
+    # a layer that reads another layer's cache rotates q only
+    q2 = torch.empty_like(q)
+    ops.rope_cache_write(qkv[:, :nh * hd].contiguous(), q2, table, positions, None, None, None, nh, nkv, hd, PAGE,
+                         write_kv=False)
+    assert torch.equal(q2, q)
+
+
+# ---------------------------------------------------------------- float32 product
+@pytest.mark.parametrize("T, N, K", [(1, 101, 53), (37, 64, 64), (130, 257, 321)])
+def test_gemm_f32(ops, T, N, K):
+    x, w = torch.randn(T, K, device=DEV), torch.randn(N, K, device=DEV)
+    y = torch.empty(T, N, device=DEV)
+    ops.gemm_f32(x, w, y)
+    ref = x.double().cpu() @ w.double().cpu().T
+    close(y, ref, 3e-6)
+    base = torch.randn(T, N, device=DEV)
+    y2 = base.clone()
+    ops.gemm_f32(x, w, y2, accumulate=True)
+    close(y2, ref + base.double().cpu(), 3e-6)
+    # a row's result does not depend on the batch it is in
+    y1 = torch.empty(1, N, device=DEV)
+    ops.gemm_f32(x[T - 1:].contiguous(), w, y1)
+    assert torch.equal(y1[0], y[T - 1])
+
+
+# ---------------------------------------------------------------- paged attention
+def paged(k, v, dtype, n_extra_pages=3, seed=0):
+    """Scatter dense per-sequence K/V ([len, nkv, hd] each) over shuffled pages.
+    Returns (k_cache, v_cache, block_table) with unused entries -1."""
+    nkv, hd = k[0].shape[1], k[0].shape[2]
+    need = [(x.shape[0] + PAGE - 1) // PAGE for x in k]
+    n_pages = sum(need) + n_extra_pages
+    g = torch.Generator().manual_seed(seed)
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    kc = torch.randn(n_pages, nkv, PAGE, hd, generator=g) * 5      # stale content must never be read
+    vc = torch.randn(n_pages, nkv, PAGE, hd, generator=g) * 5
+    bt = torch.full((len(k), max(need)), -1, dtype=torch.int32)
+    for s, (ks, vs) in enumerate(zip(k, v)):
+        for i in range(need[s]):
+            p = perm.pop()
+            bt[s, i] = p
+            n = min(PAGE, ks.shape[0] - i * PAGE)
+            kc[p, :, :n] = ks[i * PAGE:i * PAGE + n].transpose(0, 1)
+            vc[p, :, :n] = vs[i * PAGE:i * PAGE + n].transpose(0, 1)
+    return kc.to(DEV).to(dtype), vc.to(DEV).to(dtype), bt.to(DEV)
+
+
+def attention_case(nh, nkv, hd, lens, q_lens, dtype, seed=0, spike=True):
+    """Sequences of `lens` keys whose last `q_lens` tokens are the queries."""
+    g = torch.Generator().manual_seed(seed)
+    rnd = lambda *s: torch.randn(*s, generator=g).to(dtype).float()   # values exactly representable in `dtype`
+    qs, ks, vs = [], [], []
+    for n, nq in zip(lens, q_lens):
+        q, k, v = rnd(n, nh, hd), rnd(n, nkv, hd), rnd(n, nkv, hd)
+        if spike and n > 3:
+            # one far key stands out for the last query: a kernel that misses it is far off
+            k[1] = (q[n - 1, 0] * 1.5).to(dtype).float()
+            v[1] = (v[1] + 3.0).to(dtype).float()
+        qs.append(q); ks.append(k); vs.append(v)
+    return qs, ks, vs
+
+
+def plain_attention_rows(qs, ks, vs, q_lens, window):
+    outs = []
+    for q, k, v, nq in zip(qs, ks, vs, q_lens):
+        full = P.attention(q, k, v, window=window if window > 0 else None)
+        outs.append(full[q.shape[0] - nq:].reshape(nq, -1))
+    return torch.cat(outs, 0)
+
+
+@pytest.mark.parametrize("nh, nkv, hd, window", [(4, 2, 16, 0), (6, 2, 24, 0), (3, 1, 40, 0), (5, 5, 72, 70),
+                                                 (8, 2, 256, 0)])
+def test_attention_f32(ops, nh, nkv, hd, window):
+    lens, q_lens = [130, 5, 64, 200], [130, 1, 3, 17]
+    qs, ks, vs = attention_case(nh, nkv, hd, lens, q_lens, torch.float32)
+    kc, vc, bt = paged(ks, vs, torch.float32)
+    q = torch.cat([x[n - nq:].reshape(nq, -1) for x, n, nq in zip(qs, lens, q_lens)]).to(DEV)
+    token_seq = torch.cat([torch.full((nq,), i) for i, nq in enumerate(q_lens)]).to(DEV).int()
+    positions = torch.cat([torch.arange(n - nq, n) for n, nq in zip(lens, q_lens)]).to(DEV).int()
+    out = torch.empty_like(q)
+    ops.attention_f32(q, kc, vc, out, bt, token_seq, positions, nh, nkv, hd, PAGE, window, 1 / math.sqrt(hd))
+    close(out, plain_attention_rows(qs, ks, vs, q_lens, window), 2e-5)
+
+
+@pytest.mark.parametrize("nh, nkv, hd, window", [(4, 2, 16, 0), (6, 2, 24, 0), (3, 1, 40, 0), (5, 5, 72, 70),
+                                                 (32, 8, 128, 0), (8, 1, 64, 100), (40, 2, 32, 0), (4, 4, 256, 0)])
+def test_attention_bf16_prefill(ops, nh, nkv, hd, window):
+    lens, q_lens = [130, 5, 64, 200, 1], [130, 2, 64, 17, 1]
+    qs, ks, vs = attention_case(nh, nkv, hd, lens, q_lens, torch.bfloat16)
+    kc, vc, bt = paged(ks, vs, torch.bfloat16)
+    q = torch.cat([x[n - nq:].reshape(nq, -1) for x, n, nq in zip(qs, lens, q_lens)]).to(DEV).to(torch.bfloat16)
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), device=DEV, dtype=torch.int32)
+    kv_len = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    out = torch.empty_like(q)
+    ops.attention_bf16_prefill(q, kc, vc, out, bt, q_start, kv_len, len(lens), max(q_lens), nh, nkv, hd, PAGE,
+                               window, 1 / math.sqrt(hd))
+    close(out, plain_attention_rows(qs, ks, vs, q_lens, window), 1.5e-2)
+
+
+class _WS:
+    def __init__(self):
+        self.bufs = {}
+
+    def get(self, name, shape, dtype):
+        self.bufs[name] = torch.full(tuple(shape), float("nan"), device=DEV, dtype=dtype)
+        return self.bufs[name]
+
+
+@pytest.mark.parametrize("nh, nkv, hd, window", [(4, 2, 16, 0), (3, 1, 40, 0), (32, 8, 128, 0), (5, 5, 72, 70),
+                                                 (40, 2, 32, 0), (4, 4, 256, 0)])
+@pytest.mark.parametrize("n_splits", [1, 3, None])
+def test_attention_bf16_decode(ops, nh, nkv, hd, window, n_splits):
+    lens = [130, 5, 64, 1, 700, 65]
+    q_lens = [1] * len(lens)
+    qs, ks, vs = attention_case(nh, nkv, hd, lens, q_lens, torch.bfloat16, seed=1)
+    kc, vc, bt = paged(ks, vs, torch.bfloat16, seed=1)
+    q = torch.cat([x[n - 1:].reshape(1, -1) for x, n in zip(qs, lens)]).to(DEV).to(torch.bfloat16)
+    kv_len = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    out = torch.empty_like(q)
+    ops.attention_bf16_decode(q, kc, vc, out, bt, kv_len, nh, nkv, hd, PAGE, window, 1 / math.sqrt(hd), _WS(),
+                              max(lens), n_splits=n_splits)
+    close(out, plain_attention_rows(qs, ks, vs, q_lens, window), 1.5e-2)
+
+
+# ---------------------------------------------------------------- tensor-core product
+def bf16_inputs(T, N, K, seed):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, K, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16)
+    return x.to(DEV), w.to(DEV)
+
+
+@pytest.mark.parametrize("T", [1, 5, 16, 33, 64, 100, 300])
+@pytest.mark.parametrize("N, K", [(200, 120), (128, 64), (1000, 320), (384, 4096)])
+def test_gemm_bf16_store_and_add(ops, T, N, K):
+    x, w = bf16_inputs(T, N, K, T + N)
+    ref = x.double().cpu() @ w.double().cpu().T
+    y16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, y16)
+    close(y16, ref, 6e-3)
+    y32 = torch.full((T, N), float("nan"), device=DEV)
+    ops.gemm_bf16(x, w, y32)
+    close(y32, ref, 2e-5)
+    base = torch.randn(T, N, device=DEV)
+    for split in (1, None, 4):
+        acc = base.clone()
+        ops.gemm_bf16(x, w, acc, mode="add", split_k=split)
+        close(acc, ref + base.double().cpu(), 2e-5)
+    ops.check_kernel_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("T", [1, 17, 64, 200])
+@pytest.mark.parametrize("I, K", [(192, 64), (320, 96), (1000, 2048)])
+def test_gemm_bf16_swiglu(ops, T, I, K):
+    x, w = bf16_inputs(T, 2 * I, K, T + I)
+    w = (w.float() * 3).to(torch.bfloat16)
+    y = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, y, mode="swiglu")
+    ref = P.swiglu_ffn(x.double().cpu(), w[:I].double().cpu(), w[I:].double().cpu(), torch.eye(I, dtype=torch.float64))
+    close(y, ref, 6e-3)
+    ops.check_kernel_status(torch.device(DEV))
+
+
+def test_gemm_bf16_refuses_what_it_cannot_take(ops):
+    x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
+    w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(Exception, match="size not supported"):
+        ops.gemm_bf16(x, w, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16))
+
+
+# ---------------------------------------------------------------- sampling
+def run_sample(ops, logits, temperature, top_k=0, top_p=1.0, penalty=1.0, counts=None, seed=11, steps=None):
+    B, V = logits.shape
+    out = torch.empty(B, dtype=torch.int32, device=DEV)
+    seq = torch.arange(B, dtype=torch.int32, device=DEV)
+    st = torch.zeros(B, dtype=torch.int32, device=DEV) if steps is None else steps
+    rows = torch.arange(B, dtype=torch.int32, device=DEV)
+    ops.sample(logits, out, temperature, top_k, top_p, penalty, counts, rows, seed, seq, st)
+    return out.cpu().tolist()
+
+
+def test_greedy_lowest_index_wins(ops):
+    V = 1000
+    logits = torch.randn(5, V, device=DEV)
+    logits[0, 700] = logits[0, 300] = 50.0
+    logits[1, V - 1] = 60.0
+    logits[2, 0] = 60.0
+    got = run_sample(ops, logits, 0.0)
+    assert got == [P.argmax_lowest(logits[i].cpu()) for i in range(5)] and got[:3] == [300, V - 1, 0]
+
+
+@pytest.mark.parametrize("V", [384, 5003, 128256])
+@pytest.mark.parametrize("top_k, top_p", [(0, 1.0), (40, 1.0), (0, 0.8), (50, 0.9)])
+def test_temperature_sampling_follows_the_plain_distribution(ops, V, top_k, top_p):
+    B, T = 24, 0.8
+    g = torch.Generator().manual_seed(V + top_k)
+    logits = (torch.randn(B, V, generator=g) * 2.5).to(DEV)
+    got = run_sample(ops, logits, T, top_k, top_p, seed=5)
+    for b in range(B):
+        probs = P.sampling_distribution(logits[b].cpu(), T, top_k, top_p).double()
+        assert probs[got[b]] > 0, f"row {b}: token {got[b]} is outside the kept set"
+        cdf = torch.cumsum(probs, 0)
+        u = P.uniform_for(5, b, 0)
+        lo = float(cdf[got[b]] - probs[got[b]])
+        # the token's interval of the cumulative distribution holds u, up to float32 summation order
+        assert lo - 2e-4 <= u < float(cdf[got[b]]) + 2e-4, (b, got[b], lo, u, float(cdf[got[b]]))
+    # another step draws another number; the same step the same
+    assert run_sample(ops, logits, T, top_k, top_p, seed=5) == got
+    again = run_sample(ops, logits, T, top_k, top_p, seed=5, steps=torch.ones(B, dtype=torch.int32, device=DEV))
+    assert again != got
+
+
+def test_repetition_penalty_counts(ops):
+    V = 300
+    logits = torch.zeros(2, V, device=DEV)
+    logits[0, 10], logits[0, 20] = 4.0, 3.0
+    logits[1, 10], logits[1, 20] = -0.5, -1.0
+    logits[1, :10] = -3.0; logits[1, 11:20] = -3.0; logits[1, 21:] = -3.0
+    counts = torch.zeros(2, V, dtype=torch.int32, device=DEV)
+    assert run_sample(ops, logits, 0.0, penalty=2.0, counts=counts) == [10, 10]
+    assert counts[0, 10] == 1 and counts[1, 10] == 1                  # the kernel counted its own picks
+    # once counted: 4/2 < 3 and -0.5*2 = -1.0 ties with index 20 -> lowest index (10) still wins row 1
+    assert run_sample(ops, logits, 0.0, penalty=2.0, counts=counts) == [20, 10]
+    ctx = [[10, 20], [10, 10]]
+    want = [P.sample(logits[i].cpu(), 0.0, 0.0, repetition_penalty=2.0, context=ctx[i]) for i in range(2)]
+    assert run_sample(ops, logits, 0.0, penalty=2.0, counts=counts) == want
