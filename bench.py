@@ -1,0 +1,248 @@
+#!/usr/bin/env python3
+"""Benchmark of janus_b200 on one B200: decode tokens per second of a
+Llama-3.1-8B-shaped model with random bf16 weights (batch 8, sequences filled to
+2,048 tokens of a 4,096 context), plus prefill of 2,048 tokens and decode at
+batch 1 and 64.  A "step" is one decode step.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl reference]
+
+Prints one JSON line.  `value` is timed on the device with CUDA events around K
+steps of the engine's step function (index buffer copied from pinned host
+memory each step, kernels replayed from a CUDA graph); `e2e` is the same metric
+through `Model.generate` (host token ids in, sampled ids out each step).
+Each step reads every weight once (15 GB, far larger than the 126 MB L2), so no
+L2 flush is needed between steps.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: Llama-3.1-8B shape
+CONFIG_8B = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=32, num_attention_heads=32,
+    num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=128256,
+    max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=8192),
+    tie_word_embeddings=False)
+FILL = 2048          # tokens each sequence holds before decoding is timed
+PREFILL_TOKENS = 2048
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        try:
+            with open(path) as f:
+                d = json.load(f)
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
+        except (OSError, ValueError, KeyError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region is timed."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+        sm = [int(r[0]) for r in self.rows if len(r) >= 6 and r[0].isdigit()]
+        mx = [int(r[1]) for r in self.rows if len(r) >= 6 and r[1].isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(len(r) >= 6 and r[2 + i].lower() == "active" for r in self.rows)]
+        return dict(sm_mhz=int(statistics.median(sm)) if sm else None, sm_max_mhz=max(mx) if mx else None,
+                    reasons=reasons, samples=len(sm))
+
+
+def model_numbers(cfg, layers):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    nh, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    per_layer = H * (nh + 2 * nkv) * hd + nh * hd * H + 3 * H * I          # matrix elements
+    return dict(layer_params=per_layer, head_params=V * H, kv_bytes_per_token=2 * nkv * hd * 2 * layers,
+                norm_bytes=(2 * layers + 1) * H * 2)
+
+
+def decode_bytes(cfg, layers, batch, ctx):
+    n = model_numbers(cfg, layers)
+    return 2 * (layers * n["layer_params"] + n["head_params"]) + n["norm_bytes"] + batch * ctx * n["kv_bytes_per_token"]
+
+
+def prefill_flops(cfg, layers, T):
+    n = model_numbers(cfg, layers)
+    linear = 2 * T * layers * n["layer_params"] + 2 * n["head_params"]      # the head runs on one row
+    attention = layers * 4 * cfg["num_attention_heads"] * cfg["head_dim"] * T * (T + 1) // 2
+    return linear + attention
+
+
+def run_ours(args):
+    import torch
+
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    from janus_b200.kernels import ops
+
+    layers = args.layers or CONFIG_8B["num_hidden_layers"]
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers)
+    K, W = args.steps, args.warmup
+    batches = [1, 8, 64] if not args.quick else [8]
+    max_b = max(batches)
+    per_seq = FILL + 2 * (W + K) + 128
+    model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max_b * (per_seq + 64),
+                                   max_slots=max_b, norm_std=0.0)
+    eng = model.engine
+    dev = model.device
+    g = torch.Generator().manual_seed(0)
+    V = cfg["vocab_size"]
+
+    def tokens(n):
+        return torch.randint(0, V, (n,), generator=g).tolist()
+
+    def timed(fn, reps):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(dev)
+        start.record()
+        for _ in range(reps):
+            fn()
+        end.record()
+        torch.cuda.synchronize(dev)
+        return start.elapsed_time(end) / reps
+
+    # ---- prefill of 2,048 tokens ------------------------------------------------
+    prompt = tokens(PREFILL_TOKENS)
+
+    def one_prefill():
+        s = eng.alloc_slot()
+        eng.step([StepEntry(s, prompt, (PREFILL_TOKENS - 1,))])
+        eng.free_slot(s)
+
+    for _ in range(3):
+        one_prefill()
+    prefill_ms = timed(one_prefill, 5)
+    pk = peaks()
+    prefill = dict(value=round(PREFILL_TOKENS / prefill_ms * 1e3, 1), tokens=PREFILL_TOKENS, ms=round(prefill_ms, 3),
+                   frac=round(prefill_flops(cfg, layers, PREFILL_TOKENS) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4))
+
+    # ---- decode at each batch size ----------------------------------------------
+    results, launches = {}, {}
+    clocks = None
+    for B in batches:
+        slots = [eng.alloc_slot() for _ in range(B)]
+        for i in range(0, B, 8):                                   # fill the sequences, 8 prompts a step
+            eng.step([StepEntry(s, tokens(FILL), ()) for s in slots[i:i + 8]])
+        feed = [[int(t) for t in tokens(B)] for _ in range(W + K)]
+        it = iter(feed)
+
+        def one_step():
+            row = next(it)
+            eng.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, row)], borrow=True)
+
+        before = ops.launch_count()
+        for _ in range(W):
+            one_step()
+        per_step_launches = eng.last_graph_launches
+        sampler = ClockSampler() if B == args.batch else None
+        if sampler:
+            sampler.start()
+        ms = timed(one_step, K)
+        if sampler:
+            clocks = sampler.stop()
+        ops.check_kernel_status(dev)
+        results[B] = dict(ms=ms, tok_s=B / ms * 1e3)
+        launches[B] = per_step_launches * K
+        for s in slots:
+            eng.free_slot(s)
+
+    # ---- end to end through the public entry point ----------------------------------
+    B = args.batch
+    prompts = [tokens(FILL) for _ in range(B)]
+    model.generate(prompts, max_tokens=W + 2, ignore_eos=True)                       # warm-up (graphs are captured)
+    _, stats = model.generate(prompts, max_tokens=K + 1, ignore_eos=True)
+    e2e_tok_s = stats.decode_tokens_per_s
+
+    head = results[args.batch]
+    ctx = FILL + W + K // 2
+    nbytes = decode_bytes(cfg, layers, args.batch, ctx)
+    achieved = nbytes / (head["ms"] * 1e-3) / 1e9
+    out = {
+        "metric": "decode tok/s @ batch 8 (Llama-3-8B shape, bf16, ctx 4096, sequences at 2048)",
+        "value": round(head["tok_s"], 1), "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W,
+        "ms_per_step": round(head["ms"], 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic token ids, random-init weights (seed 2)", "impl": "janus_b200",
+        "config": {
+            "model": "Llama-3.1-8B shape", "layers": layers, "layers_of_config": CONFIG_8B["num_hidden_layers"],
+            "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+            "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+            "global_batch": args.batch, "seq_len": 4096, "filled_to": FILL, "prefill_tokens": PREFILL_TOKENS,
+            "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
+            "peaks": pk["source"],
+        },
+        "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": eng.last_step_h2d_bytes + 3 * 4 * B, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": launches[args.batch],
+        "prefill": prefill,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": {f"decode_b{b}": round(r["tok_s"], 1) for b, r in results.items() if b != args.batch},
+        "clocks": clocks,
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8, help="batch size of the headline number")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in `config`)")
+    ap.add_argument("--quick", action="store_true", help="headline batch only")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "DaCodeChick/Janus is a Rust workspace that runs WGSL shaders through wgpu (a graphics "
+                          "API): pip cannot install it, no cargo/rustc here, no graphics stack on this box"}))
+        return 0
+    if args.gpus != 1:
+        print(f"janus_b200 is a single-GPU library: --gpus {args.gpus} is not supported (run with --gpus 1)")
+        return 2
+    if args.warmup < 3:
+        args.warmup = 3
+    run_ours(args)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -48,7 +48,7 @@ class _EngineBackend:
         return self._sample(logits, slots, requests, [0] * len(slots))
 
     def decode(self, slots, last_tokens, requests, steps) -> List[int]:
-        logits = self.engine.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, last_tokens)])
+        logits = self.engine.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, last_tokens)], borrow=True)
         return self._sample(logits, slots, requests, steps)
 
 

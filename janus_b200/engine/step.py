@@ -17,6 +17,7 @@ import numpy as np
 import torch
 
 from ..cache import PAGE_SIZE, CacheFull, CacheView, GroupStepView, SequenceCache
+from ..kernels import ops
 from .model import DecoderModel
 from .workspace import Workspace
 
@@ -91,6 +92,8 @@ class Engine:
         self.workspace = Workspace(self.device)
         self._pinned: Optional[torch.Tensor] = None
         self._graphs: Dict[Tuple, object] = {}
+        self.last_graph_launches = 0       # kernels of this library in the last step
+        self.last_step_h2d_bytes = 0       # bytes of the last step's index buffer
 
     # -- slots -----------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -184,6 +187,7 @@ class Engine:
                 bt[i, :len(pages)] = pages
             host[o[base + 1]:o[base + 1] + S * P] = bt.reshape(-1)
         total = offsets[-1]
+        self.last_step_h2d_bytes = 4 * total
         if self._pinned is None or self._pinned.numel() < total:
             self._pinned = torch.empty(max(total, 4096), dtype=torch.int32, pin_memory=True)
         self._pinned[:total].numpy()[:] = host
@@ -214,17 +218,70 @@ class Engine:
         ctx.workspace, ctx.cache, ctx.dtype = self.workspace, cache, self.dtype
         return ctx, seg(6, W), total
 
-    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def step(self, entries: Sequence[StepEntry], borrow: bool = False) -> torch.Tensor:
         """Run one step; returns float32 logits [number of wanted places, vocab]
-        on the device, in the order of the entries and of their `want`."""
+        on the device, in the order of the entries and of their `want`.
+
+        With `borrow` the result may be a buffer that the next step overwrites
+        (the generation loop samples from it at once); otherwise it is the
+        caller's own."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         self._reserve(entries)
         if getattr(self, "_copy_done", None) is not None:
             self._copy_done.synchronize()
-        ctx, want_rows, _ = self.build_context(entries)
-        logits = torch.empty((want_rows.shape[0], self.model.vocab_size), dtype=torch.float32, device=self.device)
-        self.model.forward(ctx, want_rows, logits)
+        if (self.options.use_graphs and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
+            logits = self._graph_decode(entries)
+            if not borrow:
+                logits = logits.clone()
+        else:
+            ctx, want_rows, _ = self.build_context(entries)
+            logits = torch.empty((want_rows.shape[0], self.model.vocab_size), dtype=torch.float32,
+                                 device=self.device)
+            before = ops.launch_count()
+            self.model.forward(ctx, want_rows, logits)
+            self.last_graph_launches = ops.launch_count() - before
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
+        return logits
+
+    # -- decode steps replayed from CUDA graphs -----------------------------------
+    def _graph_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """One token per sequence, every sequence's logits wanted: the kernels of
+        the step are captured once per (batch size, page capacity) and replayed;
+        each replay only refreshes the step's index buffer.  The capacity is the
+        pages of the longest sequence, rounded up to a power of two, so that a
+        graph serves many steps before a sequence outgrows it."""
+        B = len(entries)
+        need = max((self.cache.lengths[e.slot] + 1 + PAGE_SIZE - 1) // PAGE_SIZE for e in entries)
+        cap = 1
+        while cap < need:
+            cap *= 2
+        key = (B, cap, self.workspace.generation)
+        rec = self._graphs.get(key)
+        if rec is None:
+            for k in [k for k in self._graphs if k[2] != self.workspace.generation]:
+                del self._graphs[k]          # buffers moved: those graphs hold stale addresses
+            _, _, total = self.build_context(entries, pages_capacity=cap)
+            meta = torch.zeros(total, dtype=torch.int32, device=self.device)
+            logits = torch.empty((B, self.model.vocab_size), dtype=torch.float32, device=self.device)
+            # an eager run first: it sizes the workspace and configures the kernels
+            self._copy_done.synchronize()
+            ctx, want_rows, _ = self.build_context(entries, pages_capacity=cap, into=meta)
+            self.model.forward(ctx, want_rows, logits)
+            torch.cuda.synchronize(self.device)
+            if self.workspace.generation != key[2]:
+                key = (B, cap, self.workspace.generation)
+            graph = torch.cuda.CUDAGraph()
+            before = ops.launch_count()
+            with torch.cuda.graph(graph):
+                self.model.forward(ctx, want_rows, logits)
+            rec = (graph, meta, logits, ops.launch_count() - before)
+            self._graphs[key] = rec
+            # the eager run and the capture wrote this step's keys already; replaying
+            # the graph below writes the same values again
+        graph, meta, logits, self.last_graph_launches = rec
+        self._copy_done.synchronize()
+        self.build_context(entries, pages_capacity=cap, into=meta)
+        graph.replay()
         return logits

@@ -45,8 +45,17 @@ def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
         raise KernelError(f"{name}: expected shape {tuple(shape)}, got {tuple(t.shape)}")
 
 
-def _check(code: int, what: str) -> None:
+_launches = [0]
+
+
+def launch_count() -> int:
+    """Kernels of this library launched (or captured into a graph) so far."""
+    return _launches[0]
+
+
+def _check(code: int, what: str, kernels: int = 1) -> None:
     if code == 0:
+        _launches[0] += kernels
         return
     if code >= 10000:
         names = {10001: "size not supported (see stderr)", 10002: "dtype not supported",
@@ -303,4 +312,4 @@ def attention_bf16_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     _check(_attention_lib(hd).jb_attention_bf16_decode(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
         _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
-        int(n_splits), _stream()), "attention_bf16_decode")
+        int(n_splits), _stream()), "attention_bf16_decode", kernels=2 if n_splits > 1 else 1)
