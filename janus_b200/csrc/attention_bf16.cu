@@ -471,3 +471,63 @@ JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const
   }
   return 0;
 }
+
+// ---------------------------------------------------------------------------
+// Entry point that allocates nothing (see attention_bf16_noalloc.h).
+// ---------------------------------------------------------------------------
+#include "attention_bf16_noalloc.h"
+
+namespace {
+
+// Scratch for the key splits' partial results.  In host code this name is only a
+// stand-in for the symbol; the device address comes from cudaGetSymbolAddress.
+static __device__ __align__(256) float noalloc_scratch[JB_NOALLOC_SCRATCH_FLOATS];
+
+constexpr int NOALLOC_MAX_DEVICES = 64;
+float* noalloc_device_ptr[NOALLOC_MAX_DEVICES];   // per device: address of noalloc_scratch there
+
+}  // namespace
+
+JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                               const int* block_table, const int* kv_len, int n_seqs, int nh,
+                                               int nkv, int hd, int page_size, int max_pages, int window,
+                                               float scale, int n_splits, cudaStream_t stream) {
+  if (n_seqs <= 0) return 0;
+  JB_REFUSE(hd != HD, "attention_bf16: built for head_dim %d, called with %d", HD, hd);
+  JB_REFUSE(page_size != PAGE, "attention_bf16: page size %d (need %d)", page_size, PAGE);
+  JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_bf16: %d heads are not a multiple of %d kv heads", nh, nkv);
+  JB_REFUSE(n_splits < 1, "attention_bf16 decode: n_splits must be at least 1, got %d", n_splits);
+  const size_t o_floats = (size_t)n_seqs * nh * n_splits * HD;
+  const size_t ml_floats = (size_t)n_seqs * nh * n_splits * 2;
+  JB_REFUSE(o_floats + ml_floats > JB_NOALLOC_SCRATCH_FLOATS,
+            "attention_bf16 decode without allocation: %zu scratch floats are needed (n_seqs %d x heads %d x "
+            "splits %d x (head_dim %d + 2)), the built-in array holds %u",
+            o_floats + ml_floats, n_seqs, nh, n_splits, HD, (unsigned)JB_NOALLOC_SCRATCH_FLOATS);
+  int device = 0;
+  cudaError_t e = cudaGetDevice(&device);
+  if (e != cudaSuccess) return (int)e;
+  JB_REFUSE(device < 0 || device >= NOALLOC_MAX_DEVICES, "attention_bf16 decode without allocation: device %d", device);
+  if (noalloc_device_ptr[device] == nullptr) {
+    // set-up, once per device, with that device current
+    void* p = nullptr;
+    e = cudaGetSymbolAddress(&p, noalloc_scratch);
+    if (e != cudaSuccess) return (int)e;
+    e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
+    if (e != cudaSuccess) return (int)e;
+    noalloc_device_ptr[device] = static_cast<float*>(p);
+  }
+  float* part_o = noalloc_device_ptr[device];
+  float* part_ml = part_o + o_floats;
+  const int G = nh / nkv;
+  const int n_rb = (G + 15) / 16;
+  dim3 grid(n_seqs, nkv * n_rb, n_splits);
+  decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                                                        (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
+                                                        max_pages, window, scale * LOG2E, n_splits);
+  JB_CHECK_LAUNCH();
+  if (n_splits > 1) {
+    decode_combine_kernel<<<n_seqs * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_splits);
+    JB_CHECK_LAUNCH();
+  }
+  return 0;
+}
