@@ -192,6 +192,8 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
     bf16* __restrict__ out, const int* __restrict__ block_table, const int* __restrict__ q_start,
     const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window, float scale_log2) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [64][LD]
   bf16* kv_s = q_s + 64 * LD;                     // [2 stages][K, V][64][LD]
   const int G = nh / nkv;
@@ -279,6 +281,8 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
     const int* __restrict__ block_table, const int* __restrict__ kv_len, int nh, int nkv, int max_pages,
     int window, float scale_log2, int n_splits) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [16][LD]
   bf16* kv_s = q_s + 16 * LD;                     // [2][K, V][64][LD]; reused as float scratch at the end
   const int G = nh / nkv;
@@ -391,6 +395,8 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
 
 __global__ void decode_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                       bf16* __restrict__ out, int n_splits) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   const size_t item = blockIdx.x;  // seq * nh + head
   const float* ml = part_ml + item * n_splits * 2;
   float m = -CUDART_INF_F;
@@ -433,11 +439,10 @@ JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, cons
   }
   const int tpt = 64 / G;
   dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_seqs);
-  prefill_kernel<<<grid, THREADS, PREFILL_SMEM, stream>>>(
-      (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out, block_table, q_start, kv_len, nh,
-      nkv, max_pages, window, scale * LOG2E);
-  JB_CHECK_LAUNCH();
-  return 0;
+  jb::Launch cfg(grid, dim3(THREADS), PREFILL_SMEM, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, prefill_kernel, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                                 (bf16*)out, block_table, q_start, kv_len, nh, nkv, max_pages, window,
+                                 scale * LOG2E);
 }
 
 // Scratch (when n_splits > 1): part_o float32 [n_seqs * nh * n_splits * hd], part_ml float32
@@ -461,13 +466,16 @@ JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const
   const int G = nh / nkv;
   const int n_rb = (G + 15) / 16;
   dim3 grid(n_seqs, nkv * n_rb, n_splits);
-  decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                                                        (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
-                                                        max_pages, window, scale * LOG2E, n_splits);
-  JB_CHECK_LAUNCH();
+  jb::Launch cfg(grid, dim3(THREADS), DECODE_SMEM, stream);
+  cudaError_t le = cudaLaunchKernelEx(&cfg.c, decode_kernel, (const bf16*)q, (const bf16*)k_cache,
+                                      (const bf16*)v_cache, (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
+                                      max_pages, window, scale * LOG2E, n_splits);
+  if (le != cudaSuccess) return (int)le;
   if (n_splits > 1) {
-    decode_combine_kernel<<<n_seqs * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_splits);
-    JB_CHECK_LAUNCH();
+    jb::Launch cfg2(dim3(n_seqs * nh), dim3(HD >= 128 ? 128 : 64), 0, stream);
+    le = cudaLaunchKernelEx(&cfg2.c, decode_combine_kernel, (const float*)part_o, (const float*)part_ml, (bf16*)out,
+                            n_splits);
+    if (le != cudaSuccess) return (int)le;
   }
   return 0;
 }

@@ -7,6 +7,7 @@
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 #define JB_F32 0
 #define JB_BF16 1
@@ -35,6 +36,49 @@
   } while (0)
 
 namespace jb {
+
+// ---- programmatic dependent launch ------------------------------------------------
+// Every kernel of this library is launched so that it may start while the kernel
+// before it in the stream is still running (`Launch` below).  A kernel first lets
+// its own successor start (`pdl_launch_dependents`), does what does not depend on
+// earlier kernels (barrier set-up, TMEM allocation, loading weights), and calls
+// `pdl_wait` in EVERY thread before it touches anything an earlier kernel wrote.
+// Because each kernel waits before it finishes, completion is transitive along the
+// stream.  JANUS_PDL=0 in the environment turns the launch attribute off.
+__device__ __forceinline__ void pdl_launch_dependents() {
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+inline bool pdl_enabled() {
+  static int v = -1;
+  if (v < 0) {
+    const char* e = getenv("JANUS_PDL");
+    v = (e && e[0] == '0') ? 0 : 1;
+  }
+  return v != 0;
+}
+
+struct Launch {
+  cudaLaunchConfig_t c;
+  cudaLaunchAttribute attr[1];
+  Launch(dim3 grid, dim3 block, size_t smem, cudaStream_t stream) {
+    c = cudaLaunchConfig_t{};
+    c.gridDim = grid;
+    c.blockDim = block;
+    c.dynamicSmemBytes = smem;
+    c.stream = stream;
+    c.attrs = nullptr;
+    c.numAttrs = 0;
+    if (pdl_enabled()) {
+      attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      attr[0].val.programmaticStreamSerializationAllowed = 1;
+      c.attrs = attr;
+      c.numAttrs = 1;
+    }
+  }
+  Launch(const Launch&) = delete;
+};
 
 __device__ __forceinline__ float to_f32(float x) { return x; }
 __device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }

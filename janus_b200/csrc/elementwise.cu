@@ -1,29 +1,106 @@
-// Embedding gather, RMSNorm, residual add and SwiGLU gating.
+// Embedding gather, RMSNorm, residual add, SwiGLU gating and a zero fill.
 //
 // The residual stream is float32 in both engine dtypes; norms read it and
 // write the layer input in the engine dtype.  Statistics are float32.
 // Formulas: crates/janus-engine/src/compute/shaders/embed.wgsl:46-62,
 // activations.wgsl:20-35 (SiLU), activations.wgsl:81-133 (RMSNorm).
+//
+// Rows whose width is a multiple of 4 (8 for bf16 tables) move as 16-byte
+// vectors; any other width takes the scalar kernels.
 #include <stdio.h>
 
 #include "common.cuh"
 
 namespace {
 
+typedef __nv_bfloat16 bf16;
+
+// ---- 4-element vector access for float and bf16 ------------------------------
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const bf16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void store4(bf16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<uint32_t*>(&a);
+  raw.y = *reinterpret_cast<uint32_t*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// ---- embedding ------------------------------------------------------------------
 template <typename TT>
 __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
                                     float* __restrict__ out, int H) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   const int t = blockIdx.x;
   const TT* row = table + (size_t)ids[t] * H;
   float* o = out + (size_t)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = jb::to_f32(row[i]);
+  if ((H & 3) == 0) {
+    for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) store4(o + i, load4(row + i));
+  } else {
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = jb::to_f32(row[i]);
+  }
 }
 
-// One block per output row.  y = (x / sqrt(mean(x^2) + eps)) * gamma.
+// ---- RMSNorm: one block per output row; y = (x / sqrt(mean(x^2) + eps)) * gamma -----
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_CACHE = 8;  // float4 per thread kept in registers (rows up to 8192 wide are read once)
+
+template <typename TG, typename TO>
+__global__ void __launch_bounds__(NORM_THREADS) rmsnorm_vec_kernel(const float* __restrict__ x,
+                                                                  const int* __restrict__ row_index,
+                                                                  const TG* __restrict__ gamma, float eps,
+                                                                  TO* __restrict__ out, int H) {
+  __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const int r = blockIdx.x;
+  const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
+  const float* xr = x + src * H;
+  const int n4 = H >> 2;
+  float4 cache[NORM_CACHE];
+  float ss = 0.0f;
+#pragma unroll
+  for (int c = 0; c < NORM_CACHE; ++c) {
+    const int i = threadIdx.x + c * NORM_THREADS;
+    if (i < n4) {
+      cache[c] = load4(xr + 4 * i);
+      ss += cache[c].x * cache[c].x + cache[c].y * cache[c].y + cache[c].z * cache[c].z + cache[c].w * cache[c].w;
+    }
+  }
+  for (int i = threadIdx.x + NORM_CACHE * NORM_THREADS; i < n4; i += NORM_THREADS) {
+    const float4 v = load4(xr + 4 * i);
+    ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+  }
+  ss = jb::block_sum(ss, scratch);
+  const float rms = sqrtf(ss / (float)H + eps);
+  TO* o = out + (size_t)r * H;
+#pragma unroll
+  for (int c = 0; c < NORM_CACHE; ++c) {
+    const int i = threadIdx.x + c * NORM_THREADS;
+    if (i < n4) {
+      const float4 g = load4(gamma + 4 * i), v = cache[c];
+      store4(o + 4 * i, make_float4((v.x / rms) * g.x, (v.y / rms) * g.y, (v.z / rms) * g.z, (v.w / rms) * g.w));
+    }
+  }
+  for (int i = threadIdx.x + NORM_CACHE * NORM_THREADS; i < n4; i += NORM_THREADS) {
+    const float4 g = load4(gamma + 4 * i), v = load4(xr + 4 * i);
+    store4(o + 4 * i, make_float4((v.x / rms) * g.x, (v.y / rms) * g.y, (v.z / rms) * g.z, (v.w / rms) * g.w));
+  }
+}
+
 template <typename TG, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
                                const TG* __restrict__ gamma, float eps, TO* __restrict__ out, int H) {
   __shared__ float scratch[33];
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   const int r = blockIdx.x;
   const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
   const float* xr = x + src * H;
@@ -41,6 +118,8 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 
 template <typename TD>
 __global__ void residual_add_kernel(float* __restrict__ residual, const TD* __restrict__ delta, size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i < n) residual[i] += jb::to_f32(delta[i]);
 }
@@ -48,6 +127,8 @@ __global__ void residual_add_kernel(float* __restrict__ residual, const TD* __re
 // gate_up: [T, 2I] with gate in columns [0, I) and up in [I, 2I).
 template <typename TT>
 __global__ void swiglu_kernel(const TT* __restrict__ gate_up, TT* __restrict__ out, int I, size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const size_t t = i / I, c = i % I;
@@ -57,64 +138,84 @@ __global__ void swiglu_kernel(const TT* __restrict__ gate_up, TT* __restrict__ o
   out[i] = jb::from_f32<TT>(s * u);
 }
 
+__global__ void zero_f32_kernel(float4* __restrict__ p, size_t n4) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n4) p[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+}
+
 }  // namespace
 
 JB_EXPORT int jb_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H,
                               cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
+  jb::Launch cfg(dim3(T), dim3(threads), 0, stream);
+  cudaError_t e;
   if (table_dtype == JB_F32)
-    embed_gather_kernel<float><<<T, threads, 0, stream>>>((const float*)table, ids, out, H);
+    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<float>, (const float*)table, ids, out, H);
   else if (table_dtype == JB_BF16)
-    embed_gather_kernel<__nv_bfloat16><<<T, threads, 0, stream>>>((const __nv_bfloat16*)table, ids, out, H);
+    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<bf16>, (const bf16*)table, ids, out, H);
   else
     return JB_ERR_BAD_DTYPE;
-  JB_CHECK_LAUNCH();
-  return 0;
+  return (int)e;
 }
 
 JB_EXPORT int jb_rmsnorm(const float* x, const int* row_index, const void* gamma, int gamma_dtype, float eps,
                          void* out, int out_dtype, int rows, int H, cudaStream_t stream) {
   if (rows <= 0) return 0;
-  const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
-#define JB_LAUNCH_NORM(TG, TO) \
-  rmsnorm_kernel<TG, TO><<<rows, threads, 0, stream>>>(x, row_index, (const TG*)gamma, eps, (TO*)out, H)
+  const bool vec = (H & 3) == 0;
+  jb::Launch cfg(dim3(rows), dim3(vec ? NORM_THREADS : (H >= 512 ? 256 : 128)), 0, stream);
+  cudaError_t e;
+#define JB_LAUNCH_NORM(TG, TO)                                                                              \
+  e = vec ? cudaLaunchKernelEx(&cfg.c, rmsnorm_vec_kernel<TG, TO>, x, row_index, (const TG*)gamma, eps, (TO*)out, H) \
+          : cudaLaunchKernelEx(&cfg.c, rmsnorm_kernel<TG, TO>, x, row_index, (const TG*)gamma, eps, (TO*)out, H)
   if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_NORM(float, float);
-  else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_NORM(float, __nv_bfloat16);
-  else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_NORM(__nv_bfloat16, float);
-  else if (gamma_dtype == JB_BF16 && out_dtype == JB_BF16) JB_LAUNCH_NORM(__nv_bfloat16, __nv_bfloat16);
+  else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_NORM(float, bf16);
+  else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_NORM(bf16, float);
+  else if (gamma_dtype == JB_BF16 && out_dtype == JB_BF16) JB_LAUNCH_NORM(bf16, bf16);
   else return JB_ERR_BAD_DTYPE;
 #undef JB_LAUNCH_NORM
-  JB_CHECK_LAUNCH();
-  return 0;
+  return (int)e;
 }
 
 JB_EXPORT int jb_residual_add(float* residual, const void* delta, int delta_dtype, long long n,
                               cudaStream_t stream) {
   if (n <= 0) return 0;
   const int threads = 256;
-  const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+  jb::Launch cfg(dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream);
+  cudaError_t e;
   if (delta_dtype == JB_F32)
-    residual_add_kernel<float><<<blocks, threads, 0, stream>>>(residual, (const float*)delta, (size_t)n);
+    e = cudaLaunchKernelEx(&cfg.c, residual_add_kernel<float>, residual, (const float*)delta, (size_t)n);
   else if (delta_dtype == JB_BF16)
-    residual_add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>(residual, (const __nv_bfloat16*)delta, (size_t)n);
+    e = cudaLaunchKernelEx(&cfg.c, residual_add_kernel<bf16>, residual, (const bf16*)delta, (size_t)n);
   else
     return JB_ERR_BAD_DTYPE;
-  JB_CHECK_LAUNCH();
-  return 0;
+  return (int)e;
 }
 
 JB_EXPORT int jb_swiglu(const void* gate_up, void* out, int dtype, int T, int I, cudaStream_t stream) {
   const size_t n = (size_t)T * I;
   if (n == 0) return 0;
   const int threads = 256;
-  const unsigned blocks = (unsigned)((n + threads - 1) / threads);
+  jb::Launch cfg(dim3((unsigned)((n + threads - 1) / threads)), dim3(threads), 0, stream);
+  cudaError_t e;
   if (dtype == JB_F32)
-    swiglu_kernel<float><<<blocks, threads, 0, stream>>>((const float*)gate_up, (float*)out, I, n);
+    e = cudaLaunchKernelEx(&cfg.c, swiglu_kernel<float>, (const float*)gate_up, (float*)out, I, n);
   else if (dtype == JB_BF16)
-    swiglu_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, I, n);
+    e = cudaLaunchKernelEx(&cfg.c, swiglu_kernel<bf16>, (const bf16*)gate_up, (bf16*)out, I, n);
   else
     return JB_ERR_BAD_DTYPE;
-  JB_CHECK_LAUNCH();
-  return 0;
+  return (int)e;
+}
+
+// Fill n floats with zero (n a multiple of 4, p 16-byte aligned): the target of a
+// product whose slices of K meet by atomic adds.
+JB_EXPORT int jb_zero_f32(float* p, long long n, cudaStream_t stream) {
+  if (n <= 0) return 0;
+  JB_REFUSE((n & 3) != 0 || ((uintptr_t)p & 15) != 0, "zero_f32: %lld floats at %p are not whole 16-byte vectors", n, (void*)p);
+  const size_t n4 = (size_t)n >> 2;
+  jb::Launch cfg(dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, zero_f32_kernel, (float4*)p, n4);
 }

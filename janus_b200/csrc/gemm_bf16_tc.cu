@@ -4,7 +4,9 @@
 // output feature), the tokens the N side (16..256 per tile), so the same kernel
 // serves prefill (many tokens) and decode (a handful) without wasting the M side.
 //
-// One CTA computes one 128 x BN tile (optionally over a slice of K):
+// A tile is 128 weight rows x BN tokens (optionally over a slice of K).  The kernel
+// is persistent: CTA c computes tiles c, c + gridDim.x, ...; two accumulator
+// buffers in TMEM let the epilogue of one tile run under the MMAs of the next.
 //   warp 0     TMA producer: cp.async.bulk.tensor loads of 128B-swizzled tiles into a ring of stages
 //   warp 1     allocates TMEM, one lane issues tcgen05.mma (accumulators float32 in TMEM)
 //   warps 2-5  epilogue: tcgen05.ld the accumulators, then one of
@@ -14,6 +16,11 @@
 //                SWIGLU      Y[t, f] = bf16(silu(Dg) * Du) with Dg, Du from W rows f and N/2 + f
 // Every wait on an mbarrier is bounded in time; on a timeout the kernel records
 // an error code in `*status`, skips its remaining work, frees its TMEM and returns.
+// The kernel may start while its predecessor in the stream still runs (programmatic
+// dependent launch): before it waits for the predecessor it sets up its barriers and
+// TMEM, loads the weight tiles of its first stages (weights depend on no kernel) and
+// can ask for further weight tiles to be brought into L2 (JANUS_L2_PREFETCH=n; off by default:
+// it measured slower than leaving the ring to pull them).
 //
 // The reference computes the same product on scalar cores with f32
 // accumulation (crates/janus-engine/src/compute/shaders/gemm.wgsl:58-147).
@@ -21,6 +28,19 @@
 #include <stdio.h>
 
 #include "common.cuh"
+
+// 1: the ADD_F32 epilogue always adds with fire-and-forget reductions (red.global.add.f32), which
+// need no load round trip; 0: plain load/add/store when K is not split.
+#ifndef JB_ADD_WITH_RED
+#define JB_ADD_WITH_RED 1
+#endif
+// Shared memory given to the ring of stages (KiB); the ring is as deep as fits, at most JB_MAX_STAGES.
+#ifndef JB_RING_KB
+#define JB_RING_KB 208
+#endif
+#ifndef JB_MAX_STAGES
+#define JB_MAX_STAGES 8
+#endif
 
 namespace {
 
@@ -74,6 +94,12 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
   }
 }
 
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
+  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
+}
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
       "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -138,37 +164,58 @@ struct Cfg {
   static constexpr int A_BYTES = BM * BK * 2;
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
-  static constexpr int ACC_COLS = A_TILES * BN;
-  static constexpr int TMEM_COLS = ACC_COLS <= 32 ? 32 : ACC_COLS <= 64 ? 64 : ACC_COLS <= 128 ? 128 : ACC_COLS <= 256 ? 256 : 512;
+  static constexpr int ACC_COLS = A_TILES * BN;        // one accumulator buffer
+  static constexpr int WANT_COLS = 2 * ACC_COLS;       // two buffers
+  static constexpr int TMEM_COLS = WANT_COLS <= 32 ? 32 : WANT_COLS <= 64 ? 64 : WANT_COLS <= 128 ? 128 : WANT_COLS <= 256 ? 256 : 512;
+  static_assert(WANT_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
 };
+
+struct TileCoord {
+  int t0, m0, kt_begin, n_kt;
+};
+
+// Tiles are numbered with the token tile fastest, so that CTAs running side by
+// side share weight tiles and all of X through L2.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int n_w_tiles, int k_tiles,
+                                                int k_tiles_per_split, int BN_) {
+  TileCoord c;
+  c.t0 = (tile % n_tok_tiles) * BN_;
+  const int rest = tile / n_tok_tiles;
+  c.m0 = (rest % n_w_tiles) * BM;
+  c.kt_begin = (rest / n_w_tiles) * k_tiles_per_split;
+  c.n_kt = min(k_tiles, c.kt_begin + k_tiles_per_split) - c.kt_begin;
+  return c;
+}
 
 template <int BN, int MODE, int STAGES>
 __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                           int T, int N_out, int ldy, int k_tiles, int k_tiles_per_split,
-                                                          int up_row_offset, int atomic_add, int* __restrict__ status) {
+                                                          int n_tiles, int n_tok_tiles, int n_w_tiles,
+                                                          int up_row_offset, int atomic_add, int l2_prefetch_tiles,
+                                                          int* __restrict__ status) {
   using C = Cfg<BN, MODE>;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * C::STAGE_BYTES);
-  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 1);
+  uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES, accum_bar = full0 + 16 * STAGES;
+  const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
+  const uint32_t acc_full0 = full0 + 16 * STAGES, acc_empty0 = acc_full0 + 16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int t0 = blockIdx.x * BN, m0 = blockIdx.y * BM;
-  const int kt_begin = blockIdx.z * k_tiles_per_split;
-  const int kt_end = min(k_tiles, kt_begin + k_tiles_per_split);
-  const int n_kt = kt_end - kt_begin;
-  if (n_kt <= 0) return;  // uniform for the CTA
+  jb::pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full0 + 8 * s, 1);
       mbar_init(empty0 + 8 * s, 1);
     }
-    mbar_init(accum_bar, 1);
+    for (int b = 0; b < 2; ++b) {
+      mbar_init(acc_full0 + 8 * b, 1);
+      mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+    }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -183,84 +230,148 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   if (warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      for (int i = 0; i < n_kt; ++i) {
-        const int s = i % STAGES;
-        if (i >= STAGES && !mbar_wait(empty0 + 8 * s, ((i / STAGES) - 1) & 1, status, 1)) break;
-        const uint32_t stage = smem_base + s * C::STAGE_BYTES;
-        const uint32_t bar = full0 + 8 * s;
-        mbar_expect_tx(bar, C::STAGE_BYTES);
-        const int kx = (kt_begin + i) * BK;
-        tma_load_2d(stage, &map_w, bar, kx, m0);
-        if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, kx, up_row_offset + m0);
-        tma_load_2d(stage + C::A_TILES * C::A_BYTES, &map_x, bar, kx, t0);
+      int it = 0;  // k-tiles loaded so far, over all of this CTA's tiles
+      bool ok = true;
+      bool waited = false;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
+        int first = 0;
+        if (!waited) {
+          // Weights do not depend on the kernel before this one: fill the first
+          // stages with weight tiles and ask L2 for the next ones, then wait.
+          const int early = min(tc.n_kt, STAGES);
+          for (int i = 0; i < early; ++i) {
+            const uint32_t stage = smem_base + i * C::STAGE_BYTES, bar = full0 + 8 * i;
+            mbar_expect_tx(bar, C::STAGE_BYTES);
+            const int kx = (tc.kt_begin + i) * BK;
+            tma_load_2d(stage, &map_w, bar, kx, tc.m0);
+            if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, kx, up_row_offset + tc.m0);
+          }
+          const int ahead = min(tc.n_kt, early + l2_prefetch_tiles);
+          for (int i = early; i < ahead; ++i) {
+            const int kx = (tc.kt_begin + i) * BK;
+            tma_prefetch_2d(&map_w, kx, tc.m0);
+            if (MODE == SWIGLU) tma_prefetch_2d(&map_w, kx, up_row_offset + tc.m0);
+          }
+          jb::pdl_wait();
+          waited = true;
+          for (int i = 0; i < early; ++i)
+            tma_load_2d(smem_base + i * C::STAGE_BYTES + C::A_TILES * C::A_BYTES, &map_x, full0 + 8 * i,
+                        (tc.kt_begin + i) * BK, tc.t0);
+          first = early;
+          it = early;
+        }
+        for (int i = first; i < tc.n_kt; ++i, ++it) {
+          const int s = it % STAGES;
+          if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, status, 1)) { ok = false; break; }
+          const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full0 + 8 * s;
+          mbar_expect_tx(bar, C::STAGE_BYTES);
+          const int kx = (tc.kt_begin + i) * BK;
+          tma_load_2d(stage, &map_w, bar, kx, tc.m0);
+          if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, kx, up_row_offset + tc.m0);
+          tma_load_2d(stage + C::A_TILES * C::A_BYTES, &map_x, bar, kx, tc.t0);
+        }
       }
+      if (!waited) jb::pdl_wait();
+    } else {
+      jb::pdl_wait();
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
+    jb::pdl_wait();
     if (lane == 0) {
       constexpr uint32_t idesc = instr_desc(BN);
       bool ok = true;
-      for (int i = 0; i < n_kt && ok; ++i) {
-        const int s = i % STAGES;
-        ok = mbar_wait(full0 + 8 * s, (i / STAGES) & 1, status, 2);
+      int it = 0, j = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
+        const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
+        const int buf = j & 1;
+        // the epilogue must have drained this buffer (passes at once the first two times)
+        ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, status, 2);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t stage = smem_base + s * C::STAGE_BYTES;
-        const uint64_t a_desc = smem_desc_sw128(stage);
-        const uint64_t b_desc = smem_desc_sw128(stage + C::A_TILES * C::A_BYTES);
+        const uint32_t acc_addr = tmem_base + buf * C::ACC_COLS;
+        for (int i = 0; i < tc.n_kt; ++i, ++it) {
+          const int s = it % STAGES;
+          ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, status, 2);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t stage = smem_base + s * C::STAGE_BYTES;
+          const uint64_t a_desc = smem_desc_sw128(stage);
+          const uint64_t b_desc = smem_desc_sw128(stage + C::A_TILES * C::A_BYTES);
 #pragma unroll
-        for (int k = 0; k < BK / UMMA_K; ++k) {
-          const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
-          // advancing the start address by 32 bytes steps 16 elements along K inside the swizzled row
-          umma_bf16(tmem_base, a_desc + 2 * k, b_desc + 2 * k, idesc, acc);
-          if (MODE == SWIGLU) {
-            const uint64_t u_desc = smem_desc_sw128(stage + C::A_BYTES);
-            umma_bf16(tmem_base + BN, u_desc + 2 * k, b_desc + 2 * k, idesc, acc);
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint32_t acc = (i > 0 || k > 0) ? 1u : 0u;
+            // advancing the start address by 32 bytes steps 16 elements along K inside the swizzled row
+            umma_bf16(acc_addr, a_desc + 2 * k, b_desc + 2 * k, idesc, acc);
+            if (MODE == SWIGLU) {
+              const uint64_t u_desc = smem_desc_sw128(stage + C::A_BYTES);
+              umma_bf16(acc_addr + BN, u_desc + 2 * k, b_desc + 2 * k, idesc, acc);
+            }
           }
+          umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
         }
-        umma_commit(empty0 + 8 * s);  // frees the stage when these MMAs have read it
+        if (ok) umma_commit(acc_full0 + 8 * buf);  // this tile's accumulators are complete
       }
-      if (ok) umma_commit(accum_bar);  // accumulators complete
     }
   } else {
     // ---------------- epilogue ----------------
+    jb::pdl_wait();
     const int quarter = warp & 3;  // TMEM lanes this warp may read
-    if (mbar_wait(accum_bar, 0, status, 3)) {
+    int j = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
+      const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
+      const int buf = j & 1;
+      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, status, 3)) break;
       tc_fence_after();
-      const int f = m0 + quarter * 32 + lane;
+      const int f = tc.m0 + quarter * 32 + lane;
       const bool f_ok = f < N_out;
-      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
-        if (t0 + c0 >= T) break;  // uniform
+        if (tc.t0 + c0 >= T) break;  // uniform
         uint32_t r[16];
         tmem_ld16(lane_base + c0, r);
         uint32_t u[16];
         if (MODE == SWIGLU) tmem_ld16(lane_base + BN + c0, u);
         tmem_ld_wait();
         if (f_ok) {
+          if (MODE == ADD_F32 && !atomic_add && !JB_ADD_WITH_RED) {
+            // all loads first, then all stores: one round trip per 16 tokens, not 16
+            float* y = (float*)Y + (size_t)(tc.t0 + c0) * ldy + f;
+            float old[16];
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int t = t0 + c0 + j;
-            if (t < T) {
-              const float v = __uint_as_float(r[j]);
-              const size_t o = (size_t)t * ldy + f;
-              if (MODE == STORE_BF16) {
-                ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(v);
-              } else if (MODE == STORE_F32) {
-                ((float*)Y)[o] = v;
-              } else if (MODE == ADD_F32) {
-                if (atomic_add) atomicAdd(((float*)Y) + o, v);
-                else ((float*)Y)[o] += v;
-              } else {
-                const float up = __uint_as_float(u[j]);
-                const float act = v * (1.0f / (1.0f + expf(-v)));
-                ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(act * up);
+            for (int jj = 0; jj < 16; ++jj) old[jj] = (tc.t0 + c0 + jj < T) ? y[(size_t)jj * ldy] : 0.0f;
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj)
+              if (tc.t0 + c0 + jj < T) y[(size_t)jj * ldy] = old[jj] + __uint_as_float(r[jj]);
+          } else {
+#pragma unroll
+            for (int jj = 0; jj < 16; ++jj) {
+              const int t = tc.t0 + c0 + jj;
+              if (t < T) {
+                const float v = __uint_as_float(r[jj]);
+                const size_t o = (size_t)t * ldy + f;
+                if (MODE == STORE_BF16) {
+                  ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(v);
+                } else if (MODE == STORE_F32) {
+                  ((float*)Y)[o] = v;
+                } else if (MODE == ADD_F32) {
+                  atomicAdd(((float*)Y) + o, v);
+                } else {
+                  const float up = __uint_as_float(u[jj]);
+                  const float act = v * (1.0f / (1.0f + expf(-v)));
+                  ((__nv_bfloat16*)Y)[o] = __float2bfloat16_rn(act * up);
+                }
               }
             }
           }
         }
       }
+      // hand the buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
     }
     tc_fence_before();
   }
@@ -301,25 +412,50 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uin
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+int sm_count() {
+  static int n = 0;
+  if (n == 0) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0)
+      n = 148;
+  }
+  return n;
+}
+
 template <int BN, int MODE, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_out, int ldy, int k_tiles,
            int split_k, int up_row_offset, int* status, cudaStream_t stream) {
   using C = Cfg<BN, MODE>;
-  constexpr int smem = STAGES * C::STAGE_BYTES + (2 * STAGES + 1) * 8 + 16 + 1024;
-  static bool configured = false;
-  if (!configured) {
+  constexpr int smem = STAGES * C::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
+  static int ctas_per_sm = 0;
+  if (ctas_per_sm == 0) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, MODE, STAGES>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
-    configured = true;
+    int occ = 0;
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemm_tc_kernel<BN, MODE, STAGES>, THREADS, smem);
+    if (e != cudaSuccess) return (int)e;
+    // every resident CTA holds TMEM columns for the whole kernel: never more CTAs than the 512 columns serve
+    ctas_per_sm = max(1, min(occ, 512 / C::TMEM_COLS));
   }
   const int per = (k_tiles + split_k - 1) / split_k;
   const int splits = (k_tiles + per - 1) / per;
-  dim3 grid((T + BN - 1) / BN, (N_out + BM - 1) / BM, splits);
-  gemm_tc_kernel<BN, MODE, STAGES><<<grid, THREADS, smem, stream>>>(mw, mx, Y, T, N_out, ldy, k_tiles, per,
-                                                                  up_row_offset, splits > 1 ? 1 : 0, status);
-  JB_CHECK_LAUNCH();
-  return 0;
+  const int n_tok_tiles = (T + BN - 1) / BN, n_w_tiles = (N_out + BM - 1) / BM;
+  const long long n_tiles = (long long)n_tok_tiles * n_w_tiles * splits;
+  JB_REFUSE(n_tiles > 0x7fffffffLL, "gemm_bf16: too many tiles (%lld)", n_tiles);
+  const int grid = (int)min(n_tiles, (long long)sm_count() * ctas_per_sm);
+  // a weight-streaming product (few tokens) asks L2 for the weight tiles beyond its first stages
+  static int prefetch_depth = -1;  // JANUS_L2_PREFETCH overrides the default depth (0 turns it off)
+  if (prefetch_depth < 0) {
+    const char* e = getenv("JANUS_L2_PREFETCH");
+    prefetch_depth = e ? max(0, atoi(e)) : 0;
+  }
+  const int l2_prefetch_tiles = BN <= 64 ? prefetch_depth : 0;
+  jb::Launch cfg(dim3(grid), dim3(THREADS), smem, stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, gemm_tc_kernel<BN, MODE, STAGES>, mw, mx, Y, T, N_out, ldy, k_tiles, per,
+                                 (int)n_tiles, n_tok_tiles, n_w_tiles, up_row_offset, splits > 1 ? 1 : 0,
+                                 l2_prefetch_tiles, status);
 }
 
 template <int MODE>
@@ -327,20 +463,23 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
              int up_row_offset, int* status, cudaStream_t stream) {
   const int k_tiles = (K + BK - 1) / BK;
   CUtensorMap mx;
-#define JB_GO(BN_, ST_)                                                                              \
-  do {                                                                                               \
-    if (!make_map(&mx, X, (uint64_t)T, (uint64_t)K, BN_)) return JB_ERR_TENSORMAP;                   \
-    return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_row_offset, status, \
-                                  stream);                                                           \
-  } while (0)
+#define JB_GO(BN_, ST_)                                                                                 \
+  {                                                                                                     \
+    if (!make_map(&mx, X, (uint64_t)T, (uint64_t)K, BN_)) return JB_ERR_TENSORMAP;                      \
+    return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_row_offset, status,    \
+                                  stream);                                                              \
+  }
   // Decode-sized token counts: small stages so that two or more CTAs share an SM
   // and keep enough loads in flight; prefill: wide tiles, deep ring.
-  constexpr int SMALL_STAGES = MODE == SWIGLU ? 3 : 4;
-  if (T <= 16) JB_GO(16, SMALL_STAGES);
-  if (T <= 32) JB_GO(32, SMALL_STAGES);
-  if (T <= 64) JB_GO(64, SMALL_STAGES);
-  if (MODE == SWIGLU || T <= 128) JB_GO(128, 4);
-  JB_GO(256, 4);
+#define JB_ST(BN_) (JB_RING_KB * 1024 / Cfg<BN_, MODE>::STAGE_BYTES < JB_MAX_STAGES \
+                        ? JB_RING_KB * 1024 / Cfg<BN_, MODE>::STAGE_BYTES : JB_MAX_STAGES)
+  if (T <= 16) JB_GO(16, JB_ST(16))
+  else if (T <= 32) JB_GO(32, JB_ST(32))
+  else if (T <= 64) JB_GO(64, JB_ST(64))
+  else if constexpr (MODE == SWIGLU) JB_GO(128, JB_ST(128))   // two accumulators per buffer: 128 tokens fill TMEM
+  else if (T <= 128) JB_GO(128, JB_ST(128))
+  else JB_GO(256, JB_ST(256))
+#undef JB_ST
 #undef JB_GO
 }
 

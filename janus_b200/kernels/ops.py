@@ -113,6 +113,12 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
            "swiglu")
 
 
+def zero_f32(t: torch.Tensor) -> None:
+    """Fill a float32 tensor with zeros (whole 16-byte vectors)."""
+    _need(t, "zero target", torch.float32)
+    _check(library("elementwise").jb_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), _stream()), "zero_f32")
+
+
 # -- rotary positions + cache append --------------------------------------------
 def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[torch.Tensor],
                      positions: torch.Tensor, dest: Optional[torch.Tensor], k_cache: Optional[torch.Tensor],
@@ -284,10 +290,12 @@ def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 
 
 def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: int) -> int:
-    """Splits of the key range per (sequence, kv head) so that about two CTAs
-    per SM are in flight, at most one split per page."""
+    """Splits of the key range per (sequence, kv head): a CTA should walk about
+    eight pages, and at least 128 CTAs should be in flight; at most one split
+    per page."""
     pages = max(1, (max_kv_len + page_size - 1) // page_size)
-    return max(1, min(pages, SM_COUNT_TARGET // max(1, n_seqs * nkv_blocks)))
+    base = max(1, n_seqs * nkv_blocks)
+    return max(1, min(pages, max((pages + 7) // 8, (128 + base - 1) // base)))
 
 
 def attention_bf16_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
