@@ -26,6 +26,10 @@ class _EngineBackend:
     def __init__(self, engine: Engine, sampler: DeviceSampler):
         self.engine, self.sampler = engine, sampler
         self.device = engine.device
+        self._staging = None      # pinned buffers the sampled tokens are copied into
+        self._turn = 0
+        if not engine.options.use_graphs:
+            self.decode_launch = None   # no device-side token feedback without graphs: plain loop
 
     def alloc_slot(self) -> int:
         slot = self.engine.alloc_slot()
@@ -48,8 +52,28 @@ class _EngineBackend:
         return self._sample(logits, slots, requests, [0] * len(slots))
 
     def decode(self, slots, last_tokens, requests, steps) -> List[int]:
-        logits = self.engine.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, last_tokens)], borrow=True)
-        return self._sample(logits, slots, requests, steps)
+        ids = self.engine.decode_sample(slots, last_tokens, self.sampler, requests, steps)
+        return ids.cpu().tolist()
+
+    # A step is launched and its tokens are fetched later, so that the host can lay
+    # out the next step while the device runs this one.  A token -1 stands for the
+    # one the step before sampled for that slot (it is read on the device).
+    def decode_launch(self, slots, tokens, requests, steps):
+        ids = self.engine.decode_sample(slots, tokens, self.sampler, requests, steps)
+        if self._staging is None:
+            self._staging = [torch.zeros(self.engine.cache.n_slots, dtype=torch.int32, pin_memory=True)
+                             for _ in range(3)]
+        buf = self._staging[self._turn % 3][:len(slots)]
+        self._turn += 1
+        buf.copy_(ids, non_blocking=True)       # ordered after the step, before the next one overwrites `ids`
+        done = torch.cuda.Event()
+        done.record()
+        return buf, done
+
+    def decode_collect(self, handle) -> List[int]:
+        buf, done = handle
+        done.synchronize()
+        return buf.tolist()
 
 
 class Model:
@@ -60,6 +84,7 @@ class Model:
         self.engine = engine
         self.device = engine.device
         self.dtype = engine.dtype
+        self._samplers = {}
 
     # -- the step function, for callers that schedule themselves ---------------
     def alloc_slot(self) -> int:
@@ -85,7 +110,15 @@ class Model:
         sc = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p,
                            repetition_penalty=repetition_penalty, max_tokens=max_tokens)
         cache = self.engine.cache
-        sampler = DeviceSampler(sc, self.engine.model.vocab_size, cache.n_slots, seed, self.device)
+        # samplers are kept: one with a repetition penalty owns a count table, and a decode
+        # graph that was captured with it stays valid for the next call
+        skey = (sc.temperature, sc.top_k, sc.top_p, sc.repetition_penalty, seed)
+        sampler = self._samplers.get(skey)
+        if sampler is None:
+            if len(self._samplers) >= 8:
+                self._samplers.clear()
+            sampler = DeviceSampler(sc, self.engine.model.vocab_size, cache.n_slots, seed, self.device)
+            self._samplers[skey] = sampler
         stop = [] if ignore_eos else list(getattr(self.config, "eos_token_id", ()) or ())
         stop += list(stop_token_ids or ())
         outputs, reasons, stats = run_generation(

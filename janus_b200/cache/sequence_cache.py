@@ -120,6 +120,7 @@ class SequenceCache:
         self._free_slots: List[int] = list(range(self.n_slots - 1, -1, -1))
         self._live = [False] * self.n_slots
         self.lengths = [0] * self.n_slots
+        self.epochs = [0] * self.n_slots      # bumped each time a slot is taken: tells occupants apart
 
     # -- slots ---------------------------------------------------------------
     @property
@@ -132,6 +133,7 @@ class SequenceCache:
         slot = self._free_slots.pop()
         self._live[slot] = True
         self.lengths[slot] = 0
+        self.epochs[slot] += 1
         for st in self.states.values():
             st[slot].zero_()
         return slot

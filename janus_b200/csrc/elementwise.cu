@@ -35,11 +35,14 @@ __device__ __forceinline__ void store4(bf16* p, float4 v) {
 // ---- embedding ------------------------------------------------------------------
 template <typename TT>
 __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int H) {
+                                    float* __restrict__ out, int H, const int* __restrict__ feedback,
+                                    const int* __restrict__ token_slot) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   const int t = blockIdx.x;
-  const TT* row = table + (size_t)ids[t] * H;
+  int id = ids[t];
+  if (id < 0) id = feedback[token_slot[t]];  // the token sampled for this slot by the step before
+  const TT* row = table + (size_t)id * H;
   float* o = out + (size_t)t * H;
   if ((H & 3) == 0) {
     for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) store4(o + i, load4(row + i));
@@ -147,16 +150,17 @@ __global__ void zero_f32_kernel(float4* __restrict__ p, size_t n4) {
 
 }  // namespace
 
+// ids[t] < 0 means: take feedback[token_slot[t]] (both may be null if no id is negative).
 JB_EXPORT int jb_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H,
-                              cudaStream_t stream) {
+                              const int* feedback, const int* token_slot, cudaStream_t stream) {
   if (T <= 0) return 0;
   const int threads = H >= 1024 ? 256 : 128;
   jb::Launch cfg(dim3(T), dim3(threads), 0, stream);
   cudaError_t e;
   if (table_dtype == JB_F32)
-    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<float>, (const float*)table, ids, out, H);
+    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<float>, (const float*)table, ids, out, H, feedback, token_slot);
   else if (table_dtype == JB_BF16)
-    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<bf16>, (const bf16*)table, ids, out, H);
+    e = cudaLaunchKernelEx(&cfg.c, embed_gather_kernel<bf16>, (const bf16*)table, ids, out, H, feedback, token_slot);
   else
     return JB_ERR_BAD_DTYPE;
   return (int)e;

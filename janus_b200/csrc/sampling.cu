@@ -80,7 +80,8 @@ __device__ void block_argmax(float v, int i, float* smem_val, int* smem_idx) {
 __global__ void __launch_bounds__(THREADS) sample_kernel(
     const float* __restrict__ logits, int V, int* __restrict__ out_ids, float temperature, int top_k,
     float top_p, float penalty, int* __restrict__ counts, const int* __restrict__ count_rows,
-    unsigned long long seed, const int* __restrict__ seq_ids, const int* __restrict__ steps) {
+    unsigned long long seed, const int* __restrict__ seq_ids, const int* __restrict__ steps,
+    int* __restrict__ feedback) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
   __shared__ float s_red[33];
@@ -226,6 +227,7 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   if (tid == 0) {
     out_ids[row] = token;
     if (my_counts) my_counts[token] += 1;
+    if (feedback) feedback[count_rows[row]] = token;  // the next step may read its input token from here
   }
 }
 
@@ -233,16 +235,19 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
 
 // counts: [rows, V] int32 occurrences of generated tokens per sequence (may be
 // null when penalty == 1); count_rows[b] selects the row of `counts` for batch
-// row b.  The kernel adds the sampled token to its row of `counts`.
+// row b.  The kernel adds the sampled token to its row of `counts`.  feedback (may be null):
+// int32 per cache slot; the token of batch row b is also stored at feedback[count_rows[b]].
 JB_EXPORT int jb_sample(const float* logits, int B, int V, int* out_ids, float temperature, int top_k,
                         float top_p, float penalty, int* counts, const int* count_rows,
-                        unsigned long long seed, const int* seq_ids, const int* steps, cudaStream_t stream) {
+                        unsigned long long seed, const int* seq_ids, const int* steps, int* feedback,
+                        cudaStream_t stream) {
   if (B <= 0) return 0;
   JB_REFUSE(V <= 0, "sample: vocabulary size %d", V);
   JB_REFUSE(temperature < 0.0f, "sample: negative temperature %f", temperature);
   JB_REFUSE(penalty <= 0.0f, "sample: repetition penalty %f must be positive", penalty);
+  JB_REFUSE(feedback != nullptr && count_rows == nullptr, "sample: feedback needs the rows' slots");
   sample_kernel<<<B, THREADS, 0, stream>>>(logits, V, out_ids, temperature, top_k, top_p, penalty, counts,
-                                           count_rows, seed, seq_ids, steps);
+                                           count_rows, seed, seq_ids, steps, feedback);
   JB_CHECK_LAUNCH();
   return 0;
 }

@@ -139,18 +139,66 @@ def run_generation(backend: GenerationBackend, prompts: Sequence[Sequence[int]],
             else:
                 backend.free_slot(slots.pop(r))
         t0 = time.perf_counter()
-        while live:
-            toks = backend.decode([slots[r] for r in live], [outputs[r][-1] for r in live], live,
-                                  [len(outputs[r]) for r in live])
-            stats.decode_steps += 1
-            stats.decode_tokens += len(live)
-            still: List[int] = []
-            for r, tok in zip(live, toks):
-                if accept(r, int(tok)):
-                    still.append(r)
-                else:
-                    backend.free_slot(slots.pop(r))
-            live = still
+        if getattr(backend, "decode_launch", None) is not None:
+            _decode_run_ahead(backend, live, slots, outputs, prompt_lens, max_new_tokens, max_seq_len, accept, stats)
+        else:
+            while live:
+                toks = backend.decode([slots[r] for r in live], [outputs[r][-1] for r in live], live,
+                                      [len(outputs[r]) for r in live])
+                stats.decode_steps += 1
+                stats.decode_tokens += len(live)
+                still: List[int] = []
+                for r, tok in zip(live, toks):
+                    if accept(r, int(tok)):
+                        still.append(r)
+                    else:
+                        backend.free_slot(slots.pop(r))
+                live = still
         backend.synchronize()
         stats.decode_ms += (time.perf_counter() - t0) * 1e3
     return outputs, reasons, stats
+
+
+FROM_DEVICE = -1   # as a token handed to `decode_launch`: the token the step before produced for that slot
+
+
+def _decode_run_ahead(backend, live: List[int], slots: dict, outputs: List[List[int]], prompt_lens: Sequence[int],
+                      max_new_tokens: int, max_seq_len: int, accept: Callable[[int, int], bool],
+                      stats: GenerationStats) -> None:
+    """The decode loop for a backend that can launch a step before the host has
+    read the one before (`decode_launch` / `decode_collect`): while the device
+    runs step k, step k+1 is laid out and launched for every sequence that
+    cannot end by length at step k; its input tokens stay on the device.  A
+    sequence that turns out to have met a stop token at step k has one row of
+    step k+1 computed in vain; that row is ignored.  The tokens and finish
+    reasons are those of the plain loop."""
+    def ends_by_length(r: int, produced: int) -> bool:
+        # mirrors `accept`: after `produced` tokens the request is over whatever the token is
+        return produced >= max_new_tokens or prompt_lens[r] + produced > max_seq_len
+
+    rows = list(live)
+    if not rows:
+        return
+    handle = backend.decode_launch([slots[r] for r in rows], [outputs[r][-1] for r in rows], rows,
+                                   [len(outputs[r]) for r in rows])
+    dead: set = set()
+    while rows:
+        # the step after this one: everybody whose next token cannot be the last by length
+        ahead = [r for r in rows if r not in dead and not ends_by_length(r, len(outputs[r]) + 1)]
+        ahead_handle = None
+        if ahead:
+            ahead_handle = backend.decode_launch([slots[r] for r in ahead], [FROM_DEVICE] * len(ahead), ahead,
+                                                 [len(outputs[r]) + 1 for r in ahead])
+        toks = backend.decode_collect(handle)
+        stats.decode_steps += 1
+        for r, tok in zip(rows, toks):
+            if r in dead:
+                continue
+            stats.decode_tokens += 1
+            if not accept(r, int(tok)):
+                dead.add(r)
+                backend.free_slot(slots.pop(r))
+        rows, handle = ahead, ahead_handle
+        if rows and all(r in dead for r in rows):
+            backend.decode_collect(handle)      # nothing of it is wanted; wait for it all the same
+            return

@@ -76,7 +76,8 @@ class DecoderModel:
         the logits of the rows `want_rows` (indices into the step's tokens)."""
         T = ctx.n_tokens
         residual = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
-        ops.embed_gather(self.embedding, ctx.token_ids, residual)
+        ops.embed_gather(self.embedding, ctx.token_ids, residual, ctx.feedback,
+                         ctx.seq_slot if ctx.feedback is not None else None)
         for place, entry in enumerate(self.schedule):
             view = ctx.cache_view(place if entry.reads_cache_of is None else entry.reads_cache_of)
             self.layers[entry.layer].forward(residual, ctx, view, writes_cache=entry.reads_cache_of is None)

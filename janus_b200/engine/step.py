@@ -22,6 +22,9 @@ from .model import DecoderModel
 from .workspace import Workspace
 
 
+FROM_DEVICE = -1   # as a decode step's token: "the token the step before sampled for this slot"
+
+
 class StepError(ValueError):
     """A step that cannot run: a dead slot, a token outside the vocabulary, a
     sequence past its longest length.  Raised before anything is launched."""
@@ -57,6 +60,7 @@ class StepContext:
         self.q_start: torch.Tensor = None     # [n_seqs + 1] offsets of each sequence's tokens
         self.kv_len: torch.Tensor = None      # [n_seqs] length of each sequence after this step
         self.seq_slot: torch.Tensor = None    # [n_seqs] cache slot of each sequence
+        self.feedback: torch.Tensor = None    # decode only: per slot the token sampled last (for ids < 0)
         self.groups: List[GroupStepView] = []
         self.workspace: Workspace = None
         self.cache: SequenceCache = None
@@ -94,6 +98,9 @@ class Engine:
         self._graphs: Dict[Tuple, object] = {}
         self.last_graph_launches = 0       # kernels of this library in the last step
         self.last_step_h2d_bytes = 0       # bytes of the last step's index buffer
+        # per slot: the token sampled last by a graph step, so that the next step can
+        # read its input on the device before the host has seen it
+        self.feedback = torch.zeros(n_slots, dtype=torch.int32, device=self.device)
 
     # -- slots -----------------------------------------------------------------
     def alloc_slot(self) -> int:
@@ -103,7 +110,7 @@ class Engine:
         self.cache.free_slot(slot)
 
     # -- the step --------------------------------------------------------------
-    def _validate(self, entries: Sequence[StepEntry]) -> None:
+    def _validate(self, entries: Sequence[StepEntry], device_tokens: bool = False) -> None:
         if not entries:
             raise StepError("a step needs at least one sequence")
         seen = set()
@@ -117,7 +124,7 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"slot {e.slot} brings no tokens")
-            bad = [t for t in e.tokens if not 0 <= int(t) < V]
+            bad = [t for t in e.tokens if not (0 <= int(t) < V or (device_tokens and int(t) == FROM_DEVICE))]
             if bad:
                 raise StepError(f"token id {bad[0]} is outside the vocabulary of {V}")
             if self.cache.lengths[e.slot] + n > self.max_seq_len:
@@ -228,13 +235,13 @@ class Engine:
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         self._reserve(entries)
-        if getattr(self, "_copy_done", None) is not None:
-            self._copy_done.synchronize()
         if (self.options.use_graphs and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
-            logits = self._graph_decode(entries)
+            logits = self._graph_decode(entries, None)[0]
             if not borrow:
                 logits = logits.clone()
         else:
+            if getattr(self, "_copy_done", None) is not None:
+                self._copy_done.synchronize()
             ctx, want_rows, _ = self.build_context(entries)
             logits = torch.empty((want_rows.shape[0], self.model.vocab_size), dtype=torch.float32,
                                  device=self.device)
@@ -245,43 +252,162 @@ class Engine:
             self.cache.advance(e.slot, len(e.tokens))
         return logits
 
+    def decode_sample(self, slots: Sequence[int], tokens: Sequence[int], sampler, requests: Sequence[int],
+                      steps: Sequence[int]) -> torch.Tensor:
+        """One token per sequence in, the sampled next token of each out (int32
+        on the device, a buffer that the next call overwrites).  Forward pass and
+        sampling replay from one CUDA graph; `requests` and `steps` key the
+        sampler's random numbers.  A token FROM_DEVICE stands for the token that
+        the call before sampled for that slot, so that a step can be launched
+        before the host has read the last one's result."""
+        entries = [StepEntry(s, (int(t),), (0,)) for s, t in zip(slots, tokens)]
+        self._validate(entries, device_tokens=self.options.use_graphs)
+        self._reserve(entries)
+        if self.options.use_graphs:
+            out = self._graph_decode(entries, (sampler, requests, steps))[1]
+        else:
+            if getattr(self, "_copy_done", None) is not None:
+                self._copy_done.synchronize()
+            ctx, want_rows, _ = self.build_context(entries)
+            logits = torch.empty((len(entries), self.model.vocab_size), dtype=torch.float32, device=self.device)
+            self.model.forward(ctx, want_rows, logits)
+            meta = torch.tensor([list(requests), list(steps), list(slots)], dtype=torch.int32).to(self.device)
+            out = sampler.sample(logits, meta[0], meta[1], meta[2])
+        for e in entries:
+            self.cache.advance(e.slot, 1)
+        return out
+
     # -- decode steps replayed from CUDA graphs -----------------------------------
-    def _graph_decode(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+    def _graph_decode(self, entries: Sequence[StepEntry], sampling):
         """One token per sequence, every sequence's logits wanted: the kernels of
-        the step are captured once per (batch size, page capacity) and replayed;
-        each replay only refreshes the step's index buffer.  The capacity is the
-        pages of the longest sequence, rounded up to a power of two, so that a
-        graph serves many steps before a sequence outgrows it."""
+        the step (and of sampling, if asked for) are captured once per (batch
+        size, page capacity, sampler) and replayed; a replay only refreshes the
+        step's index buffer.  The capacity is the pages of the longest sequence,
+        rounded up to a power of two, so that a graph serves many steps before a
+        sequence outgrows it.  Returns (logits, sampled tokens or None)."""
         B = len(entries)
         need = max((self.cache.lengths[e.slot] + 1 + PAGE_SIZE - 1) // PAGE_SIZE for e in entries)
         cap = 1
         while cap < need:
             cap *= 2
-        key = (B, cap, self.workspace.generation)
+        sampler = sampling[0] if sampling is not None else None
+        # a graph bakes in the sampler's options, seed and count table: samplers equal in those share it
+        key = (B, cap, self.workspace.generation, sampler.graph_key() if sampler is not None else 0)
         rec = self._graphs.get(key)
         if rec is None:
             for k in [k for k in self._graphs if k[2] != self.workspace.generation]:
                 del self._graphs[k]          # buffers moved: those graphs hold stale addresses
-            _, _, total = self.build_context(entries, pages_capacity=cap)
-            meta = torch.zeros(total, dtype=torch.int32, device=self.device)
-            logits = torch.empty((B, self.model.vocab_size), dtype=torch.float32, device=self.device)
-            # an eager run first: it sizes the workspace and configures the kernels
-            self._copy_done.synchronize()
-            ctx, want_rows, _ = self.build_context(entries, pages_capacity=cap, into=meta)
-            self.model.forward(ctx, want_rows, logits)
+            rec = _DecodeGraph(self, B, cap, sampler)
+            rec.fill(entries, sampling)
+            rec.run_forward(sample=False)    # eager: sizes the workspace, configures the kernels
             torch.cuda.synchronize(self.device)
-            if self.workspace.generation != key[2]:
-                key = (B, cap, self.workspace.generation)
+            key = (B, cap, self.workspace.generation, key[3])
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             with torch.cuda.graph(graph):
-                self.model.forward(ctx, want_rows, logits)
-            rec = (graph, meta, logits, ops.launch_count() - before)
+                rec.run_forward()
+            rec.graph, rec.launches = graph, ops.launch_count() - before
             self._graphs[key] = rec
-            # the eager run and the capture wrote this step's keys already; replaying
-            # the graph below writes the same values again
-        graph, meta, logits, self.last_graph_launches = rec
-        self._copy_done.synchronize()
-        self.build_context(entries, pages_capacity=cap, into=meta)
-        graph.replay()
-        return logits
+            # the eager run and the capture wrote this step's keys already; the
+            # replay below writes the same values again
+        else:
+            rec.fill(entries, sampling)
+        self.last_graph_launches = rec.launches
+        self.last_step_h2d_bytes = 4 * rec.total
+        rec.graph.replay()
+        return rec.logits, rec.tokens_out
+
+
+class _DecodeGraph:
+    """The fixed buffers of one captured decode step and the fast refill of its
+    index buffer: two pinned host copies alternate so that a refill never
+    overwrites a copy still in flight."""
+
+    def __init__(self, engine: "Engine", B: int, cap: int, sampler):
+        self.engine, self.B, self.cap, self.sampler = engine, B, cap, sampler
+        cache = engine.cache
+        G = len(cache.groups)
+        sizes = [B, B, B, B + 1, B, B, B] + [B, B * cap] * G + [B, B, B]
+        self.offsets = [0]
+        for n in sizes:
+            self.offsets.append(self.offsets[-1] + _pad4(n))
+        self.total = self.offsets[-1]
+        self.extra = 7 + 2 * G                      # first of the three sampling segments
+        dev = engine.device
+        self.meta = torch.zeros(self.total, dtype=torch.int32, device=dev)
+        self.logits = torch.empty((B, engine.model.vocab_size), dtype=torch.float32, device=dev)
+        self.tokens_out = torch.zeros(B, dtype=torch.int32, device=dev) if sampler is not None else None
+        self.host = [torch.zeros(self.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.host_np = [h.numpy() for h in self.host]
+        o = self.offsets
+        for h in self.host_np:                      # the parts that never change
+            h[o[2]:o[2] + B] = np.arange(B)
+            h[o[3]:o[3] + B + 1] = np.arange(B + 1)
+            h[o[6]:o[6] + B] = np.arange(B)
+            for gi in range(G):
+                h[o[8 + 2 * gi]:o[8 + 2 * gi] + B * cap] = -1
+        self.row_sig = [[[None] * B for _ in range(G)] for _ in range(2)]
+        self.events = [None, None]
+        self.flip = 0
+        self.graph, self.launches = None, 0
+
+        def seg(i: int, n: int) -> torch.Tensor:
+            return self.meta[o[i]:o[i] + n]
+
+        ctx = StepContext()
+        ctx.n_tokens, ctx.n_seqs, ctx.is_decode, ctx.max_q_len = B, B, True, 1
+        ctx.max_kv_len_bound = cap * PAGE_SIZE
+        ctx.token_ids, ctx.positions, ctx.token_seq = seg(0, B), seg(1, B), seg(2, B)
+        ctx.q_start, ctx.kv_len, ctx.seq_slot = seg(3, B + 1), seg(4, B), seg(5, B)
+        ctx.groups = [GroupStepView(seg(7 + 2 * gi, B), seg(8 + 2 * gi, B * cap).view(B, cap), PAGE_SIZE)
+                      for gi in range(G)]
+        ctx.workspace, ctx.cache, ctx.dtype = engine.workspace, cache, engine.dtype
+        ctx.feedback = engine.feedback
+        self.ctx, self.want_rows = ctx, seg(6, B)
+        self.sample_meta = (seg(self.extra, B), seg(self.extra + 1, B), seg(self.extra + 2, B))
+
+    def run_forward(self, sample: bool = True) -> None:
+        self.engine.model.forward(self.ctx, self.want_rows, self.logits)
+        if sample and self.sampler is not None:   # sampling may count tokens: it runs in the replay only
+            requests, steps, count_rows = self.sample_meta
+            self.sampler.sample_into(self.logits, self.tokens_out, requests, steps, count_rows,
+                                     self.engine.feedback)
+
+    def fill(self, entries: Sequence[StepEntry], sampling) -> None:
+        B, cap, o = self.B, self.cap, self.offsets
+        cache = self.engine.cache
+        k = self.flip
+        self.flip ^= 1
+        if self.events[k] is not None:
+            self.events[k].synchronize()
+        h = self.host_np[k]
+        slots = [e.slot for e in entries]
+        lens = [cache.lengths[s] for s in slots]
+        h[o[0]:o[0] + B] = [e.tokens[0] for e in entries]
+        h[o[1]:o[1] + B] = lens
+        h[o[4]:o[4] + B] = [n + 1 for n in lens]
+        h[o[5]:o[5] + B] = slots
+        for gi, g in enumerate(cache.groups):
+            pages = g.pages
+            h[o[7 + 2 * gi]:o[7 + 2 * gi] + B] = [pages[s][n // PAGE_SIZE] * PAGE_SIZE + n % PAGE_SIZE
+                                                  for s, n in zip(slots, lens)]
+            table = h[o[8 + 2 * gi]:o[8 + 2 * gi] + B * cap].reshape(B, cap)
+            sigs = self.row_sig[k][gi]
+            windowed = g.spec.window > 0
+            for i, s in enumerate(slots):
+                row = pages[s]
+                sig = (s, cache.epochs[s], len(row))
+                if windowed or sigs[i] != sig:       # a window group's rows lose pages as they pass
+                    table[i, :len(row)] = row
+                    table[i, len(row):] = -1
+                    sigs[i] = sig
+        if sampling is not None:
+            _, requests, steps = sampling
+            e0 = self.extra
+            h[o[e0]:o[e0] + B] = requests
+            h[o[e0 + 1]:o[e0 + 1] + B] = steps
+            h[o[e0 + 2]:o[e0 + 2] + B] = slots
+        self.meta.copy_(self.host[k], non_blocking=True)
+        ev = torch.cuda.Event()
+        ev.record()
+        self.events[k] = ev

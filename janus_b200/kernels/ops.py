@@ -65,8 +65,9 @@ def _check(code: int, what: str, kernels: int = 1) -> None:
 
 
 # -- embedding, norm, elementwise ---------------------------------------------
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t, :] = float32(table[ids[t], :])"""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
+                 feedback: Optional[torch.Tensor] = None, token_slot: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = float32(table[ids[t], :]); a negative id stands for feedback[token_slot[t]]"""
     T, H = out.shape
     _need(table, "embed table")
     _need(ids, "token ids", torch.int32, (T,))
@@ -74,7 +75,8 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor) -> N
     if table.shape[1] != H:
         raise KernelError(f"embed: table width {table.shape[1]} != output width {H}")
     _check(library("elementwise").jb_embed_gather(
-        _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), T, H, _stream()), "embed_gather")
+        _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), T, H, _ptr(feedback), _ptr(token_slot),
+        _stream()), "embed_gather")
 
 
 def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, out: torch.Tensor,
@@ -245,21 +247,25 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "st
 # -- sampling -----------------------------------------------------------------------
 def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_k: int, top_p: float,
            repetition_penalty: float, counts: Optional[torch.Tensor], count_rows: Optional[torch.Tensor],
-           seed: int, seq_ids: torch.Tensor, steps: torch.Tensor) -> None:
+           seed: int, seq_ids: torch.Tensor, steps: torch.Tensor, feedback: Optional[torch.Tensor] = None) -> None:
     B, V = logits.shape
     _need(logits, "logits", torch.float32)
     _need(out_ids, "sampled ids", torch.int32, (B,))
     _need(seq_ids, "sequence ids", torch.int32, (B,))
     _need(steps, "step counters", torch.int32, (B,))
+    if count_rows is not None:
+        _need(count_rows, "rows' slots", torch.int32, (B,))
+    if feedback is not None:
+        _need(feedback, "token feedback", torch.int32)
     if counts is not None:
         _need(counts, "token counts", torch.int32)
-        _need(count_rows, "count rows", torch.int32, (B,))
         if counts.shape[1] != V:
             raise KernelError("sample: counts width differs from the vocabulary")
     _check(library("sampling").jb_sample(
         _ptr(logits), B, V, _ptr(out_ids), ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p),
         ctypes.c_float(repetition_penalty), _ptr(counts), _ptr(count_rows),
-        ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(seq_ids), _ptr(steps), _stream()), "sample")
+        ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(seq_ids), _ptr(steps), _ptr(feedback), _stream()),
+        "sample")
 
 
 # -- bfloat16 attention (one library per head size) -----------------------------------

@@ -106,6 +106,54 @@ def test_callback_can_end_a_request():
     assert (0, 3) not in seen
 
 
+class RunAheadBackend(ScriptedBackend):
+    """A backend that can launch a step before the one before was read; a token
+    -1 stands for what the step before produced for that slot."""
+
+    def __init__(self, script, n_slots):
+        super().__init__(script, n_slots)
+        self.last = {}          # slot -> token produced last ("on the device")
+        self.in_flight = 0
+        self.max_in_flight = 0
+        self.wasted_rows = 0
+
+    def prefill(self, slots, prompts, requests):
+        out = super().prefill(slots, prompts, requests)
+        self.last.update(dict(zip(slots, out)))
+        return out
+
+    def decode_launch(self, slots, tokens, requests, steps):
+        fed = [self.last[s] if t == -1 else t for s, t in zip(slots, tokens)]
+        for s in slots:
+            assert s in self.held, "a step was launched for a slot that was given back"
+        out = self.decode(slots, fed, requests, steps)
+        self.last.update(dict(zip(slots, out)))
+        self.in_flight += 1
+        self.max_in_flight = max(self.max_in_flight, self.in_flight)
+        return out
+
+    def decode_collect(self, handle):
+        self.in_flight -= 1
+        return handle
+
+
+@pytest.mark.parametrize("case", range(4))
+def test_run_ahead_loop_gives_the_plain_loop_s_results(case):
+    import random
+    rng = random.Random(case)
+    n = 6
+    script = {r: [rng.choice([1, 2, 3, 4, 99]) for _ in range(12)] for r in range(n)}
+    prompts = [[7] * rng.randint(1, 9) for _ in range(n)]
+    kw = dict(stop=[99], batch=3, max_seq=15, slots=4)
+    _, plain = run(script, prompts, 8, **kw)
+    b = RunAheadBackend(script, 4)
+    ahead = run_generation(b, prompts, 8, [99], 3, 10_000, 15, 4, 64, None)
+    assert not b.held and ahead[0] == plain[0] and ahead[1] == plain[1]
+    assert ahead[2].decode_tokens == plain[2].decode_tokens and ahead[2].decode_steps == plain[2].decode_steps
+    assert b.max_in_flight == 2                      # a step is launched while the one before is unread
+    assert b.in_flight == 0
+
+
 def test_sampler_config_names_and_checks():
     c = SamplerConfig()
     assert (c.temperature, c.top_k, c.top_p, c.beam_width, c.max_tokens) == (0.0, 0, 1.0, 1, 128)
