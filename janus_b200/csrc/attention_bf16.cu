@@ -39,6 +39,11 @@ constexpr int CHUNKS = HD / 8;        // 16-byte chunks per row that exist in gl
 constexpr int THREADS = 128;
 constexpr int KV_TILE = PAGE * LD;    // elements
 constexpr float LOG2E = 1.4426950408889634f;
+#ifndef JB_DECODE_STAGES
+#define JB_DECODE_STAGES 3
+#endif
+constexpr int DECODE_STAGES = JB_DECODE_STAGES;  // K/V pages in the decode kernel's ring
+constexpr int RED_LD = HD + 8;                   // row stride (floats) of the warps' exchange of partial outputs
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -284,7 +289,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [16][LD]
-  bf16* kv_s = q_s + 16 * LD;                     // [2][K, V][64][LD]; reused as float scratch at the end
+  bf16* kv_s = q_s + 16 * LD;                     // [DECODE_STAGES][K, V][64][LD]; reused as float scratch at the end
   const int G = nh / nkv;
   const int n_rb = (G + 15) / 16;
   const int seq = blockIdx.x, kvh = blockIdx.y / n_rb, rb = blockIdx.y % n_rb, split = blockIdx.z;
@@ -303,7 +308,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   RowState st;
   st.init();
   if (kb_start <= kb_end) {
-    zero_pad_columns(q_s, 16 + 4 * PAGE);
+    zero_pad_columns(q_s, 16 + 2 * DECODE_STAGES * PAGE);
     for (int ch = threadIdx.x; ch < 16 * CHUNKS; ch += THREADS) {
       const int r = ch / CHUNKS, col = ch % CHUNKS;
       const bool valid = r < n_rows;
@@ -316,8 +321,12 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
       load_page(kv_s + (size_t)stage * 2 * KV_TILE, k_cache + off);
       load_page(kv_s + (size_t)stage * 2 * KV_TILE + KV_TILE, v_cache + off);
     };
-    issue(kb_start, 0);
-    cp_async_commit();
+    // ring of DECODE_STAGES pages: DECODE_STAGES - 1 loads are in flight while one page is computed
+#pragma unroll
+    for (int s = 0; s < DECODE_STAGES - 1; ++s) {
+      if (kb_start + s <= kb_end) issue(kb_start + s, s);
+      cp_async_commit();  // a group per stage, empty or not, keeps the group count in step with the pages
+    }
     int row_pos[2], row_lo[2];
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
@@ -325,14 +334,11 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
       row_lo[r] = lo;
     }
     for (int kb = kb_start; kb <= kb_end; ++kb) {
-      const int stage = (kb - kb_start) & 1;
-      if (kb < kb_end) {
-        issue(kb + 1, stage ^ 1);
-        cp_async_commit();
-        cp_async_wait<1>();
-      } else {
-        cp_async_wait<0>();
-      }
+      const int stage = (kb - kb_start) % DECODE_STAGES;
+      if (kb + DECODE_STAGES - 1 <= kb_end)
+        issue(kb + DECODE_STAGES - 1, (kb - kb_start + DECODE_STAGES - 1) % DECODE_STAGES);
+      cp_async_commit();
+      cp_async_wait<DECODE_STAGES - 1>();  // everything but the newest DECODE_STAGES - 1 groups: page kb has landed
       __syncthreads();
       const bf16* k_tile = kv_s + (size_t)stage * 2 * KV_TILE;
       // this warp's 16 keys of the page
@@ -344,8 +350,8 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
     }
   }
   // ---- the four warps' partial results meet in shared memory ----
-  float* red_o = reinterpret_cast<float*>(kv_s);           // [4][16][HD]
-  float* red_ml = red_o + 4 * 16 * HD;                      // [4][16][2]
+  float* red_o = reinterpret_cast<float*>(kv_s);           // [4][16][RED_LD]: padded rows, no 8-way bank conflicts
+  float* red_ml = red_o + 4 * 16 * RED_LD;                  // [4][16][2]
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     float l = st.l[r];
@@ -359,7 +365,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
 #pragma unroll
     for (int j = 0; j < HDP / 8; ++j) {
       if (j * 8 < HD) {
-        float* o = red_o + ((size_t)(warp * 16 + row)) * HD + j * 8 + 2 * (lane & 3);
+        float* o = red_o + ((size_t)(warp * 16 + row)) * RED_LD + j * 8 + 2 * (lane & 3);
         o[0] = st.o[j][2 * r];
         o[1] = st.o[j][2 * r + 1];
       }
@@ -376,7 +382,7 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
 #pragma unroll
     for (int w = 0; w < 4; ++w) {
       const float f = exp2f(red_ml[(w * 16 + row) * 2] - m_use);
-      o += red_o[((size_t)(w * 16 + row)) * HD + d] * f;
+      o += red_o[((size_t)(w * 16 + row)) * RED_LD + d] * f;
       l += red_ml[(w * 16 + row) * 2 + 1] * f;
     }
     const int head = kvh * G + g0 + row;
@@ -413,8 +419,8 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 }
 
 constexpr int PREFILL_SMEM = (64 * LD + 4 * KV_TILE) * 2;
-constexpr int DECODE_KV_BYTES = 4 * KV_TILE * 2;
-constexpr int DECODE_RED_BYTES = (4 * 16 * HD + 4 * 16 * 2) * 4;
+constexpr int DECODE_KV_BYTES = 2 * DECODE_STAGES * KV_TILE * 2;
+constexpr int DECODE_RED_BYTES = (4 * 16 * RED_LD + 4 * 16 * 2) * 4;
 constexpr int DECODE_SMEM = 16 * LD * 2 + (DECODE_KV_BYTES > DECODE_RED_BYTES ? DECODE_KV_BYTES : DECODE_RED_BYTES);
 
 }  // namespace

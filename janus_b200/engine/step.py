@@ -10,6 +10,7 @@ crates/janus-engine/src/model/transformer/forward.rs:25,139-141.)
 """
 from __future__ import annotations
 
+import gc
 from dataclasses import dataclass, field
 from typing import Dict, List, Optional, Sequence, Tuple
 
@@ -304,8 +305,17 @@ class Engine:
             key = (B, cap, self.workspace.generation, key[3])
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
-            with torch.cuda.graph(graph):
-                rec.run_forward()
+            # No garbage collection while capturing: collecting an older engine would destroy
+            # its CUDA graphs in the middle of this capture, which invalidates it.
+            gc.collect()
+            gc_was_on = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(graph):
+                    rec.run_forward()
+            finally:
+                if gc_was_on:
+                    gc.enable()
             rec.graph, rec.launches = graph, ops.launch_count() - before
             self._graphs[key] = rec
             # the eager run and the capture wrote this step's keys already; the

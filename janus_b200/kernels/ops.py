@@ -327,3 +327,32 @@ def attention_bf16_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
         _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
         int(n_splits), _stream()), "attention_bf16_decode", kernels=2 if n_splits > 1 else 1)
+
+
+# -- tcgen05 prefill attention (head sizes 64 and 128, power-of-two groups) ------------------
+def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
+    import os
+    g = nh // max(nkv, 1)
+    return (os.environ.get("JANUS_ATTN_TC", "1") != "0" and hd in (64, 128) and nkv > 0 and nh % nkv == 0
+            and g <= 128 and (g & (g - 1)) == 0)
+
+
+def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                         block_table: torch.Tensor, q_start: torch.Tensor, kv_len: torch.Tensor,
+                         n_seqs: int, max_q_len: int, nh: int, nkv: int, hd: int, page_size: int,
+                         window: int, scale: float) -> None:
+    """As attention_bf16_prefill, on the tcgen05 tensor cores."""
+    T = q.shape[0]
+    _need(q, "attention q", torch.bfloat16, (T, nh * hd))
+    _need(out, "attention out", torch.bfloat16, (T, nh * hd))
+    _need(k_cache, "k cache", torch.bfloat16)
+    _need(v_cache, "v cache", torch.bfloat16)
+    _need(block_table, "block table", torch.int32)
+    _need(q_start, "q_start", torch.int32, (n_seqs + 1,))
+    _need(kv_len, "kv_len", torch.int32, (n_seqs,))
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
+        raise KernelError(f"attention_tc: cache shape {tuple(k_cache.shape)} does not fit [pages, {nkv}, {page_size}, {hd}]")
+    _check(library("attention_tc", {"JB_HEAD_DIM": int(hd)}).jb_attention_tc_prefill(
+        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
+        T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
+        ctypes.c_float(scale), _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")

@@ -78,6 +78,11 @@ class GQAttention(Mixer):
             ops.attention_bf16_decode(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.kv_len,
                                       self.nh, self.nkv, self.hd, group.page_size, self.window, self.scale,
                                       ctx.workspace, ctx.max_kv_len_bound)
+        elif ops.attention_tc_supported(self.nh, self.nkv, self.hd):
+            # head sizes 64 / 128 and power-of-two groups: flash attention on the tcgen05 tensor cores
+            ops.attention_tc_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start,
+                                     ctx.kv_len, ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, self.hd,
+                                     group.page_size, self.window, self.scale)
         else:
             ops.attention_bf16_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start,
                                        ctx.kv_len, ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, self.hd,

@@ -1,0 +1,65 @@
+"""One layer with the Llama-3.1-8B sizes (hidden 4096, 32 heads over 8 kv heads of
+128, intermediate 14336, llama3 rope scaling) and a small vocabulary, against the
+plain implementation, in float32 and in bfloat16: a prompt in one step, the rest
+token by token across page boundaries, and two sequences of unequal length in
+one batch.  The product path's tile sizes, split-K and key splits are those of
+the full model, which the tiny configurations never reach."""
+import numpy as np
+import pytest
+import torch
+
+import plain_llama as P
+from helpers import make_model_dir, random_tokens, rel_err, tol_for
+
+pytestmark = pytest.mark.gpu
+
+BIG_LAYER = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=4096, num_hidden_layers=1, num_attention_heads=32,
+    num_key_value_heads=8, head_dim=128, intermediate_size=14336, vocab_size=2048, max_position_embeddings=1024,
+    rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=256),
+    tie_word_embeddings=False)
+
+
+@pytest.fixture(scope="module")
+def big_model(tmp_path_factory):
+    d = make_model_dir(BIG_LAYER, str(tmp_path_factory.mktemp("big") / "m"), seed=11, dtype="bfloat16", sharpen=1.5)
+    cfg, w = P.read_model_dir(d)
+    ids = [random_tokens(n, BIG_LAYER["vocab_size"], 70 + n) for n in (330, 150)]
+    ref = [P.forward(cfg, w, x).numpy() for x in ids]
+    return d, ids, ref
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_one_big_layer_matches_plain(big_model, dtype):
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    from janus_b200.kernels import ops
+    d, ids, ref = big_model
+    model = janus_b200.load(d, dtype=dtype, max_tokens=1024)
+    tol = tol_for(dtype)
+    a, b = model.alloc_slot(), model.alloc_slot()
+    # unequal prompts in one step; the first stops short of a page boundary (position 320)
+    out = model.step([StepEntry(a, ids[0][:310], range(310)), StepEntry(b, ids[1][:100], range(100))]).cpu().numpy()
+    assert rel_err(out[:310], ref[0][:310]) < tol and rel_err(out[310:], ref[1][:100]) < tol
+    # one token each (CUDA-graph decode), across the boundary; the shorter sequence ends earlier
+    rows_a, rows_b = [], []
+    for j in range(20):
+        entries = [StepEntry(a, [ids[0][310 + j]], [0])]
+        if j < 12:
+            entries.append(StepEntry(b, [ids[1][100 + j]], [0]))
+        got = model.step(entries).cpu().numpy()
+        rows_a.append(got[0:1])
+        if j < 12:
+            rows_b.append(got[1:2])
+        if j == 11:
+            model.free_slot(b)
+    assert rel_err(np.concatenate(rows_a), ref[0][310:330]) < tol
+    assert rel_err(np.concatenate(rows_b), ref[1][100:112]) < tol
+    # the freed slot is used again: the rest of the second sequence from its start, in two chunks
+    c = model.alloc_slot()
+    first = model.step([StepEntry(c, ids[1][:64], [63])]).cpu().numpy()
+    rest = model.step([StepEntry(c, ids[1][64:], range(86))]).cpu().numpy()
+    assert rel_err(first, ref[1][63:64]) < tol and rel_err(rest, ref[1][64:]) < tol
+    ops.check_kernel_status(model.device)
