@@ -220,6 +220,61 @@ def run_ours(args):
     print(json.dumps(out))
 
 
+# BASELINE.json configs[3] and configs[4]: whole workloads through the public entry point
+WORKLOADS = {
+    "1b": dict(
+        config=dict(architectures=["LlamaForCausalLM"], hidden_size=2048, num_hidden_layers=16, num_attention_heads=32,
+                    num_key_value_heads=8, head_dim=64, intermediate_size=8192, vocab_size=128256,
+                    max_position_embeddings=2048, rms_norm_eps=1e-5, rope_theta=500000.0,
+                    rope_scaling=dict(rope_type="llama3", factor=32.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                      original_max_position_embeddings=8192),
+                    tie_word_embeddings=True),
+        seed=3, batch=64, prompt_range=(16, 1024), max_new=256, context=2048),
+    "13b": dict(
+        config=dict(architectures=["LlamaForCausalLM"], hidden_size=5120, num_hidden_layers=40, num_attention_heads=40,
+                    num_key_value_heads=40, head_dim=128, intermediate_size=13824, vocab_size=32000,
+                    max_position_embeddings=4096, rms_norm_eps=1e-5, rope_theta=10000.0, rope_scaling=None,
+                    tie_word_embeddings=False),
+        seed=4, batch=16, prompt_range=(128, 3072), max_new=4096, context=4096),
+}
+
+
+def run_workload(name):
+    """A whole workload of BASELINE.json (1B: 64 sequences, prompts U[16,1024], 256 new tokens each;
+    13B: batch 16, prompts U[128,3072], decoding until 4,096 positions) through Model.generate."""
+    import torch
+
+    import janus_b200
+    w = WORKLOADS[name]
+    g = torch.Generator().manual_seed(w["seed"])
+    lo, hi = w["prompt_range"]
+    lens = torch.randint(lo, hi + 1, (w["batch"],), generator=g).tolist()
+    V = w["config"]["vocab_size"]
+    prompts = [torch.randint(0, V, (n,), generator=g).tolist() for n in lens]
+    room = sum((min(n + w["max_new"], w["context"]) + 63) // 64 * 64 for n in lens)
+    model = janus_b200.load_random(w["config"], seed=w["seed"], dtype="bfloat16", max_tokens=room + 64 * w["batch"],
+                                   max_slots=w["batch"], max_seq_len=w["context"], norm_std=0.0)
+    model.generate([p[:32] for p in prompts[:w["batch"]]], max_tokens=4, ignore_eos=True)      # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    out, stats = model.generate(prompts, max_tokens=w["max_new"], ignore_eos=True)
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - t0
+    new_tokens = sum(len(o) for o in out)
+    print(json.dumps({
+        "impl": "janus_b200", "workload": name, "metric": "generated tokens/s, whole workload through Model.generate",
+        "value": round(new_tokens / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3),
+        "prompt_tokens": sum(lens), "new_tokens": new_tokens, "decode_steps": stats.decode_steps,
+        "prefill_tokens_per_s": round(stats.prefill_tokens_per_s, 1),
+        "decode_tokens_per_s": round(stats.decode_tokens_per_s, 1), "dtype": "bf16",
+        "data": f"synthetic token ids, random-init weights (seed {w['seed']})",
+        "config": {"batch": w["batch"], "prompt_lengths": f"U[{lo},{hi}]", "context": w["context"],
+                   "layers": w["config"]["num_hidden_layers"], "hidden": w["config"]["hidden_size"],
+                   "heads": w["config"]["num_attention_heads"], "kv_heads": w["config"]["num_key_value_heads"],
+                   "head_dim": w["config"]["head_dim"], "intermediate": w["config"]["intermediate_size"],
+                   "vocab": V}}))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -229,6 +284,8 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="batch size of the headline number")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in `config`)")
     ap.add_argument("--quick", action="store_true", help="headline batch only")
+    ap.add_argument("--workload", default="8b", choices=["8b", "1b", "13b"],
+                    help="8b: the headline benchmark; 1b / 13b: the other workloads of BASELINE.json, end to end")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -240,6 +297,9 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.workload != "8b":
+        run_workload(args.workload)
+        return 0
     run_ours(args)
     return 0
 
