@@ -279,17 +279,43 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
 }
 
 // ------------------------------- decode -------------------------------------
+// Optional fused input of the decode kernel: instead of rotated bf16 queries and a cache that
+// already holds the new token, the q/k/v projection's float32 output [seq][q heads | k heads | v heads];
+// the kernel rotates q and k at the token's position (cos_sin null = no rotation), appends k and v
+// to the cache (write_kv) and uses them.  qkv == nullptr turns this off.
+struct FusedInput {
+  const float* qkv;
+  int qkv_stride;
+  const float* cos_sin;  // [positions][HD / 2][2]
+  const int* dest;       // [seq] cache row (page * 64 + row) of the new token
+  bf16* k_out;
+  bf16* v_out;
+  int write_kv;
+};
+
+__device__ __forceinline__ void rotate_pair(float x0, float x1, const float* cs, int i, float& y0, float& y1) {
+  if (cs == nullptr) {
+    y0 = x0;
+    y1 = x1;
+    return;
+  }
+  const float c = cs[2 * i], s = cs[2 * i + 1];
+  y0 = x0 * c - x1 * s;
+  y1 = x0 * s + x1 * c;
+}
+
 // part_o: [seq][head][split][HD] float32 (unnormalised), part_ml: [seq][head][split][2] (max, sum).
 __global__ void __launch_bounds__(THREADS) decode_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     const int* __restrict__ block_table, const int* __restrict__ kv_len, int nh, int nkv, int max_pages,
-    int window, float scale_log2, int n_splits) {
+    int window, float scale_log2, int n_splits, FusedInput fused) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   jb::pdl_launch_dependents();
   jb::pdl_wait();
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [16][LD]
-  bf16* kv_s = q_s + 16 * LD;                     // [DECODE_STAGES][K, V][64][LD]; reused as float scratch at the end
+  bf16* new_kv = q_s + 16 * LD;                   // [2][LD]: the new token's rotated key and its value (fused input)
+  bf16* kv_s = new_kv + 2 * LD;                   // [DECODE_STAGES][K, V][64][LD]; reused as float scratch at the end
   const int G = nh / nkv;
   const int n_rb = (G + 15) / 16;
   const int seq = blockIdx.x, kvh = blockIdx.y / n_rb, rb = blockIdx.y % n_rb, split = blockIdx.z;
@@ -308,12 +334,15 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   RowState st;
   st.init();
   if (kb_start <= kb_end) {
-    zero_pad_columns(q_s, 16 + 2 * DECODE_STAGES * PAGE);
-    for (int ch = threadIdx.x; ch < 16 * CHUNKS; ch += THREADS) {
-      const int r = ch / CHUNKS, col = ch % CHUNKS;
-      const bool valid = r < n_rows;
-      const bf16* src = q + ((size_t)seq * nh + kvh * G + g0 + (valid ? r : 0)) * HD + col * 8;
-      cp_async16(q_s + r * LD + col * 8, src, valid);
+    zero_pad_columns(q_s, 16 + 2 + 2 * DECODE_STAGES * PAGE);
+    const bool patch_new = fused.qkv != nullptr && fused.write_kv && kb_end == kb_last;  // this CTA sees the new key
+    if (fused.qkv == nullptr) {
+      for (int ch = threadIdx.x; ch < 16 * CHUNKS; ch += THREADS) {
+        const int r = ch / CHUNKS, col = ch % CHUNKS;
+        const bool valid = r < n_rows;
+        const bf16* src = q + ((size_t)seq * nh + kvh * G + g0 + (valid ? r : 0)) * HD + col * 8;
+        cp_async16(q_s + r * LD + col * 8, src, valid);
+      }
     }
     auto issue = [&](int kb, int stage) {
       const size_t page = (size_t)pages[kb];
@@ -326,6 +355,41 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
     for (int s = 0; s < DECODE_STAGES - 1; ++s) {
       if (kb_start + s <= kb_end) issue(kb_start + s, s);
       cp_async_commit();  // a group per stage, empty or not, keeps the group count in step with the pages
+    }
+    if (fused.qkv != nullptr) {
+      // (after the first page loads are in flight, so that the rotation hides behind them)
+      // q (and the new k, v) come as the projection's float32 accumulators: rotate here
+      constexpr int HALF = HD / 2;
+      const float* row = fused.qkv + (size_t)seq * fused.qkv_stride;
+      const float* cs = fused.cos_sin ? fused.cos_sin + (size_t)pos * HD : nullptr;  // [HALF][2] at this position
+      for (int idx = threadIdx.x; idx < n_rows * HALF; idx += THREADS) {  // the rows that exist
+        const int r = idx / HALF, i = idx % HALF;
+        const float* x = row + (size_t)(kvh * G + g0 + r) * HD;
+        float y0, y1;
+        rotate_pair(x[i], x[i + HALF], cs, i, y0, y1);
+        q_s[r * LD + i] = __float2bfloat16_rn(y0);
+        q_s[r * LD + i + HALF] = __float2bfloat16_rn(y1);
+      }
+      for (int idx = n_rows * HD + threadIdx.x; idx < 16 * HD; idx += THREADS)  // the rest of the 16-row tile
+        q_s[(idx / HD) * LD + idx % HD] = __float2bfloat16_rn(0.0f);
+      if (patch_new) {
+        const float* kx = row + (size_t)(nh + kvh) * HD;
+        const float* vx = row + (size_t)(nh + nkv + kvh) * HD;
+        const int dst = fused.dest[seq];
+        const size_t g_off = (((size_t)(dst / PAGE) * nkv + kvh) * PAGE + dst % PAGE) * HD;
+        for (int i = threadIdx.x; i < HALF; i += THREADS) {
+          float y0, y1;
+          rotate_pair(kx[i], kx[i + HALF], cs, i, y0, y1);
+          const bf16 k0 = __float2bfloat16_rn(y0), k1 = __float2bfloat16_rn(y1);
+          const bf16 v0 = __float2bfloat16_rn(vx[i]), v1 = __float2bfloat16_rn(vx[i + HALF]);
+          new_kv[i] = k0; new_kv[i + HALF] = k1;
+          new_kv[LD + i] = v0; new_kv[LD + i + HALF] = v1;
+          if (rb == 0) {  // one CTA per (sequence, kv head) appends to the cache for the steps to come
+            fused.k_out[g_off + i] = k0; fused.k_out[g_off + i + HALF] = k1;
+            fused.v_out[g_off + i] = v0; fused.v_out[g_off + i + HALF] = v1;
+          }
+        }
+      }
     }
     int row_pos[2], row_lo[2];
 #pragma unroll
@@ -340,7 +404,16 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
       cp_async_commit();
       cp_async_wait<DECODE_STAGES - 1>();  // everything but the newest DECODE_STAGES - 1 groups: page kb has landed
       __syncthreads();
-      const bf16* k_tile = kv_s + (size_t)stage * 2 * KV_TILE;
+      bf16* k_tile = kv_s + (size_t)stage * 2 * KV_TILE;
+      if (patch_new && kb == kb_last) {
+        // the page as loaded holds a stale row at the new position: put the new key and value there
+        const int r = pos % PAGE;
+        for (int i = threadIdx.x; i < 2 * HD; i += THREADS) {
+          const int which = i / HD, d = i % HD;
+          k_tile[which * KV_TILE + r * LD + d] = new_kv[which * LD + d];
+        }
+        __syncthreads();
+      }
       // this warp's 16 keys of the page
       float s[2][4];
       qk_product<2>(s, q_s, k_tile + warp * 16 * LD, lane);
@@ -421,7 +494,7 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 constexpr int PREFILL_SMEM = (64 * LD + 4 * KV_TILE) * 2;
 constexpr int DECODE_KV_BYTES = 2 * DECODE_STAGES * KV_TILE * 2;
 constexpr int DECODE_RED_BYTES = (4 * 16 * RED_LD + 4 * 16 * 2) * 4;
-constexpr int DECODE_SMEM = 16 * LD * 2 + (DECODE_KV_BYTES > DECODE_RED_BYTES ? DECODE_KV_BYTES : DECODE_RED_BYTES);
+constexpr int DECODE_SMEM = (16 + 2) * LD * 2 + (DECODE_KV_BYTES > DECODE_RED_BYTES ? DECODE_KV_BYTES : DECODE_RED_BYTES);
 
 }  // namespace
 
@@ -453,11 +526,11 @@ JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, cons
 
 // Scratch (when n_splits > 1): part_o float32 [n_seqs * nh * n_splits * hd], part_ml float32
 // [n_seqs * nh * n_splits * 2].
-JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
-                                       float* part_o, float* part_ml, const int* block_table,
-                                       const int* kv_len, int n_seqs, int nh, int nkv, int hd, int page_size,
-                                       int max_pages, int window, float scale, int n_splits,
-                                       cudaStream_t stream) {
+namespace {
+int decode_launch(const void* q, const void* k_cache, const void* v_cache, void* out, float* part_o, float* part_ml,
+                  const int* block_table, const int* kv_len, int n_seqs, int nh, int nkv, int hd, int page_size,
+                  int max_pages, int window, float scale, int n_splits, const FusedInput& fused,
+                  cudaStream_t stream) {
   if (n_seqs <= 0) return 0;
   JB_REFUSE(hd != HD, "attention_bf16: built for head_dim %d, called with %d", HD, hd);
   JB_REFUSE(page_size != PAGE, "attention_bf16: page size %d (need %d)", page_size, PAGE);
@@ -475,7 +548,7 @@ JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const
   jb::Launch cfg(grid, dim3(THREADS), DECODE_SMEM, stream);
   cudaError_t le = cudaLaunchKernelEx(&cfg.c, decode_kernel, (const bf16*)q, (const bf16*)k_cache,
                                       (const bf16*)v_cache, (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
-                                      max_pages, window, scale * LOG2E, n_splits);
+                                      max_pages, window, scale * LOG2E, n_splits, fused);
   if (le != cudaSuccess) return (int)le;
   if (n_splits > 1) {
     jb::Launch cfg2(dim3(n_seqs * nh), dim3(HD >= 128 ? 128 : 64), 0, stream);
@@ -484,6 +557,33 @@ JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const
     if (le != cudaSuccess) return (int)le;
   }
   return 0;
+}
+}  // namespace
+
+JB_EXPORT int jb_attention_bf16_decode(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                       float* part_o, float* part_ml, const int* block_table,
+                                       const int* kv_len, int n_seqs, int nh, int nkv, int hd, int page_size,
+                                       int max_pages, int window, float scale, int n_splits,
+                                       cudaStream_t stream) {
+  return decode_launch(q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, n_seqs, nh, nkv, hd,
+                       page_size, max_pages, window, scale, n_splits, FusedInput{}, stream);
+}
+
+// As jb_attention_bf16_decode, but q, k and v of the new tokens come as the projection's float32
+// output qkv[seq][q heads | k heads | v heads] (row stride qkv_stride floats): the kernel rotates q
+// and k with cos_sin[position] (null = no rotation), appends k and v at cache row dest[seq]
+// (write_kv = 0: a layer that reads another layer's cache; only q is used) and attends.
+JB_EXPORT int jb_attention_bf16_decode_fused(const float* qkv, int qkv_stride, const float* cos_sin,
+                                             const int* dest, void* k_cache, void* v_cache, void* out,
+                                             float* part_o, float* part_ml, const int* block_table,
+                                             const int* kv_len, int n_seqs, int nh, int nkv, int hd,
+                                             int page_size, int max_pages, int window, float scale,
+                                             int n_splits, int write_kv, cudaStream_t stream) {
+  JB_REFUSE(qkv == nullptr || (write_kv && dest == nullptr), "attention_bf16 fused decode: missing input");
+  JB_REFUSE(hd % 2 != 0, "attention_bf16 fused decode: head_dim %d must be even for the rotation", hd);
+  FusedInput fused{qkv, qkv_stride, cos_sin, dest, (bf16*)k_cache, (bf16*)v_cache, write_kv};
+  return decode_launch(nullptr, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, n_seqs, nh, nkv, hd,
+                       page_size, max_pages, window, scale, n_splits, fused, stream);
 }
 
 // ---------------------------------------------------------------------------
@@ -537,7 +637,7 @@ JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cach
   dim3 grid(n_seqs, nkv * n_rb, n_splits);
   decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                                         (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
-                                                        max_pages, window, scale * LOG2E, n_splits);
+                                                        max_pages, window, scale * LOG2E, n_splits, FusedInput{});
   JB_CHECK_LAUNCH();
   if (n_splits > 1) {
     decode_combine_kernel<<<n_seqs * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_splits);

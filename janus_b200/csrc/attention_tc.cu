@@ -8,11 +8,12 @@
 //   warp 0     TMA producer: the Q tile once (4-D tensor map: dim, group head, kv head, token),
 //              then K and V pages into a 3-stage ring (128-byte swizzle)
 //   warp 1     one lane issues tcgen05.mma:  S_j = Q . K_j^T  into one of two TMEM buffers,
-//              O_j = P_j . V_j  into one of two more; V is the MN-major operand (its rows are keys)
-//   warps 2-5  one thread per row: read S_j from TMEM, mask, online softmax in float32 (exp2),
-//              write P_j as bf16 into swizzled shared memory, add O_{j-1} from TMEM into the
-//              row's float32 accumulator registers and rescale them
-// so that the tensor core computes S_{j+1} and O_{j-1} while the softmax of block j runs.
+//              O += P_j . V_j  into a float32 accumulator in TMEM; V is the MN-major operand (its rows are keys)
+//   warps 2-5  one thread per row: read S_j from TMEM, mask, softmax in float32 (exp2) against a
+//              reference maximum, write P_j as bf16 into swizzled shared memory.  The reference maximum
+//              is raised, and O in TMEM rescaled, only when a row's maximum has grown by more than 2^8
+//              since it was set (P then stays below 256, exact enough in bf16 and harmless in float32).
+// so that the tensor core computes S_{j+1} and the P.V product of block j-1 while the softmax of block j runs.
 // Every mbarrier wait is bounded in time and reports through `*status` (codes 11-13).
 // Formulas: crates/janus-engine/src/compute/shaders/attention.wgsl:96-115,170-185,
 // softmax.wgsl:29-50; kv head of query head h is floor(h * nkv / nh).
@@ -42,8 +43,9 @@ constexpr int K_BYTES = NH64 * PAGE * 128, V_BYTES = K_BYTES;
 constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr int P_BYTES = BM * 128;      // 128 rows x 64 keys bf16
 constexpr int TMEM_S0 = 0, TMEM_O0 = 128;
-constexpr int TMEM_COLS = (128 + 2 * HD) <= 256 ? 256 : 512;
-constexpr int N_BARS = 1 + 2 * STAGES + 2 + 2 + 2 + 2 + 2;
+constexpr int TMEM_COLS = 256;         // S: 2 x 64 columns, O: HD <= 128 columns
+constexpr float RESCALE_LOG2 = 8.0f;   // the reference maximum follows a row's maximum when it has grown by 2^8
+constexpr int N_BARS = 1 + 2 * STAGES + 2 + 2 + 2 + 1;
 constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + N_BARS * 8 + 16 + 1024;
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
@@ -123,6 +125,21 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, uint32_t* r) {
       : "memory");
 }
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+__device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t* r) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], "
+      "{%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+        "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+      : "memory");
+}
+__device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// 2^x by the special-function unit (2 ulp); arguments are <= 8, -inf gives 0
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 
 // K-major operand, rows of 128 bytes, 128-byte swizzle in 8-row groups of 1024 bytes.
 __device__ __forceinline__ uint64_t desc_k_sw128(uint32_t addr) {
@@ -168,7 +185,7 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
   uint32_t* tmem_slot = (uint32_t*)(bars + N_BARS);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * STAGES, s_full = kv_empty + 8 * STAGES,
-                 s_free = s_full + 16, p_full = s_free + 16, o_full = p_full + 16, o_free = o_full + 16;
+                 s_free = s_full + 16, p_full = s_free + 16, o_full = p_full + 16;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   jb::pdl_launch_dependents();
@@ -182,9 +199,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
       mbar_init(s_full + 8 * b, 1);
       mbar_init(s_free + 8 * b, 128);
       mbar_init(p_full + 8 * b, 128);
-      mbar_init(o_full + 8 * b, 1);
-      mbar_init(o_free + 8 * b, 128);
     }
+    mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -257,15 +273,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
         if (j + 1 < nb) ok = issue_s(j + 1);  // the tensor core works on S_{j+1} while the softmax of block j runs
         if (!ok) break;
         const int s = j % STAGES, b = j & 1;
-        ok = mbar_wait(p_full + 8 * b, (j >> 1) & 1, status, 12) && mbar_wait(o_free + 8 * b, ((j >> 1) & 1) ^ 1, status, 12);
+        ok = mbar_wait(p_full + 8 * b, (j >> 1) & 1, status, 12);  // P_j is written and O is rescaled if it had to be
         if (!ok) break;
         tc_fence_after();
         const uint32_t v_base = kv_s + s * STAGE_BYTES + K_BYTES;
         const uint64_t p = desc_k_sw128(p_s + b * P_BYTES);
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks)  // 16 keys per step = two 8-key atoms of 1024 bytes
-          umma(tmem + TMEM_O0 + b * HD, p + 2 * ks, desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o, ks ? 1u : 0u);
-        umma_commit(o_full + 8 * b);
+          umma(tmem + TMEM_O0, p + 2 * ks, desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o, (j | ks) ? 1u : 0u);
+        umma_commit(o_full);
         umma_commit(kv_empty + 8 * s);
       }
     }
@@ -278,28 +294,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
     const int row_pos = valid ? pos0 + tl : -1;
     const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    float m = -CUDART_INF_F, l = 0.0f;
-    float o[HD];
-#pragma unroll
-    for (int d = 0; d < HD; ++d) o[d] = 0.0f;
+    float m_ref = -CUDART_INF_F, l = 0.0f;   // l is the row sum relative to m_ref
     bool ok = true;
-    auto add_o = [&](int j) -> bool {  // o += O_j (TMEM buffer j & 1)
-      const int b = j & 1;
-      if (!mbar_wait(o_full + 8 * b, (j >> 1) & 1, status, 13)) return false;
-      tc_fence_after();
-#pragma unroll
-      for (int c0 = 0; c0 < HD; c0 += 32) {
-        uint32_t r[32];
-        tmem_ld16(lane_addr + TMEM_O0 + b * HD + c0, r);
-        tmem_ld16(lane_addr + TMEM_O0 + b * HD + c0 + 16, r + 16);
-        tmem_ld_wait();
-#pragma unroll
-        for (int i = 0; i < 32; ++i) o[c0 + i] += __uint_as_float(r[i]);
-      }
-      tc_fence_before();
-      mbar_arrive(o_free + 8 * b);
-      return true;
-    };
     for (int j = 0; j < nb && ok; ++j) {
       const int b = j & 1;
       ok = mbar_wait(s_full + 8 * b, (j >> 1) & 1, status, 13);
@@ -312,17 +308,41 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
       tc_fence_before();
       mbar_arrive(s_free + 8 * b);
       const int key0 = (kb_start + j) * PAGE;
+      if (key0 + PAGE - 1 > row_pos || key0 < row_lo) {   // only blocks that touch the causal edge or the window
+#pragma unroll
+        for (int c = 0; c < 64; ++c) {
+          const int kp = key0 + c;
+          if (!(kp <= row_pos && kp >= row_lo)) sr[c] = 0xff800000u;  // -inf
+        }
+      }
       float mx = -CUDART_INF_F;
 #pragma unroll
-      for (int c = 0; c < 64; ++c) {
-        const int kp = key0 + c;
-        const float v = (kp <= row_pos && kp >= row_lo) ? __uint_as_float(sr[c]) * scale_log2 : -CUDART_INF_F;
-        sr[c] = __float_as_uint(v);
-        mx = fmaxf(mx, v);
+      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
+      mx *= scale_log2;  // the scale is positive: the maximum commutes with it
+      // tcgen05.ld/st are warp-wide: the warp rescales together if any of its rows has to
+      const bool grow = mx > m_ref + RESCALE_LOG2 || (m_ref == -CUDART_INF_F && mx > -CUDART_INF_F);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mx);
+        if (j > 0) {
+          ok = mbar_wait(o_full, (j - 1) & 1, status, 13);  // the P.V product of block j-1 has landed in O
+          if (!ok) break;
+          tc_fence_after();
+          const float corr = m_new == -CUDART_INF_F ? 1.0f : exp2f(m_ref - m_new);  // 0 if nothing was seen before
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + TMEM_O0 + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            tmem_st16(lane_addr + TMEM_O0 + c0, r);
+          }
+          tmem_st_wait();
+          l *= corr;
+        }
+        m_ref = m_new;
       }
-      const float m_new = fmaxf(m, mx);
-      const float m_use = m_new == -CUDART_INF_F ? 0.0f : m_new;
-      const float corr = exp2f(m - m_use);
+      const float neg_ref = m_ref == -CUDART_INF_F ? 0.0f : -m_ref;
       float sum = 0.0f;
       // P_j as bf16 into the swizzled tile: 16-byte chunk c of row r lies at r*128 + ((c ^ (r & 7)) * 16)
       const uint32_t p_row = p_s + b * P_BYTES + row * 128;
@@ -331,8 +351,8 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
         uint32_t w[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
-          const float p0 = exp2f(__uint_as_float(sr[c * 8 + 2 * e]) - m_use);
-          const float p1 = exp2f(__uint_as_float(sr[c * 8 + 2 * e + 1]) - m_use);
+          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c * 8 + 2 * e]), scale_log2, neg_ref));
+          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c * 8 + 2 * e + 1]), scale_log2, neg_ref));
           sum += p0 + p1;
           w[e] = pack_bf16(p0, p1);
         }
@@ -340,26 +360,34 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
                      "r"(w[1]), "r"(w[2]), "r"(w[3])
                      : "memory");
       }
+      l += sum;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+      tc_fence_before();
       mbar_arrive(p_full + 8 * b);
-      if (j > 0) ok = add_o(j - 1);  // O_{j-1} belongs to the running maximum before this block
-#pragma unroll
-      for (int d = 0; d < HD; ++d) o[d] *= corr;
-      l = l * corr + sum;
-      m = m_new;
     }
-    if (ok && nb > 0) ok = add_o(nb - 1);
-    if (ok && valid) {
+    if (ok && nb > 0) ok = mbar_wait(o_full, (nb - 1) & 1, status, 13);
+    if (ok) {
+      tc_fence_after();
       const float inv = 1.0f / l;
-      bf16* dst = out + ((size_t)(qs + tok0 + tl) * nh + kvh * G + row % G) * HD;
+      bf16* dst = out + ((size_t)(qs + tok0 + (valid ? tl : 0)) * nh + kvh * G + row % G) * HD;
 #pragma unroll
-      for (int c = 0; c < HD / 8; ++c) {
-        uint4 w;
-        w.x = pack_bf16(o[c * 8] * inv, o[c * 8 + 1] * inv);
-        w.y = pack_bf16(o[c * 8 + 2] * inv, o[c * 8 + 3] * inv);
-        w.z = pack_bf16(o[c * 8 + 4] * inv, o[c * 8 + 5] * inv);
-        w.w = pack_bf16(o[c * 8 + 6] * inv, o[c * 8 + 7] * inv);
-        *reinterpret_cast<uint4*>(dst + c * 8) = w;
+      for (int c0 = 0; c0 < HD; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_addr + TMEM_O0 + c0, r);   // warp-wide: rows without a token load too and store nothing
+        tmem_ld_wait();
+        if (valid) {
+          uint4 w0, w1;
+          w0.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          w0.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          w0.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          w0.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          w1.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          w1.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          w1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          w1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          *reinterpret_cast<uint4*>(dst + c0) = w0;
+          *reinterpret_cast<uint4*>(dst + c0 + 8) = w1;
+        }
       }
     }
     tc_fence_before();

@@ -51,6 +51,14 @@ __global__ void embed_gather_kernel(const TT* __restrict__ table, const int* __r
   }
 }
 
+// A norm can also clear a scratch buffer for the part that runs after it (the target of a
+// product whose slices of K meet by atomic adds): each block clears its share.
+__device__ __forceinline__ void clear_slice(float4* __restrict__ clear, size_t n4) {
+  if (clear == nullptr) return;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n4; i += (size_t)gridDim.x * blockDim.x)
+    clear[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+}
+
 // ---- RMSNorm: one block per output row; y = (x / sqrt(mean(x^2) + eps)) * gamma -----
 constexpr int NORM_THREADS = 256;
 constexpr int NORM_CACHE = 8;  // float4 per thread kept in registers (rows up to 8192 wide are read once)
@@ -59,10 +67,12 @@ template <typename TG, typename TO>
 __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_vec_kernel(const float* __restrict__ x,
                                                                   const int* __restrict__ row_index,
                                                                   const TG* __restrict__ gamma, float eps,
-                                                                  TO* __restrict__ out, int H) {
+                                                                  TO* __restrict__ out, int H,
+                                                                  float4* __restrict__ clear, size_t clear_n4) {
   __shared__ float scratch[33];
   jb::pdl_launch_dependents();
   jb::pdl_wait();
+  clear_slice(clear, clear_n4);
   const int r = blockIdx.x;
   const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
   const float* xr = x + src * H;
@@ -100,10 +110,12 @@ __global__ void __launch_bounds__(NORM_THREADS) rmsnorm_vec_kernel(const float* 
 
 template <typename TG, typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index,
-                               const TG* __restrict__ gamma, float eps, TO* __restrict__ out, int H) {
+                               const TG* __restrict__ gamma, float eps, TO* __restrict__ out, int H,
+                               float4* __restrict__ clear, size_t clear_n4) {
   __shared__ float scratch[33];
   jb::pdl_launch_dependents();
   jb::pdl_wait();
+  clear_slice(clear, clear_n4);
   const int r = blockIdx.x;
   const size_t src = row_index ? (size_t)row_index[r] : (size_t)r;
   const float* xr = x + src * H;
@@ -166,15 +178,23 @@ JB_EXPORT int jb_embed_gather(const void* table, int table_dtype, const int* ids
   return (int)e;
 }
 
+// clear (may be null): clear_n floats (a multiple of 4, 16-byte aligned) that the kernel sets to zero besides.
 JB_EXPORT int jb_rmsnorm(const float* x, const int* row_index, const void* gamma, int gamma_dtype, float eps,
-                         void* out, int out_dtype, int rows, int H, cudaStream_t stream) {
+                         void* out, int out_dtype, int rows, int H, float* clear, long long clear_n,
+                         cudaStream_t stream) {
   if (rows <= 0) return 0;
+  JB_REFUSE(clear != nullptr && ((clear_n & 3) != 0 || ((uintptr_t)clear & 15) != 0),
+            "rmsnorm: the buffer to clear is not made of whole 16-byte vectors");
+  float4* clear4 = (float4*)clear;
+  const size_t clear_n4 = clear ? (size_t)clear_n >> 2 : 0;
   const bool vec = (H & 3) == 0;
   jb::Launch cfg(dim3(rows), dim3(vec ? NORM_THREADS : (H >= 512 ? 256 : 128)), 0, stream);
   cudaError_t e;
 #define JB_LAUNCH_NORM(TG, TO)                                                                              \
-  e = vec ? cudaLaunchKernelEx(&cfg.c, rmsnorm_vec_kernel<TG, TO>, x, row_index, (const TG*)gamma, eps, (TO*)out, H) \
-          : cudaLaunchKernelEx(&cfg.c, rmsnorm_kernel<TG, TO>, x, row_index, (const TG*)gamma, eps, (TO*)out, H)
+  e = vec ? cudaLaunchKernelEx(&cfg.c, rmsnorm_vec_kernel<TG, TO>, x, row_index, (const TG*)gamma, eps, (TO*)out, H, \
+                               clear4, clear_n4)                                                                     \
+          : cudaLaunchKernelEx(&cfg.c, rmsnorm_kernel<TG, TO>, x, row_index, (const TG*)gamma, eps, (TO*)out, H,     \
+                               clear4, clear_n4)
   if (gamma_dtype == JB_F32 && out_dtype == JB_F32) JB_LAUNCH_NORM(float, float);
   else if (gamma_dtype == JB_F32 && out_dtype == JB_BF16) JB_LAUNCH_NORM(float, bf16);
   else if (gamma_dtype == JB_BF16 && out_dtype == JB_F32) JB_LAUNCH_NORM(bf16, float);

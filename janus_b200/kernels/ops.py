@@ -80,21 +80,25 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
 
 
 def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, out: torch.Tensor,
-            row_index: Optional[torch.Tensor] = None) -> None:
-    """out[r] = x[row_index[r] or r] / sqrt(mean(x^2) + eps) * gamma"""
+            row_index: Optional[torch.Tensor] = None, clear: Optional[torch.Tensor] = None) -> None:
+    """out[r] = x[row_index[r] or r] / sqrt(mean(x^2) + eps) * gamma.  `clear`: a float32
+    scratch tensor (whole 16-byte vectors) that the same launch sets to zero."""
     rows, H = out.shape
     _need(x, "rmsnorm x", torch.float32)
     _need(gamma, "rmsnorm gamma", None, (H,))
     _need(out, "rmsnorm out")
     if x.shape[1] != H:
         raise KernelError(f"rmsnorm: input width {x.shape[1]} != output width {H}")
+    if clear is not None:
+        _need(clear, "rmsnorm clear", torch.float32)
     if row_index is not None:
         _need(row_index, "rmsnorm row_index", torch.int32, (rows,))
     elif x.shape[0] < rows:
         raise KernelError("rmsnorm: fewer input rows than output rows")
     _check(library("elementwise").jb_rmsnorm(
         _ptr(x), _ptr(row_index), _ptr(gamma), dtype_code(gamma.dtype), ctypes.c_float(eps), _ptr(out),
-        dtype_code(out.dtype), rows, H, _stream()), "rmsnorm")
+        dtype_code(out.dtype), rows, H, _ptr(clear), ctypes.c_longlong(0 if clear is None else clear.numel()),
+        _stream()), "rmsnorm")
 
 
 def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
@@ -304,13 +308,18 @@ def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: 
     return max(1, min(pages, max((pages + 7) // 8, (128 + base - 1) // base)))
 
 
-def attention_bf16_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                           block_table: torch.Tensor, kv_len: torch.Tensor, nh: int, nkv: int, hd: int,
                           page_size: int, window: int, scale: float, workspace, max_kv_len: int,
-                          n_splits: Optional[int] = None) -> None:
-    """One new token per sequence (its last position) over its cached keys."""
-    B = q.shape[0]
-    _need(q, "attention q", torch.bfloat16, (B, nh * hd))
+                          n_splits: Optional[int] = None, qkv: Optional[torch.Tensor] = None,
+                          cos_sin: Optional[torch.Tensor] = None, dest: Optional[torch.Tensor] = None,
+                          write_kv: bool = True) -> None:
+    """One new token per sequence (its last position) over its cached keys.
+
+    Either `q` (rotated bf16 queries; the cache already holds the new token), or `qkv`: the
+    projection's float32 output [B, (nh + 2 nkv) hd] (or [B, nh hd] with write_kv False), which the
+    kernel rotates with `cos_sin` (None: no rotation), appends to the cache at rows `dest` and uses."""
+    B = out.shape[0]
     _need(out, "attention out", torch.bfloat16, (B, nh * hd))
     _need(k_cache, "k cache", torch.bfloat16)
     _need(v_cache, "v cache", torch.bfloat16)
@@ -323,10 +332,29 @@ def attention_bf16_decode(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch
     if n_splits > 1:
         part_o = workspace.get("attn_part_o", (B * nh * n_splits * hd,), torch.float32)
         part_ml = workspace.get("attn_part_ml", (B * nh * n_splits * 2,), torch.float32)
-    _check(_attention_lib(hd).jb_attention_bf16_decode(
-        _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
-        _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
-        int(n_splits), _stream()), "attention_bf16_decode", kernels=2 if n_splits > 1 else 1)
+    lib = _attention_lib(hd)
+    kernels = 2 if n_splits > 1 else 1
+    if qkv is None:
+        _need(q, "attention q", torch.bfloat16, (B, nh * hd))
+        _check(lib.jb_attention_bf16_decode(
+            _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
+            _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
+            int(n_splits), _stream()), "attention_bf16_decode", kernels=kernels)
+        return
+    _need(qkv, "qkv", torch.float32)
+    width = (nh + 2 * nkv) * hd if write_kv else nh * hd
+    if qkv.shape[0] != B or qkv.shape[1] < width:
+        raise KernelError(f"attention decode: qkv shape {tuple(qkv.shape)} does not hold {B} rows of width {width}")
+    if cos_sin is not None:
+        _need(cos_sin, "rope table", torch.float32)
+        if cos_sin.shape[1:] != (hd // 2, 2):
+            raise KernelError(f"attention decode: table shape {tuple(cos_sin.shape)} does not fit head_dim {hd}")
+    if write_kv:
+        _need(dest, "cache rows", torch.int32, (B,))
+    _check(lib.jb_attention_bf16_decode_fused(
+        _ptr(qkv), qkv.shape[1], _ptr(cos_sin), _ptr(dest), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o),
+        _ptr(part_ml), _ptr(block_table), _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window),
+        ctypes.c_float(scale), int(n_splits), int(write_kv), _stream()), "attention_bf16_decode_fused", kernels=kernels)
 
 
 # -- tcgen05 prefill attention (head sizes 64 and 128, power-of-two groups) ------------------

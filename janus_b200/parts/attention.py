@@ -11,6 +11,7 @@ crates/janus-engine/src/compute/shaders/attention.wgsl:96-115,170-185
 from __future__ import annotations
 
 import math
+import os
 from typing import Optional
 
 import torch
@@ -18,6 +19,11 @@ import torch
 from ..kernels import ops
 from .base import KVSpec, Mixer, PartSpec, make_part, register_part
 from .linear import Linear
+
+
+# JANUS_FUSED_DECODE=0 keeps rotation and cache append in a kernel of their own for decode steps too
+_FUSED_DECODE = os.environ.get("JANUS_FUSED_DECODE", "1") != "0"
+_FUSED_DECODE_MAX_PAIRS = 148      # (sequence, kv head) pairs up to which the fused decode kernel is used
 
 
 class GQAttention(Mixer):
@@ -51,25 +57,46 @@ class GQAttention(Mixer):
         self.q_only = Linear(self.hidden_size, self.q_width, self.dtype, self.device)
         self.q_only.weight = self.qkv.weight[: self.q_width]
 
-    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
+    def scratch_to_clear(self, ctx, tokens: int, writes_cache: bool = True) -> Optional[torch.Tensor]:
+        """The q/k/v buffer, if this step's projection adds K slices into it (decode-sized
+        steps): the norm before this mixer clears it in the same launch."""
+        proj = self.qkv if writes_cache else self.q_only
+        if proj is None or not proj.meets_by_adds(tokens, torch.float32):
+            return None
+        qkv = ctx.workspace.get("qkv", (tokens, proj.out_features), torch.float32)
+        return qkv if qkv.numel() % 4 == 0 else None
+
+    def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True,
+                scratch_cleared: bool = False) -> None:
         T = x.shape[0]
         ws = ctx.workspace
         proj = self.qkv if writes_cache else self.q_only
         # the projection's float32 accumulators go straight into the rotation
         qkv = ws.get("qkv", (T, proj.out_features), torch.float32)
-        proj.forward(x, qkv)
-        q = ws.get("q_rot", (T, self.q_width), self.dtype)
+        proj.forward(x, qkv, y_is_zero=scratch_cleared)
         table = self.position.fused_rotary_table() if self.position is not None else None
-        if self.position is not None and table is None:
+        custom_positions = self.position is not None and table is None
+        if custom_positions:
             self.position.apply(qkv[:, : self.q_width], self.nh, self.hd, ctx.positions)
             if writes_cache:
                 self.position.apply(qkv[:, self.q_width: self.q_width + self.kv_width], self.nkv, self.hd,
                                     ctx.positions)
         group = cache_view.group
+        attn = ws.get("attn_out", (T, self.q_width), self.dtype)
+        if (ctx.is_decode and self.dtype == torch.bfloat16 and _FUSED_DECODE and not custom_positions
+                and ctx.n_seqs * self.nkv <= _FUSED_DECODE_MAX_PAIRS):
+            # a few sequences, one token each: rotation and cache append happen inside the attention
+            # kernel (one launch less; with many sequences the rotation kernel of its own is faster)
+            ops.attention_bf16_decode(None, cache_view.k, cache_view.v, attn, group.block_table, ctx.kv_len,
+                                      self.nh, self.nkv, self.hd, group.page_size, self.window, self.scale,
+                                      ctx.workspace, ctx.max_kv_len_bound, qkv=qkv, cos_sin=table,
+                                      dest=group.dest_rows if writes_cache else None, write_kv=writes_cache)
+            self.o.forward_add(attn, residual)
+            return
+        q = ws.get("q_rot", (T, self.q_width), self.dtype)
         ops.rope_cache_write(qkv, q, table, ctx.positions, group.dest_rows if writes_cache else None,
                              cache_view.k if writes_cache else None, cache_view.v if writes_cache else None,
                              self.nh, self.nkv, self.hd, group.page_size, write_kv=writes_cache)
-        attn = ws.get("attn_out", (T, self.q_width), self.dtype)
         if self.dtype == torch.float32:
             ops.attention_f32(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.token_seq,
                               ctx.positions, self.nh, self.nkv, self.hd, group.page_size, self.window,

@@ -17,8 +17,15 @@ class PreNormBlock:
 
     def forward(self, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
         x = ctx.workspace.get("normed", (residual.shape[0], self.hidden_size), self.dtype)
-        self.mixer_norm.forward(residual, x)
-        self.mixer.forward(x, residual, ctx, cache_view, writes_cache)
+        # a mixer may name a scratch buffer that it wants zeroed; the norm before it does that in passing
+        wants = getattr(self.mixer, "scratch_to_clear", None)
+        scratch = wants(ctx, residual.shape[0], writes_cache) if wants is not None else None
+        if scratch is not None:
+            self.mixer_norm.forward(residual, x, clear=scratch)
+            self.mixer.forward(x, residual, ctx, cache_view, writes_cache, scratch_cleared=True)
+        else:
+            self.mixer_norm.forward(residual, x)
+            self.mixer.forward(x, residual, ctx, cache_view, writes_cache)
         self.feed_forward_norm.forward(residual, x)
         self.feed_forward.forward(x, residual, ctx)
 

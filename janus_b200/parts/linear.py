@@ -40,13 +40,21 @@ class Linear:
         """Use another product's storage (a head tied to the embedding)."""
         self.weight = other.weight
 
+    def meets_by_adds(self, tokens: int, y_dtype: torch.dtype) -> bool:
+        """Whether `forward` into a float32 `y` for this many tokens cuts K into slices that
+        meet in `y` by atomic adds, so that `y` has to be zero beforehand."""
+        return (self.dtype != torch.float32 and y_dtype == torch.float32
+                and ops.split_k_for(tokens, self.out_features, self.in_features) > 1)
+
     # y = x W^T, stored in y's dtype (engine dtype, or float32 for logits)
-    def forward(self, x: torch.Tensor, y: torch.Tensor) -> None:
+    def forward(self, x: torch.Tensor, y: torch.Tensor, y_is_zero: bool = False) -> None:
         if self.dtype == torch.float32:
             ops.gemm_f32(x, self.weight, y, accumulate=False)
-        elif y.dtype == torch.float32 and ops.split_k_for(x.shape[0], self.out_features, self.in_features) > 1:
+        elif self.meets_by_adds(x.shape[0], y.dtype):
             # few tokens and few output tiles: slices of K run as CTAs of their own and meet in y
-            if y.numel() % 4 == 0 and y.data_ptr() % 16 == 0:
+            if y_is_zero:
+                pass
+            elif y.numel() % 4 == 0 and y.data_ptr() % 16 == 0:
                 ops.zero_f32(y)
             else:
                 y.zero_()

@@ -28,8 +28,10 @@ class RMSNorm(Norm):
             gamma = gamma.to(torch.float32)
         self.gamma = gamma.to(self.device).contiguous()
 
-    def forward(self, x: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None) -> None:
-        ops.rmsnorm(x, self.gamma, self.eps, out, row_index)
+    def forward(self, x: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None,
+                clear: Optional[torch.Tensor] = None) -> None:
+        """`clear`: a float32 scratch tensor of the part that runs next, set to zero by the same launch."""
+        ops.rmsnorm(x, self.gamma, self.eps, out, row_index, clear)
 
 
 register_part("norm", "rms_norm", RMSNorm)

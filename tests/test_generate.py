@@ -113,6 +113,27 @@ def test_temperature_sampling_is_seeded_and_independent_of_the_batch(tmp_path, d
                 assert probs[tok] > 0
 
 
+def test_command_line(tmp_path):
+    """`<model_dir> "<prompt>" --max-tokens N --temperature T`, as the reference's examples take them."""
+    import json
+    import os
+    import subprocess
+    import sys
+    from helpers import ROOT
+    d = make_model_dir(TINY["A"], str(tmp_path / "m"), seed=3, dtype="float32")
+    cfg, w = P.read_model_dir(d)
+    prompts = [random_tokens(6, 256, 1), random_tokens(3, 256, 2), random_tokens(9, 256, 3)]
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "janus_b200"), d] + [",".join(map(str, p)) for p in prompts] + \
+          ["--max-tokens", "5", "--batch-size", "2", "--temperature", "0.0", "--dtype", "float32", "--ignore-eos", "--json"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    got = json.loads(res.stdout.strip().splitlines()[-1])
+    assert got["tokens"] == [P.generate(cfg, w, p, 5) for p in prompts]
+    assert got["finish_reasons"] == ["length"] * 3
+    bad = subprocess.run(cmd[:3] + ["1,x,3"], capture_output=True, text=True, timeout=120)
+    assert bad.returncode != 0 and "token ids" in (bad.stderr + bad.stdout)
+
+
 def test_errors_before_launch(tmp_path):
     from janus_b200.cache import CacheFull
     from janus_b200.engine import StepEntry, StepError

@@ -238,6 +238,39 @@ def test_attention_bf16_decode(ops, nh, nkv, hd, window, n_splits):
     close(out, plain_attention_rows(qs, ks, vs, q_lens, window), 1.5e-2)
 
 
+@pytest.mark.parametrize("nh, nkv, hd, window, rotate", [(4, 2, 16, 0, True), (3, 1, 40, 0, True), (32, 8, 128, 0, True),
+                                                         (5, 5, 72, 70, False), (40, 2, 32, 0, True)])
+def test_attention_bf16_decode_with_fused_rotation_and_append(ops, nh, nkv, hd, window, rotate):
+    """The decode kernel fed with the projection's float32 q/k/v (it rotates, appends to the cache
+    and attends) against the two-kernel path: rotate + append, then attend."""
+    lens = [130, 5, 64, 1, 700, 65, 128]
+    B = len(lens)
+    _, ks, vs = attention_case(nh, nkv, hd, lens, [1] * B, torch.bfloat16, seed=2, spike=False)
+    kc, vc, bt = paged(ks, vs, torch.bfloat16, seed=2)
+    g = torch.Generator().manual_seed(5)
+    qkv = torch.randn(B, (nh + 2 * nkv) * hd, generator=g).to(DEV)
+    kv_len = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    positions = kv_len - 1
+    dest = torch.stack([bt[i, (n - 1) // PAGE] * PAGE + (n - 1) % PAGE for i, n in enumerate(lens)]).to(torch.int32)
+    table = None
+    if rotate:
+        cos, sin = P.rope_cos_sin(torch.arange(800), P.rope_inv_freq(hd, 10000.0, None))
+        table = torch.stack([cos, sin], -1).contiguous().to(DEV)
+    scale = 1 / math.sqrt(hd)
+    for n_splits in (1, 3):
+        k1, v1, k2, v2 = kc.clone(), vc.clone(), kc.clone(), vc.clone()
+        q = torch.empty(B, nh * hd, device=DEV, dtype=torch.bfloat16)
+        ops.rope_cache_write(qkv, q, table, positions, dest, k1, v1, nh, nkv, hd, PAGE)
+        want = torch.empty_like(q)
+        ops.attention_bf16_decode(q, k1, v1, want, bt, kv_len, nh, nkv, hd, PAGE, window, scale, _WS(), max(lens),
+                                  n_splits=n_splits)
+        got = torch.full_like(q, float("nan"))
+        ops.attention_bf16_decode(None, k2, v2, got, bt, kv_len, nh, nkv, hd, PAGE, window, scale, _WS(), max(lens),
+                                  n_splits=n_splits, qkv=qkv, cos_sin=table, dest=dest)
+        assert torch.equal(k1, k2) and torch.equal(v1, v2)          # the same rows were appended
+        close(got, want.float(), 4e-3)
+
+
 # ---------------------------------------------------------------- tensor-core product
 def bf16_inputs(T, N, K, seed):
     g = torch.Generator().manual_seed(seed)

@@ -102,6 +102,53 @@ def test_schedule_is_data(tmp_path, dtype):
         assert rel_err(torch.cat([first, rest]), ref) < tol_for(dtype)
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_layers_with_and_without_a_window_have_storage_of_their_own(tmp_path, dtype):
+    """Layer 0 keeps all keys, layers 1 and 2 only the last 70: two cache groups; the window
+    group gives back the pages its queries have passed, and the logits match the plain model
+    at the window's edge, for a prompt cut into steps and decoded past several pages."""
+    from dataclasses import replace
+    from janus_b200.config import LlamaConfig
+    from janus_b200.engine import DecoderModel, Engine, EngineOptions, StepEntry
+    from janus_b200.models.llama import llama_spec
+    from janus_b200.parts import PartSpec
+    from janus_b200.weights import FolderCheckpoint
+
+    window = 70
+    d = make_model_dir(TINY["B"], str(tmp_path / "m"), seed=5, dtype=dtype)
+    cfg, w = P.read_model_dir(d)
+    tdt = torch.float32 if dtype == "float32" else torch.bfloat16
+    base = llama_spec(LlamaConfig.from_dict(TINY["B"]))
+    layers = [base.layers[0]] + [
+        replace(l, mixer=PartSpec(l.mixer.kind, dict(l.mixer.params, window=window), l.mixer.weights))
+        for l in base.layers[1:]]
+    m = DecoderModel(replace(base, layers=tuple(layers)), tdt, torch.device(DEV))
+    m.load(FolderCheckpoint(d))
+    eng = Engine(m, EngineOptions(max_tokens=512, use_graphs=(dtype == "bfloat16")))
+    assert len(eng.cache.groups) == 2 and sorted(g.spec.window for g in eng.cache.groups) == [0, window]
+    ids = random_tokens(230, cfg["vocab_size"], 6)
+
+    def plain(ids):      # the plain model with a window on layers 1 and 2
+        x = P.embed(w["model.embed_tokens.weight"], torch.tensor(ids))
+        pos = torch.arange(len(ids))
+        for layer in range(3):
+            x, _ = P.decoder_block(x, pos, cfg, w, layer, window=None if layer == 0 else window)
+        z = P.rms_norm(x, w["model.norm.weight"], P.cfg_get(cfg, "rms_norm_eps"))
+        return P.linear(z, P.lm_head_weight(cfg, w))
+
+    ref = plain(ids)
+    s = eng.alloc_slot()
+    got = [eng.step([StepEntry(s, ids[:100], range(100))]).cpu(), eng.step([StepEntry(s, ids[100:150], range(50))]).cpu()]
+    got += [eng.step([StepEntry(s, [t], [0])]).cpu() for t in ids[150:]]
+    assert rel_err(torch.cat(got), ref) < tol_for(dtype)
+    full, win = sorted(eng.cache.groups, key=lambda g: g.spec.window)
+    assert full.pool.n_held == 4 and win.pool.n_held <= 3           # 230 tokens: 4 pages; a window of 70 spans at most 3
+    assert win.pages[s][0] == -1 and win.pages[s][1] == -1
+    eng.free_slot(s)
+    eng.cache.check()
+    assert full.pool.n_held == 0 and win.pool.n_held == 0
+
+
 class RunningMeanMixer:
     """Toy mixer with fixed-size state: out_t = scale * mean(x_0 .. x_t) over the
     sequence so far.  State per sequence: the running sum (H floats) and the count."""
