@@ -214,6 +214,16 @@ def split_k_for(T: int, N: int, K: int) -> int:
     return max(1, min(SM_COUNT_TARGET // max(tiles, 1), k_tiles // 4))
 
 
+def _gemm_defines():
+    """Build-time overrides of the product kernel's tuning macros for experiments, e.g.
+    JANUS_GEMM_DEFINES="JB_RING_KB=104,JB_MAX_STAGES=6"; none by default."""
+    import os
+    text = os.environ.get("JANUS_GEMM_DEFINES", "")
+    if not text:
+        return None
+    return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "store",
               split_k: Optional[int] = None) -> None:
     """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation.
@@ -243,7 +253,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "st
         raise KernelError(f"gemm {mode}: output must be {want} [{T}, {N}], got {y.dtype} {tuple(y.shape)}")
     if split_k is None:
         split_k = split_k_for(T, N, K) if code == 2 else 1
-    _check(library("gemm_bf16_tc").jb_gemm_bf16(
+    _check(library("gemm_bf16_tc", _gemm_defines()).jb_gemm_bf16(
         _ptr(x), _ptr(w), _ptr(y), T, N, K, N, code, int(split_k), _ptr(kernel_status(x.device)), _stream()),
         "gemm_bf16")
 
