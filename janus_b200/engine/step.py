@@ -24,6 +24,7 @@ from .workspace import Workspace
 
 
 FROM_DEVICE = -1   # as a decode step's token: "the token the step before sampled for this slot"
+MAX_DECODE_GRAPHS = 48   # captured decode steps kept per engine (one per batch size, page capacity and sampler)
 
 
 class StepError(ValueError):
@@ -317,6 +318,8 @@ class Engine:
                 if gc_was_on:
                     gc.enable()
             rec.graph, rec.launches = graph, ops.launch_count() - before
+            while len(self._graphs) >= MAX_DECODE_GRAPHS:      # each holds a logits buffer: keep the newest
+                del self._graphs[next(iter(self._graphs))]
             self._graphs[key] = rec
             # the eager run and the capture wrote this step's keys already; the
             # replay below writes the same values again
