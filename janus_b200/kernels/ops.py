@@ -5,6 +5,7 @@ a non-zero return.  Nothing here computes; there is no other code path.
 from __future__ import annotations
 
 import ctypes
+import os
 from typing import Optional
 
 import torch
@@ -200,7 +201,7 @@ def check_kernel_status(device: torch.device) -> None:
     code = int(kernel_status(device).item())
     if code != 0:
         kernel_status(device).zero_()
-        who = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code, "?")
+        who = {1: "TMA producer", 2: "MMA issuer", 3: "epilogue"}.get(code % 10, "?")
         raise KernelError(f"a tensor-core kernel timed out waiting on an mbarrier ({who}, code {code})")
 
 
@@ -224,8 +225,21 @@ def _gemm_defines():
     return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
 
 
+# token counts from which the CTA-pair kernel (cta_group::2, 256-row weight tiles) runs the product;
+# JANUS_GEMM_PAIR=0 keeps every product on the single-CTA kernel
+GEMM_PAIR_MIN_TOKENS = int(os.environ.get("JANUS_GEMM_PAIR_MIN_TOKENS", "512"))
+_GEMM_PAIR = os.environ.get("JANUS_GEMM_PAIR", "1") != "0"
+
+
+def _pair_defines():
+    text = os.environ.get("JANUS_GEMM_PAIR_DEFINES", "")
+    if not text:
+        return None
+    return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
+
+
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "store",
-              split_k: Optional[int] = None) -> None:
+              split_k: Optional[int] = None, pair: Optional[bool] = None) -> None:
     """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation.
     mode "store": y[T, N] = result (bf16 or float32 by y's dtype);
     mode "add":   y[T, N] += result, y float32 (K may be split, sums meet by atomic adds);
@@ -251,6 +265,13 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "st
             raise KernelError(f"gemm: unknown mode {mode!r}")
     if y.dtype != want or tuple(y.shape) != (T, N):
         raise KernelError(f"gemm {mode}: output must be {want} [{T}, {N}], got {y.dtype} {tuple(y.shape)}")
+    if pair is None:
+        pair = _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS and split_k in (None, 1)
+    if pair:
+        _check(library("gemm_bf16_tc2", _pair_defines()).jb_gemm_bf16_pair(
+            _ptr(x), _ptr(w), _ptr(y), T, N, K, N, code, _ptr(kernel_status(x.device)), _stream()),
+            "gemm_bf16_pair")
+        return
     if split_k is None:
         split_k = split_k_for(T, N, K) if code == 2 else 1
     _check(library("gemm_bf16_tc", _gemm_defines()).jb_gemm_bf16(

@@ -310,6 +310,38 @@ def test_gemm_bf16_swiglu(ops, T, I, K):
     ops.check_kernel_status(torch.device(DEV))
 
 
+@pytest.mark.parametrize("T", [256, 300, 513, 1100])
+@pytest.mark.parametrize("N, K", [(200, 120), (256, 64), (1000, 320), (640, 4096)])
+def test_gemm_bf16_cta_pairs(ops, T, N, K):
+    """The cta_group::2 kernel (256 weight rows per CTA pair, each CTA loads half of the token tile):
+    ragged token counts, widths that are no multiple of 256, a K tail, several tiles per pair."""
+    x, w = bf16_inputs(T, N, K, T + N + 1)
+    ref = x.double().cpu() @ w.double().cpu().T
+    y16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, y16, pair=True)
+    close(y16, ref, 6e-3)
+    y32 = torch.full((T, N), float("nan"), device=DEV)
+    ops.gemm_bf16(x, w, y32, pair=True)
+    close(y32, ref, 2e-5)
+    base = torch.randn(T, N, device=DEV)
+    acc = base.clone()
+    ops.gemm_bf16(x, w, acc, mode="add", pair=True)
+    close(acc, ref + base.double().cpu(), 2e-5)
+    ops.check_kernel_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("T", [256, 700])
+@pytest.mark.parametrize("I, K", [(192, 64), (320, 96), (1000, 2048)])
+def test_gemm_bf16_cta_pairs_swiglu(ops, T, I, K):
+    x, w = bf16_inputs(T, 2 * I, K, T + I + 1)
+    w = (w.float() * 3).to(torch.bfloat16)
+    y = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_bf16(x, w, y, mode="swiglu", pair=True)
+    ref = P.swiglu_ffn(x.double().cpu(), w[:I].double().cpu(), w[I:].double().cpu(), torch.eye(I, dtype=torch.float64))
+    close(y, ref, 6e-3)
+    ops.check_kernel_status(torch.device(DEV))
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take(ops):
     x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
     w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)

@@ -3,7 +3,8 @@
 plain implementation, in float32 and in bfloat16: a prompt in one step, the rest
 token by token across page boundaries, and two sequences of unequal length in
 one batch.  The product path's tile sizes, split-K and key splits are those of
-the full model, which the tiny configurations never reach."""
+the full model, which the tiny configurations never reach; a prompt of 600
+tokens runs the products that work in CTA pairs."""
 import numpy as np
 import pytest
 import torch
@@ -26,7 +27,7 @@ BIG_LAYER = dict(
 def big_model(tmp_path_factory):
     d = make_model_dir(BIG_LAYER, str(tmp_path_factory.mktemp("big") / "m"), seed=11, dtype="bfloat16", sharpen=1.5)
     cfg, w = P.read_model_dir(d)
-    ids = [random_tokens(n, BIG_LAYER["vocab_size"], 70 + n) for n in (330, 150)]
+    ids = [random_tokens(n, BIG_LAYER["vocab_size"], 70 + n) for n in (330, 150, 600)]
     ref = [P.forward(cfg, w, x).numpy() for x in ids]
     return d, ids, ref
 
@@ -62,4 +63,17 @@ def test_one_big_layer_matches_plain(big_model, dtype):
     first = model.step([StepEntry(c, ids[1][:64], [63])]).cpu().numpy()
     rest = model.step([StepEntry(c, ids[1][64:], range(86))]).cpu().numpy()
     assert rel_err(first, ref[1][63:64]) < tol and rel_err(rest, ref[1][64:]) < tol
+    ops.check_kernel_status(model.device)
+
+
+def test_long_prompt_runs_the_pair_products(big_model):
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    from janus_b200.kernels import ops
+    d, ids, ref = big_model
+    assert len(ids[2]) >= ops.GEMM_PAIR_MIN_TOKENS
+    model = janus_b200.load(d, dtype="bfloat16", max_tokens=1024)
+    a = model.alloc_slot()
+    out = model.step([StepEntry(a, ids[2], range(600))]).cpu().numpy()
+    assert rel_err(out, ref[2]) < tol_for("bfloat16")
     ops.check_kernel_status(model.device)
