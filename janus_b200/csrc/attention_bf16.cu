@@ -325,9 +325,10 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int kb_first = lo / PAGE, kb_last = pos / PAGE;
   const int n_blocks = kb_last - kb_first + 1;
-  const int per = (n_blocks + n_splits - 1) / n_splits;
-  const int kb_start = kb_first + split * per;
-  const int kb_end = min(kb_last, kb_start + per - 1);
+  // the pages are cut evenly: split s walks pages [s n / S, (s + 1) n / S), so that no split is left
+  // without pages while another walks a rounded-up share
+  const int kb_start = kb_first + (int)(((long long)split * n_blocks) / n_splits);
+  const int kb_end = kb_first + (int)(((long long)(split + 1) * n_blocks) / n_splits) - 1;
   const int* pages = block_table + (size_t)seq * max_pages;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
