@@ -312,7 +312,6 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
     int window, float scale_log2, int n_splits, FusedInput fused) {
   extern __shared__ __align__(16) uint8_t smem_raw[];
   jb::pdl_launch_dependents();
-  jb::pdl_wait();
   bf16* q_s = reinterpret_cast<bf16*>(smem_raw);  // [16][LD]
   bf16* new_kv = q_s + 16 * LD;                   // [2][LD]: the new token's rotated key and its value (fused input)
   bf16* kv_s = new_kv + 2 * LD;                   // [DECODE_STAGES][K, V][64][LD]; reused as float scratch at the end
@@ -334,28 +333,40 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
 
   RowState st;
   st.init();
-  if (kb_start <= kb_end) {
-    zero_pad_columns(q_s, 16 + 2 + 2 * DECODE_STAGES * PAGE);
-    const bool patch_new = fused.qkv != nullptr && fused.write_kv && kb_end == kb_last;  // this CTA sees the new key
-    if (fused.qkv == nullptr) {
-      for (int ch = threadIdx.x; ch < 16 * CHUNKS; ch += THREADS) {
-        const int r = ch / CHUNKS, col = ch % CHUNKS;
-        const bool valid = r < n_rows;
-        const bf16* src = q + ((size_t)seq * nh + kvh * G + g0 + (valid ? r : 0)) * HD + col * 8;
-        cp_async16(q_s + r * LD + col * 8, src, valid);
-      }
-    }
-    auto issue = [&](int kb, int stage) {
-      const size_t page = (size_t)pages[kb];
-      const size_t off = (page * nkv + kvh) * PAGE * HD;
-      load_page(kv_s + (size_t)stage * 2 * KV_TILE, k_cache + off);
-      load_page(kv_s + (size_t)stage * 2 * KV_TILE + KV_TILE, v_cache + off);
-    };
-    // ring of DECODE_STAGES pages: DECODE_STAGES - 1 loads are in flight while one page is computed
+  // The lengths, the block table and the cached pages were written before this step's kernels began, so
+  // the first pages are asked for BEFORE the wait on the kernel that produces q: their latency hides
+  // behind that kernel's end.  The one page that may be written in this step (the last one, which takes
+  // the new token from the kernel before this one, unless this kernel appends it itself) waits.
+  const bool appends_here = fused.qkv != nullptr && fused.write_kv;
+  const bool early = appends_here || kb_start + DECODE_STAGES - 2 < kb_last;
+  auto issue = [&](int kb, int stage) {
+    const size_t page = (size_t)pages[kb];
+    const size_t off = (page * nkv + kvh) * PAGE * HD;
+    load_page(kv_s + (size_t)stage * 2 * KV_TILE, k_cache + off);
+    load_page(kv_s + (size_t)stage * 2 * KV_TILE + KV_TILE, v_cache + off);
+  };
+  // ring of DECODE_STAGES pages: DECODE_STAGES - 1 loads are in flight while one page is computed
+  auto issue_first_pages = [&]() {
 #pragma unroll
     for (int s = 0; s < DECODE_STAGES - 1; ++s) {
       if (kb_start + s <= kb_end) issue(kb_start + s, s);
       cp_async_commit();  // a group per stage, empty or not, keeps the group count in step with the pages
+    }
+  };
+  if (kb_start <= kb_end && early) issue_first_pages();
+  jb::pdl_wait();
+  if (kb_start <= kb_end) {
+    zero_pad_columns(q_s, 16 + 2 + 2 * DECODE_STAGES * PAGE);
+    const bool patch_new = appends_here && kb_end == kb_last;  // this CTA sees the new key
+    if (!early) issue_first_pages();
+    if (fused.qkv == nullptr) {
+      // rotated queries of the kernel before: plain loads, visible after the loop's first barrier
+      for (int ch = threadIdx.x; ch < 16 * CHUNKS; ch += THREADS) {
+        const int r = ch / CHUNKS, col = ch % CHUNKS;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < n_rows) v = *reinterpret_cast<const uint4*>(q + ((size_t)seq * nh + kvh * G + g0 + r) * HD + col * 8);
+        *reinterpret_cast<uint4*>(q_s + r * LD + col * 8) = v;
+      }
     }
     if (fused.qkv != nullptr) {
       // (after the first page loads are in flight, so that the rotation hides behind them)
