@@ -16,6 +16,9 @@
 // the 256 columns are 128 gate rows of the weight (loaded by the first CTA) beside the 128 up rows of the
 // same features (loaded by the second), so one MMA per k-step computes both and a thread of the epilogue
 // finds gate and up of a feature in two columns of its own TMEM lane.
+// The stacked q/k/v projection of a prompt lies the same way (tokens on the rows, 256 features = whole heads
+// on the columns): its epilogue rotates q and k by the token's position and writes q as bfloat16 and k, v
+// straight into the paged cache, so the projection's float32 output never goes to memory.
 // The kernel is persistent (pair p computes tiles p, p + pairs, ...) with two accumulator buffers.
 // Every mbarrier wait is bounded in time (status codes 21-23).  No TMA load uses multicast.
 #include <cuda.h>
@@ -31,7 +34,7 @@ constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair's first CTA
 
-enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3 };
+enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3, QKV_ROPE = 4 };
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -144,7 +147,19 @@ constexpr int TMEM_COLS = 512;    // two accumulator buffers
 #endif
 constexpr int STAGES = JB_PAIR_STAGES;   // 32 KB each
 
-// A tile is 256 features x 256 tokens, or for the gated product 256 tokens x 128 features.
+// Where the q/k/v epilogue writes: rotated queries, and keys and values at their cache rows.
+struct RopeOut {
+  __nv_bfloat16* q_out;      // [T, nh * hd]
+  __nv_bfloat16* k_cache;    // [pages, nkv, page_size, hd]
+  __nv_bfloat16* v_cache;
+  const float* cos_sin;      // [positions, hd / 2, 2]
+  const int* positions;      // [T]
+  const int* dest;           // [T] cache row of each token: page * page_size + row
+  int nh, nkv, hd, page_size;
+};
+
+// A tile is 256 features x 256 tokens; tokens on the rows: 256 tokens x 128 (gated) or 256 (q/k/v) features.
+__host__ __device__ constexpr bool tokens_on_rows(int mode) { return mode == SWIGLU || mode == QKV_ROPE; }
 struct TileCoord {
   int t0, f0;
 };
@@ -160,7 +175,7 @@ template <int MODE>
 __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w,
                                                            const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                            int T, int N_out, int ldy, int k_tiles, int n_tiles,
-                                                           int n_tok_tiles, int up_row_offset, int* __restrict__ status) {
+                                                           int n_tok_tiles, int up_row_offset, RopeOut rope, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -207,6 +222,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles);
         // rows of this CTA's two loads: its 128 rows of the pair's M side, its half of the column operand
         const int w_row = MODE == SWIGLU ? (rank ? up_row_offset + tc.f0 : tc.f0) : tc.f0 + (int)rank * BM;
+        constexpr bool TOK_ROWS = tokens_on_rows(MODE);
         const int x_row = tc.t0 + (int)rank * BM;
         for (int i = 0; i < k_tiles; ++i, ++it) {
           const int s = it % STAGES;
@@ -215,8 +231,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
           const uint32_t bar = (full0 + 8 * s) & PEER_MASK;   // the first CTA's barrier collects both CTAs' bytes
           mbar_expect_tx_cluster(bar, STAGE_BYTES);
           const int kx = i * BK;
-          tma_load_2d_pair(stage, MODE == SWIGLU ? &map_x : &map_w, bar, kx, MODE == SWIGLU ? x_row : w_row);
-          tma_load_2d_pair(stage + A_BYTES, MODE == SWIGLU ? &map_w : &map_x, bar, kx, MODE == SWIGLU ? w_row : x_row);
+          tma_load_2d_pair(stage, TOK_ROWS ? &map_x : &map_w, bar, kx, TOK_ROWS ? x_row : w_row);
+          tma_load_2d_pair(stage + A_BYTES, TOK_ROWS ? &map_w : &map_x, bar, kx, TOK_ROWS ? w_row : x_row);
         }
       }
     }
@@ -290,6 +306,64 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
               for (int jj = 0; jj < 16; ++jj)
                 if (f + jj < N_out)
                   yrow[f + jj] = __ushort_as_bfloat16((unsigned short)(packed[jj / 2] >> (16 * (jj & 1))));
+            }
+          }
+        }
+      } else if (MODE == QKV_ROPE) {
+        // this lane is a token; the 256 columns are whole heads of q, k or v
+        const int t = tc.t0 + (int)rank * BM + quarter * 32 + lane;
+        const bool t_ok = t < T;
+        const int hd = rope.hd, half = hd >> 1;
+        const int pos = t_ok ? rope.positions[t] : 0;
+        const int dst = t_ok ? rope.dest[t] : 0;
+        const float* cs = rope.cos_sin + (size_t)pos * hd;
+#pragma unroll 1
+        for (int c = 0; c < BN; c += hd) {
+          const int f = tc.f0 + c;
+          if (f >= N_out) break;
+          const int head = f / hd;
+          __nv_bfloat16* out;
+          const bool rotate = head < rope.nh + rope.nkv;
+          if (head < rope.nh) {
+            out = rope.q_out + ((size_t)t * rope.nh + head) * hd;
+          } else {
+            const int kvh = (head - rope.nh) % rope.nkv;
+            __nv_bfloat16* base = head < rope.nh + rope.nkv ? rope.k_cache : rope.v_cache;
+            out = base + (((size_t)(dst / rope.page_size) * rope.nkv + kvh) * rope.page_size + dst % rope.page_size) * hd;
+          }
+#pragma unroll 1
+          for (int i = 0; i < half; i += 16) {
+            uint32_t lo[16], hi[16];
+            tmem_ld16(lane_base + c + i, lo);
+            tmem_ld16(lane_base + c + half + i, hi);
+            tmem_ld_wait();
+            if (t_ok) {
+              uint32_t plo[8], phi[8];
+#pragma unroll
+              for (int jj = 0; jj < 16; jj += 2) {
+                float y0[2], y1[2];
+#pragma unroll
+                for (int e = 0; e < 2; ++e) {
+                  const float x0 = __uint_as_float(lo[jj + e]), x1 = __uint_as_float(hi[jj + e]);
+                  if (rotate) {
+                    const float2 k = *reinterpret_cast<const float2*>(cs + 2 * (i + jj + e));   // (cos, sin)
+                    y0[e] = x0 * k.x - x1 * k.y;
+                    y1[e] = x0 * k.y + x1 * k.x;
+                  } else {
+                    y0[e] = x0;
+                    y1[e] = x1;
+                  }
+                }
+                const __nv_bfloat162 a = __floats2bfloat162_rn(y0[0], y0[1]), b = __floats2bfloat162_rn(y1[0], y1[1]);
+                plo[jj / 2] = *(const uint32_t*)&a;
+                phi[jj / 2] = *(const uint32_t*)&b;
+              }
+              uint4* d0 = (uint4*)(out + i);
+              uint4* d1 = (uint4*)(out + half + i);
+              d0[0] = make_uint4(plo[0], plo[1], plo[2], plo[3]);
+              d0[1] = make_uint4(plo[4], plo[5], plo[6], plo[7]);
+              d1[0] = make_uint4(phi[0], phi[1], phi[2], phi[3]);
+              d1[1] = make_uint4(phi[4], phi[5], phi[6], phi[7]);
             }
           }
         }
@@ -375,7 +449,8 @@ int sm_count() {
 }
 
 template <int MODE>
-int launch(const void* X, const void* W, void* Y, int T, int N_out, int K, int ldy, int* status, cudaStream_t stream) {
+int launch(const void* X, const void* W, void* Y, int T, int N_out, int K, int ldy, const RopeOut& rope, int* status,
+           cudaStream_t stream) {
   constexpr int smem = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -410,7 +485,7 @@ int launch(const void* X, const void* W, void* Y, int T, int N_out, int K, int l
     cfg.numAttrs = 2;
   }
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, Y, T, N_out, ldy, k_tiles, n_tiles,
-                                 n_tok_tiles, MODE == SWIGLU ? N_out : 0, status);
+                                 n_tok_tiles, MODE == SWIGLU ? N_out : 0, rope, status);
 }
 
 }  // namespace
@@ -423,10 +498,28 @@ JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, void* Y, int T, in
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16_pair: operands must be 16-byte aligned");
   switch (mode) {
-    case STORE_BF16: return launch<STORE_BF16>(X, W, Y, T, N_out, K, ldy, status, stream);
-    case STORE_F32: return launch<STORE_F32>(X, W, Y, T, N_out, K, ldy, status, stream);
-    case ADD_F32: return launch<ADD_F32>(X, W, Y, T, N_out, K, ldy, status, stream);
-    case SWIGLU: return launch<SWIGLU>(X, W, Y, T, N_out, K, ldy, status, stream);
+    case STORE_BF16: return launch<STORE_BF16>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case STORE_F32: return launch<STORE_F32>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case ADD_F32: return launch<ADD_F32>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case SWIGLU: return launch<SWIGLU>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     default: JB_REFUSE(true, "gemm_bf16_pair: unknown mode %d", mode);
   }
+}
+
+// The stacked q/k/v projection of prompt tokens with its consumers fused in: X [T, K] . W [(nh + 2 nkv) hd, K]^T,
+// q and k rotated by cos_sin[positions[t]] (pairs i, i + hd/2), q written to q_out [T, nh hd] and k, v to the
+// paged cache at row dest[t], all bfloat16.  hd must divide 256 and hd/2 be a multiple of 16 (32, 64, 128, 256).
+JB_EXPORT int jb_gemm_bf16_pair_qkv_rope(const void* X, const void* W, int T, int K, void* q_out, void* k_cache,
+                                         void* v_cache, const float* cos_sin, const int* positions, const int* dest,
+                                         int nh, int nkv, int hd, int page_size, int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair_qkv_rope: K = %d must be a positive multiple of 8", K);
+  JB_REFUSE(((uintptr_t)X | (uintptr_t)W | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 15,
+            "gemm_bf16_pair_qkv_rope: tensors must be 16-byte aligned");
+  JB_REFUSE(hd <= 0 || 256 % hd != 0 || (hd / 2) % 16 != 0,
+            "gemm_bf16_pair_qkv_rope: head_dim %d is not one of 32, 64, 128, 256", hd);
+  JB_REFUSE(nh <= 0 || nkv <= 0 || page_size <= 0 || !cos_sin || !positions || !dest, "gemm_bf16_pair_qkv_rope: bad arguments");
+  RopeOut rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, cos_sin, positions, dest,
+               nh, nkv, hd, page_size};
+  return launch<QKV_ROPE>(X, W, nullptr, T, (nh + 2 * nkv) * hd, K, 0, rope, status, stream);
 }

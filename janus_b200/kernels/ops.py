@@ -279,6 +279,39 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "st
         "gemm_bf16")
 
 
+def gemm_qkv_rope_supported(T: int, hd: int) -> bool:
+    """Whether the fused projection below takes this step: prompt-sized token counts and a head size that
+    divides the kernel's 256 columns with half-heads of whole 16-column loads."""
+    return _GEMM_PAIR and _QKV_FUSED and T >= GEMM_PAIR_MIN_TOKENS and hd in (32, 64, 128, 256)
+
+
+_QKV_FUSED = os.environ.get("JANUS_QKV_FUSED", "1") != "0"   # 0: projection, then rotation and cache append apart
+
+
+def gemm_qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: torch.Tensor,
+                        positions: torch.Tensor, dest: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                        nh: int, nkv: int, hd: int, page_size: int) -> None:
+    """The stacked q/k/v projection x[T, K] . w[(nh + 2 nkv) hd, K]^T on CTA pairs with its consumers fused
+    into the epilogue: q and k rotated by cos_sin[positions], q to q_out[T, nh hd], k and v to the paged
+    cache at rows dest, all bfloat16 from the float32 accumulators."""
+    T, K = x.shape
+    _need(x, "qkv x", torch.bfloat16)
+    _need(w, "qkv w", torch.bfloat16, ((nh + 2 * nkv) * hd, K))
+    _need(q_out, "q_out", torch.bfloat16, (T, nh * hd))
+    _need(cos_sin, "rope table", torch.float32)
+    if cos_sin.shape[1:] != (hd // 2, 2):
+        raise KernelError(f"qkv: table shape {tuple(cos_sin.shape)} does not fit head_dim {hd}")
+    _need(positions, "positions", torch.int32, (T,))
+    _need(dest, "cache rows", torch.int32, (T,))
+    _need(k_cache, "k cache", torch.bfloat16)
+    _need(v_cache, "v cache", torch.bfloat16)
+    if k_cache.shape[1:] != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
+        raise KernelError(f"qkv: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
+    _check(library("gemm_bf16_tc2", _pair_defines()).jb_gemm_bf16_pair_qkv_rope(
+        _ptr(x), _ptr(w), T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(cos_sin), _ptr(positions), _ptr(dest),
+        nh, nkv, hd, page_size, _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair_qkv_rope")
+
+
 # -- sampling -----------------------------------------------------------------------
 def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_k: int, top_p: float,
            repetition_penalty: float, counts: Optional[torch.Tensor], count_rows: Optional[torch.Tensor],

@@ -70,18 +70,26 @@ class GQAttention(Mixer):
                 scratch_cleared: bool = False) -> None:
         T = x.shape[0]
         ws = ctx.workspace
+        group = cache_view.group
+        table = self.position.fused_rotary_table() if self.position is not None else None
+        if (self.dtype == torch.bfloat16 and writes_cache and table is not None and not ctx.is_decode
+                and ops.gemm_qkv_rope_supported(T, self.hd)):
+            # a prompt: the projection's epilogue rotates q and k and appends k and v to the cache
+            q = ws.get("q_rot", (T, self.q_width), self.dtype)
+            ops.gemm_qkv_rope_cache(x, self.qkv.weight, q, table, ctx.positions, group.dest_rows, cache_view.k,
+                                    cache_view.v, self.nh, self.nkv, self.hd, group.page_size)
+            self._attend_prompt(q, residual, ctx, cache_view)
+            return
         proj = self.qkv if writes_cache else self.q_only
         # the projection's float32 accumulators go straight into the rotation
         qkv = ws.get("qkv", (T, proj.out_features), torch.float32)
         proj.forward(x, qkv, y_is_zero=scratch_cleared)
-        table = self.position.fused_rotary_table() if self.position is not None else None
         custom_positions = self.position is not None and table is None
         if custom_positions:
             self.position.apply(qkv[:, : self.q_width], self.nh, self.hd, ctx.positions)
             if writes_cache:
                 self.position.apply(qkv[:, self.q_width: self.q_width + self.kv_width], self.nkv, self.hd,
                                     ctx.positions)
-        group = cache_view.group
         attn = ws.get("attn_out", (T, self.q_width), self.dtype)
         if (ctx.is_decode and self.dtype == torch.bfloat16 and _FUSED_DECODE and not custom_positions
                 and ctx.n_seqs * self.nkv <= _FUSED_DECODE_MAX_PAIRS):
@@ -105,7 +113,16 @@ class GQAttention(Mixer):
             ops.attention_bf16_decode(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.kv_len,
                                       self.nh, self.nkv, self.hd, group.page_size, self.window, self.scale,
                                       ctx.workspace, ctx.max_kv_len_bound)
-        elif ops.attention_tc_supported(self.nh, self.nkv, self.hd):
+        else:
+            self._attend_prompt(q, residual, ctx, cache_view)
+            return
+        self.o.forward_add(attn, residual)
+
+    def _attend_prompt(self, q: torch.Tensor, residual: torch.Tensor, ctx, cache_view) -> None:
+        """bfloat16 attention of several new tokens per sequence over the cache, then the output projection."""
+        group = cache_view.group
+        attn = ctx.workspace.get("attn_out", (q.shape[0], self.q_width), self.dtype)
+        if ops.attention_tc_supported(self.nh, self.nkv, self.hd):
             # head sizes 64 / 128 and power-of-two groups: flash attention on the tcgen05 tensor cores
             ops.attention_tc_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start,
                                      ctx.kv_len, ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, self.hd,

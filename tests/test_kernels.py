@@ -342,6 +342,38 @@ def test_gemm_bf16_cta_pairs_swiglu(ops, T, I, K):
     ops.check_kernel_status(torch.device(DEV))
 
 
+@pytest.mark.parametrize("T", [256, 700])
+@pytest.mark.parametrize("nh, nkv, hd, K", [(3, 1, 128, 320), (6, 3, 64, 96), (5, 5, 32, 2048), (2, 1, 256, 64)])
+def test_gemm_qkv_with_rotation_and_cache_append(ops, T, nh, nkv, hd, K):
+    """The stacked q/k/v projection whose epilogue rotates q and k and writes k, v into the paged cache:
+    widths that are no multiple of the 256-column tile, tiles that hold q, k and v heads side by side."""
+    n_pages = (T + PAGE - 1) // PAGE + 3
+    x, w = bf16_inputs(T, (nh + 2 * nkv) * hd, K, T + hd)
+    positions = torch.randint(0, 900, (T,), device=DEV, dtype=torch.int32)
+    dest = torch.randperm(n_pages * PAGE, device=DEV)[:T].to(torch.int32)
+    inv = P.rope_inv_freq(hd, 50000.0, None)
+    cos, sin = P.rope_cos_sin(torch.arange(900), inv)
+    table = torch.stack([cos, sin], -1).contiguous().to(DEV)
+    kc = torch.zeros(n_pages, nkv, PAGE, hd, device=DEV, dtype=torch.bfloat16)
+    vc = torch.zeros_like(kc)
+    q = torch.full((T, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.gemm_qkv_rope_cache(x, w, q, table, positions, dest, kc, vc, nh, nkv, hd, PAGE)
+    ops.check_kernel_status(torch.device(DEV))
+    y = x.double().cpu() @ w.double().cpu().T
+    c, s_ = P.rope_cos_sin(positions.cpu(), inv)
+    q_ref = P.apply_rope(y[:, :nh * hd].view(T, nh, hd), c.double(), s_.double()).reshape(T, -1)
+    k_ref = P.apply_rope(y[:, nh * hd:(nh + nkv) * hd].view(T, nkv, hd), c.double(), s_.double())
+    v_ref = y[:, (nh + nkv) * hd:].view(T, nkv, hd)
+    close(q, q_ref, 6e-3)
+    page, row = (dest.cpu() // PAGE).long(), (dest.cpu() % PAGE).long()
+    close(kc.cpu()[page, :, row, :], k_ref, 6e-3)
+    close(vc.cpu()[page, :, row, :], v_ref, 6e-3)
+    untouched = torch.ones(n_pages * PAGE, dtype=torch.bool)
+    untouched[dest.cpu().long()] = False
+    for cache in (kc, vc):
+        assert float(cache.float().cpu().permute(0, 2, 1, 3).reshape(n_pages * PAGE, -1)[untouched].abs().sum()) == 0.0
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take(ops):
     x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
     w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)
