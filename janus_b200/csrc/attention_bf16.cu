@@ -339,11 +339,18 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   // the new token from the kernel before this one, unless this kernel appends it itself) waits.
   const bool appends_here = fused.qkv != nullptr && fused.write_kv;
   const bool early = appends_here || kb_start + DECODE_STAGES - 2 < kb_last;
+  // Every warp loads, waits for and computes ITS OWN 16 keys of each page, so the ring needs no barrier of
+  // the whole CTA: a warp asks for its rows of the page after next as soon as it is done with its rows of
+  // this one, whatever the other warps are doing.
   auto issue = [&](int kb, int stage) {
     const size_t page = (size_t)pages[kb];
-    const size_t off = (page * nkv + kvh) * PAGE * HD;
-    load_page(kv_s + (size_t)stage * 2 * KV_TILE, k_cache + off);
-    load_page(kv_s + (size_t)stage * 2 * KV_TILE + KV_TILE, v_cache + off);
+    const size_t off = ((page * nkv + kvh) * PAGE + warp * 16) * HD;
+    bf16* k_rows = kv_s + (size_t)stage * 2 * KV_TILE + warp * 16 * LD;
+    for (int ch = lane; ch < 16 * CHUNKS; ch += 32) {
+      const int row = ch / CHUNKS, col = ch % CHUNKS;
+      cp_async16(k_rows + row * LD + col * 8, k_cache + off + (size_t)row * HD + col * 8, true);
+      cp_async16(k_rows + KV_TILE + row * LD + col * 8, v_cache + off + (size_t)row * HD + col * 8, true);
+    }
   };
   // ring of DECODE_STAGES pages: DECODE_STAGES - 1 loads are in flight while one page is computed
   auto issue_first_pages = [&]() {
@@ -409,31 +416,34 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
       row_pos[r] = ((lane >> 2) + 8 * r) < n_rows ? pos : -1;
       row_lo[r] = lo;
     }
+    __syncthreads();  // q (and the new key and value) are in shared memory for every warp
     for (int kb = kb_start; kb <= kb_end; ++kb) {
       const int stage = (kb - kb_start) % DECODE_STAGES;
       if (kb + DECODE_STAGES - 1 <= kb_end)
         issue(kb + DECODE_STAGES - 1, (kb - kb_start + DECODE_STAGES - 1) % DECODE_STAGES);
       cp_async_commit();
       cp_async_wait<DECODE_STAGES - 1>();  // everything but the newest DECODE_STAGES - 1 groups: page kb has landed
-      __syncthreads();
+      __syncwarp();
       bf16* k_tile = kv_s + (size_t)stage * 2 * KV_TILE;
-      if (patch_new && kb == kb_last) {
-        // the page as loaded holds a stale row at the new position: put the new key and value there
+      if (patch_new && kb == kb_last && warp == (pos % PAGE) / 16) {
+        // the page as loaded holds a stale row at the new position: the warp that owns the row puts the
+        // new key and value there
         const int r = pos % PAGE;
-        for (int i = threadIdx.x; i < 2 * HD; i += THREADS) {
+        for (int i = lane; i < 2 * HD; i += 32) {
           const int which = i / HD, d = i % HD;
           k_tile[which * KV_TILE + r * LD + d] = new_kv[which * LD + d];
         }
-        __syncthreads();
+        __syncwarp();
       }
       // this warp's 16 keys of the page
       float s[2][4];
       qk_product<2>(s, q_s, k_tile + warp * 16 * LD, lane);
       softmax_pv<2>(st, s, k_tile + KV_TILE + warp * 16 * LD, kb * PAGE + warp * 16, row_pos, row_lo,
                     scale_log2, lane);
-      __syncthreads();
+      __syncwarp();  // the warp is done with its rows of this stage before its next loads overwrite them
     }
   }
+  __syncthreads();  // every warp has left the ring: its memory becomes the exchange buffer
   // ---- the four warps' partial results meet in shared memory ----
   float* red_o = reinterpret_cast<float*>(kv_s);           // [4][16][RED_LD]: padded rows, no 8-way bank conflicts
   float* red_ml = red_o + 4 * 16 * RED_LD;                  // [4][16][2]
