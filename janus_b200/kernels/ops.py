@@ -367,13 +367,13 @@ def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: 
     """Splits of the key range per (sequence, kv head).  The kernel runs two CTAs per SM; with fewer
     (sequence, kv head) pairs than such places the keys are cut so that one wave of CTAs fills them
     (at least about four pages of the longest sequence per split), and with more pairs than places
-    only long sequences are cut (32 pages per split).  Measured at 8 kv heads, 2,080 keys: 1 sequence
-    16 splits, 8 sequences 4, 64 sequences 2."""
+    only long sequences are cut (64 pages per split).  Measured at 8 kv heads, 2,080 keys: 1 sequence
+    16 splits, 8 sequences 4, 64 sequences 1."""
     pages = max(1, (max_kv_len + page_size - 1) // page_size)
     base = max(1, n_seqs * nkv_blocks)
     places = SM_COUNT_TARGET
     if base >= places:
-        return max(1, min(pages, pages // 32))
+        return max(1, min(pages, pages // 64))
     return max(1, min(places // base, max(1, pages // 4)))
 
 

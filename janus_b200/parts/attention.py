@@ -23,7 +23,7 @@ from .linear import Linear
 
 # JANUS_FUSED_DECODE=0 keeps rotation and cache append in a kernel of their own for decode steps too
 _FUSED_DECODE = os.environ.get("JANUS_FUSED_DECODE", "1") != "0"
-_FUSED_DECODE_MAX_PAIRS = 148      # (sequence, kv head) pairs up to which the fused decode kernel is used
+_FUSED_DECODE_MAX_PAIRS = int(os.environ.get("JANUS_FUSED_DECODE_MAX_PAIRS", "148"))      # (sequence, kv head) pairs up to which the fused decode kernel is used
 
 
 class GQAttention(Mixer):
