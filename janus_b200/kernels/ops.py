@@ -364,17 +364,21 @@ def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
 
 
 def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: int) -> int:
-    """Splits of the key range per (sequence, kv head).  The kernel runs two CTAs per SM; with fewer
-    (sequence, kv head) pairs than such places the keys are cut so that one wave of CTAs fills them
-    (at least about four pages of the longest sequence per split), and with more pairs than places
-    only long sequences are cut (64 pages per split).  Measured at 8 kv heads, 2,080 keys: 1 sequence
-    16 splits, 8 sequences 4, 64 sequences 1."""
+    """Splits of the key range per (sequence, kv head).  The kernel runs two CTAs per SM.  With at most
+    half as many (sequence, kv head) pairs as such places the keys are cut so that one wave of CTAs fills
+    them (at least about four pages of the longest sequence per split); with about as many pairs as
+    places one wave would leave no room to even out sequences of unequal length, so splits of 16 pages;
+    with more pairs than places only long sequences are cut (64 pages per split).  Measured at 8 kv
+    heads, 2,080 keys: 1 sequence 16 splits, 8 sequences 4, 64 sequences 1."""
     pages = max(1, (max_kv_len + page_size - 1) // page_size)
     base = max(1, n_seqs * nkv_blocks)
     places = SM_COUNT_TARGET
     if base >= places:
-        return max(1, min(pages, pages // 64))
-    return max(1, min(places // base, max(1, pages // 4)))
+        return max(1, pages // 64)
+    wave = places // base
+    if wave < 2:
+        return max(1, pages // 16)
+    return max(1, min(wave, max(1, pages // 4)))
 
 
 def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
