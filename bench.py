@@ -296,6 +296,118 @@ def run_workload(name):
                    "vocab": V}}))
 
 
+def run_kernels():
+    """The step's hot kernels alone at the 8B layer shapes, for the roofline figures under profiles/:
+    each is captured 24 times into one CUDA graph (as the engine runs them: back to back, programmatic
+    dependent launch) over several copies of its weights or cache, so that every launch reads from DRAM,
+    and timed with CUDA events around 5 replays.  One line per kernel; nothing here is the headline."""
+    import math
+
+    import torch
+
+    from janus_b200.kernels import ops
+    dev = "cuda:0"
+    H, NH, NKV, HD, I, V = 4096, 32, 8, 128, 14336, 128256
+
+    def timed(fn, reps=24):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        time.sleep(SETTLE_S)              # the clocks come back from the power cap of the kernel before
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        for _ in range(5):
+            g.replay()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end) / (5 * reps) * 1e3          # microseconds per launch
+
+    class Scratch:
+        def __init__(self):
+            self.buffers = {}
+
+        def get(self, name, shape, dtype):
+            n = math.prod(shape)
+            if name not in self.buffers or self.buffers[name].numel() < n:
+                self.buffers[name] = torch.empty(n, dtype=dtype, device=dev)
+            return self.buffers[name][:n].view(*shape)
+
+    def product(name, T, N, K, mode, copies=6):
+        rows = 2 * N if mode == "swiglu" else N
+        ws = [(torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+        y = torch.zeros(T, N, device=dev, dtype=torch.bfloat16 if mode == "swiglu" else torch.float32)
+        turn = [0]
+        # a stored product of few tokens runs as the engine runs it: scratch cleared, slices of K added
+        as_add = mode == "store" and T <= 64 and ops.split_k_for(T, N, K) > 1
+
+        def fn():
+            w = ws[turn[0] % copies]
+            turn[0] += 1
+            if as_add:
+                ops.zero_f32(y)
+                ops.gemm_bf16(x, w, y, mode="add")
+            else:
+                ops.gemm_bf16(x, w, y, mode=mode)
+
+        us = timed(fn)
+        print(json.dumps({"kernel": f"product {name}", "tokens": T, "us": round(us, 1),
+                          "weights_GBps": round(rows * K * 2 / us / 1e3, 1),
+                          "TFLOPs": round(2 * T * rows * K / us / 1e6, 1)}), flush=True)
+
+    for T in (8, 64, 2048):
+        product("qkv", T, (NH + 2 * NKV) * HD, H, "store")
+        product("o (add)", T, H, NH * HD, "add")
+        product("gate_up (SiLU gate)", T, I, H, "swiglu")
+        product("down (add)", T, H, I, "add")
+    product("lm_head", 8, V, H, "store", copies=3)
+
+    for B, ctx in ((1, 2080), (8, 2080), (64, 2080)):
+        pages = (ctx + 63) // 64
+        n_pages = B * pages
+        copies = max(1, min(8, int(3e9 // (n_pages * NKV * 64 * HD * 4))))
+        kcs = [torch.randn(n_pages, NKV, 64, HD, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        vcs = [torch.randn(n_pages, NKV, 64, HD, device=dev).to(torch.bfloat16) for _ in range(copies)]
+        table = torch.arange(n_pages, device=dev, dtype=torch.int32).view(B, pages)
+        kv_len = torch.full((B,), ctx, device=dev, dtype=torch.int32)
+        q = torch.randn(B, NH * HD, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        ws, turn = Scratch(), [0]
+        cap = 1 << (pages - 1).bit_length()                          # the engine's graphs are keyed by this bound
+
+        def fn():
+            i = turn[0] % copies
+            turn[0] += 1
+            ops.attention_bf16_decode(q, kcs[i], vcs[i], out, table, kv_len, NH, NKV, HD, 64, 0, 1 / math.sqrt(HD),
+                                      ws, cap * 64)
+
+        us = timed(fn)
+        print(json.dumps({"kernel": "decode attention + combine", "sequences": B, "keys": ctx,
+                          "splits": ops.decode_splits_for(B, NKV, cap * 64, 64), "us": round(us, 1),
+                          "kv_GBps": round(B * ctx * NKV * HD * 4 / us / 1e3, 1)}), flush=True)
+
+    for B, L in ((1, 2048), (1, 8192)):
+        pages = (L + 63) // 64
+        kc = torch.randn(B * pages, NKV, 64, HD, device=dev).to(torch.bfloat16)
+        vc = torch.randn_like(kc)
+        table = torch.arange(B * pages, device=dev, dtype=torch.int32).view(B, pages)
+        q = torch.randn(B * L, NH * HD, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        q_start = torch.arange(B + 1, device=dev, dtype=torch.int32) * L
+        kv_len = torch.full((B,), L, device=dev, dtype=torch.int32)
+        us = timed(lambda: ops.attention_tc_prefill(q, kc, vc, out, table, q_start, kv_len, B, L, NH, NKV, HD, 64, 0,
+                                                    1 / math.sqrt(HD)), reps=6)
+        print(json.dumps({"kernel": "prefill attention (tcgen05)", "tokens": L, "us": round(us, 1),
+                          "TFLOPs": round(B * 4 * NH * HD * L * (L + 1) / 2 / us / 1e6, 1)}), flush=True)
+    ops.check_kernel_status(torch.device(dev))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -307,6 +419,8 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline batch only")
     ap.add_argument("--workload", default="8b", choices=["8b", "1b", "13b"],
                     help="8b: the headline benchmark; 1b / 13b: the other workloads of BASELINE.json, end to end")
+    ap.add_argument("--kernels", action="store_true",
+                    help="time the step's hot kernels alone at the 8B layer shapes (one JSON line each)")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
@@ -318,6 +432,9 @@ def main():
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.kernels:
+        run_kernels()
+        return 0
     if args.workload != "8b":
         run_workload(args.workload)
         return 0
