@@ -19,11 +19,20 @@ def _to_engine(w: torch.Tensor, dtype: torch.dtype, device: torch.device) -> tor
     return w.to(device=device, dtype=dtype).contiguous()
 
 
+def _check_width(in_features: int, dtype: torch.dtype) -> None:
+    """The tensor-core product reads its operands by TMA, whose rows must be multiples of 16 bytes: refuse
+    other widths when the model is built, not at the first step."""
+    if dtype == torch.bfloat16 and in_features % 8 != 0:
+        raise ValueError(f"a bfloat16 product over {in_features} input features is not supported (the width "
+                         f"must be a multiple of 8); such a model runs with dtype float32")
+
+
 class Linear:
     """One weight matrix, possibly the row-wise stack of several tensors of the
     checkpoint (q, k, v stacked so that one product serves all three)."""
 
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device):
+        _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
         self.weight: Optional[torch.Tensor] = None
@@ -75,6 +84,7 @@ class GatedLinear:
     (crates/janus-engine/src/model/block.rs:383-430)."""
 
     def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device):
+        _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
         self.weight: Optional[torch.Tensor] = None   # [2 * out, in]

@@ -83,3 +83,13 @@ def test_read_config_json_errors(tmp_path):
     (tmp_path / "config.json").write_text(json.dumps(TINY_B))
     assert read_config_json(str(tmp_path))["hidden_size"] == 96
     assert read_config_json(str(tmp_path / "config.json"))["hidden_size"] == 96
+
+
+def test_a_width_the_bfloat16_products_cannot_take_is_refused_when_the_model_is_built():
+    import torch
+    from janus_b200.engine.model import DecoderModel
+    from janus_b200.models.llama import llama_spec
+    cfg = LlamaConfig.from_dict(dict(TINY_A, intermediate_size=100))      # rows of 200 bytes: no multiple of 16
+    with pytest.raises(ValueError, match="multiple of 8"):
+        DecoderModel(llama_spec(cfg), torch.bfloat16, torch.device("cpu"))
+    DecoderModel(llama_spec(cfg), torch.float32, torch.device("cpu"))     # the 32-bit path has no such limit
