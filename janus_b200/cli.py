@@ -10,11 +10,15 @@ of crates/janus-engine/examples/batch_inference.rs:101-147 (4, 50, 0.0 = greedy)
 The reference's tokenizer reads only GGUF metadata and is out of scope here, so a
 prompt is a list of token ids ("1,15043,3186" or "1 15043 3186").  The remaining
 options carry the sampler's names (crates/janus-engine/src/model/sampler.rs:20-39).
+Longer spellings are accepted for the same options (`--prompt-ids`, `--prompt-ids-file`,
+`--max-new-tokens`, `--max-batch`, `--max-seq-len`, `--dtype bf16|fp32`), and
+`--random-weights [--seed-weights S]` runs a folder that holds only config.json.
 """
 from __future__ import annotations
 
 import argparse
 import json
+import os
 import sys
 from typing import List
 
@@ -35,9 +39,13 @@ def main(argv=None) -> int:
         usage='%(prog)s <model_dir> "<prompt>" [--batch-size N] [--max-tokens N] [--temperature T]')
     ap.add_argument("model_dir", help="folder with config.json and model.safetensors")
     ap.add_argument("prompts", nargs="*", help='token ids of a prompt, e.g. "1,2,3"; several prompts form a batch')
-    ap.add_argument("--prompts-file", help="file with one prompt (token ids) per line")
-    ap.add_argument("--batch-size", type=int, default=4, help="prompts processed in parallel (default: 4)")
-    ap.add_argument("--max-tokens", type=int, default=50, help="tokens to generate per sequence at most (default: 50)")
+    ap.add_argument("--prompt-ids", action="append", default=[], help="a prompt as an option (repeatable)")
+    ap.add_argument("--prompts-file", "--prompt-ids-file", action="append", default=[],
+                    help="file with one prompt (token ids) per line (repeatable)")
+    ap.add_argument("--batch-size", "--max-batch", type=int, default=4,
+                    help="prompts processed in parallel (default: 4)")
+    ap.add_argument("--max-tokens", "--max-new-tokens", type=int, default=50,
+                    help="tokens to generate per sequence at most (default: 50)")
     ap.add_argument("--temperature", type=float, default=0.0, help="sampling temperature (default: 0.0 = greedy)")
     ap.add_argument("--top-k", type=int, default=0, help="top-k filtering (0 = disabled)")
     ap.add_argument("--top-p", type=float, default=1.0, help="top-p (nucleus) filtering (1.0 = disabled)")
@@ -45,14 +53,18 @@ def main(argv=None) -> int:
     ap.add_argument("--seed", type=int, default=0, help="seed of the sampler's random numbers")
     ap.add_argument("--stop-id", type=int, action="append", default=[], help="extra stop token id (repeatable)")
     ap.add_argument("--ignore-eos", action="store_true", help="do not stop at config.json's eos_token_id")
-    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
-    ap.add_argument("--context-size", type=int, default=None, help="longest sequence (default: the model's)")
+    ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
+    ap.add_argument("--context-size", "--max-seq-len", type=int, default=None,
+                    help="longest sequence (default: the model's)")
+    ap.add_argument("--random-weights", action="store_true",
+                    help="the folder holds only config.json: run it with random weights")
+    ap.add_argument("--seed-weights", type=int, default=0, help="seed of --random-weights")
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
     args = ap.parse_args(argv)
 
-    prompts = [parse_prompt(p) for p in args.prompts]
-    if args.prompts_file:
-        with open(args.prompts_file) as f:
+    prompts = [parse_prompt(p) for p in list(args.prompts) + args.prompt_ids]
+    for path in args.prompts_file:
+        with open(path) as f:
             prompts += [parse_prompt(line) for line in f if line.strip()]
     if not prompts:
         ap.error("give at least one prompt")
@@ -62,8 +74,15 @@ def main(argv=None) -> int:
 
     batch = max(1, min(args.batch_size, len(prompts)))
     room = sorted((tokens_held(len(p), args.max_tokens, 64) for p in prompts), reverse=True)
-    model = janus_b200.load(args.model_dir, dtype=args.dtype, max_tokens=sum(room[:batch]),
-                            max_seq_len=args.context_size, max_slots=batch)
+    dtype = {"bf16": "bfloat16", "fp32": "float32"}.get(args.dtype, args.dtype)
+    if args.random_weights:
+        with open(os.path.join(args.model_dir, "config.json")) as f:
+            config = json.load(f)
+        model = janus_b200.load_random(config, seed=args.seed_weights, dtype=dtype, max_tokens=sum(room[:batch]),
+                                       max_seq_len=args.context_size, max_slots=batch)
+    else:
+        model = janus_b200.load(args.model_dir, dtype=dtype, max_tokens=sum(room[:batch]),
+                                max_seq_len=args.context_size, max_slots=batch)
     out, reasons, stats = model.generate(
         prompts, max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
         repetition_penalty=args.repetition_penalty, seed=args.seed, stop_token_ids=args.stop_id,

@@ -132,6 +132,25 @@ def test_command_line(tmp_path):
     assert got["finish_reasons"] == ["length"] * 3
     bad = subprocess.run(cmd[:3] + ["1,x,3"], capture_output=True, text=True, timeout=120)
     assert bad.returncode != 0 and "token ids" in (bad.stderr + bad.stdout)
+    # the longer spellings of the same options, prompts given as options and from a file
+    listing = tmp_path / "prompts.txt"
+    listing.write_text(" ".join(map(str, prompts[2])) + "\n")
+    alias = cmd[:3] + ["--prompt-ids", ",".join(map(str, prompts[0])), "--prompt-ids", ",".join(map(str, prompts[1])),
+                       "--prompt-ids-file", str(listing), "--max-new-tokens", "5", "--max-batch", "2", "--dtype", "fp32",
+                       "--max-seq-len", "64", "--ignore-eos", "--json"]
+    res = subprocess.run(alias, capture_output=True, text=True, timeout=300)
+    assert res.returncode == 0, res.stderr[-2000:]
+    assert json.loads(res.stdout.strip().splitlines()[-1])["tokens"] == got["tokens"]
+    # a folder with config.json only, run with seeded random weights: the same seed gives the same tokens
+    only_config = tmp_path / "c"
+    only_config.mkdir()
+    (only_config / "config.json").write_text(json.dumps(TINY["A"]))
+    rnd = [sys.executable, os.path.join(ROOT, "bin", "janus_b200"), str(only_config), "1,2,3", "--random-weights",
+           "--seed-weights", "7", "--max-tokens", "4", "--ignore-eos", "--json"]
+    runs = [subprocess.run(rnd, capture_output=True, text=True, timeout=300) for _ in range(2)]
+    assert all(r.returncode == 0 for r in runs), runs[0].stderr[-2000:]
+    outs = [json.loads(r.stdout.strip().splitlines()[-1])["tokens"] for r in runs]
+    assert outs[0] == outs[1] and len(outs[0][0]) == 4
 
 
 def test_errors_before_launch(tmp_path):
