@@ -374,6 +374,71 @@ def test_gemm_qkv_with_rotation_and_cache_append(ops, T, nh, nkv, hd, K):
         assert float(cache.float().cpu().permute(0, 2, 1, 3).reshape(n_pages * PAGE, -1)[untouched].abs().sum()) == 0.0
 
 
+def _guarded(shape, dtype, fill):
+    """A tensor in the middle of a larger buffer whose rest holds a guard value."""
+    n = math.prod(shape)
+    pad = 4096
+    buf = torch.full((n + 2 * pad,), fill, device=DEV, dtype=dtype)
+    return buf, buf[pad:pad + n].view(*shape), pad
+
+
+def _guards_intact(buf, pad, fill):
+    head, tail = buf[:pad].float().cpu(), buf[-pad:].float().cpu()
+    return bool((head == fill).all()) and bool((tail == fill).all())
+
+
+@pytest.mark.parametrize("T", [5, 33, 300, 700])
+def test_kernels_write_nothing_outside_their_outputs(ops, T):
+    """Guard values before and after every output of the bfloat16 path stay as they were, at token counts and
+    widths that leave the last tile of every kernel partly empty."""
+    N, K, I, nh, nkv, hd = 200, 120, 104, 5, 5, 40
+    x, w = bf16_inputs(T, N, K, T)
+    for dtype, mode in ((torch.bfloat16, "store"), (torch.float32, "store"), (torch.float32, "add")):
+        buf, y, pad = _guarded((T, N), dtype, 7.0)
+        ops.gemm_bf16(x, w, y, mode=mode)
+        assert _guards_intact(buf, pad, 7.0), (T, dtype, mode)
+    _, wg = bf16_inputs(T, 2 * I, K, T + 1)
+    buf, act, pad = _guarded((T, I), torch.bfloat16, 7.0)
+    ops.gemm_bf16(x, wg, act, mode="swiglu")
+    assert _guards_intact(buf, pad, 7.0)
+    if T >= 256:                                        # the CTA-pair kernels, asked for by name
+        for dtype, mode in ((torch.float32, "store"), (torch.float32, "add")):
+            buf, y, pad = _guarded((T, N), dtype, 7.0)
+            ops.gemm_bf16(x, w, y, mode=mode, pair=True)
+            assert _guards_intact(buf, pad, 7.0), (T, dtype, mode)
+        buf, act, pad = _guarded((T, I), torch.bfloat16, 7.0)
+        ops.gemm_bf16(x, wg, act, mode="swiglu", pair=True)
+        assert _guards_intact(buf, pad, 7.0)
+    # norm and the rotation with cache append
+    res = torch.randn(T, K, device=DEV)
+    gamma = torch.ones(K, device=DEV, dtype=torch.bfloat16)
+    buf, normed, pad = _guarded((T, K), torch.bfloat16, 7.0)
+    ops.rmsnorm(res, gamma, 1e-5, normed)
+    assert _guards_intact(buf, pad, 7.0)
+    n_pages = (T + PAGE - 1) // PAGE
+    qkv = torch.randn(T, (nh + 2 * nkv) * hd, device=DEV)
+    cos, sin = P.rope_cos_sin(torch.arange(T), P.rope_inv_freq(hd, 10000.0, None))
+    table = torch.stack([cos, sin], -1).contiguous().to(DEV)
+    positions = torch.arange(T, device=DEV, dtype=torch.int32)
+    bq, q, pq = _guarded((T, nh * hd), torch.bfloat16, 7.0)
+    bk, kc, pk = _guarded((n_pages, nkv, PAGE, hd), torch.bfloat16, 7.0)
+    bv, vc, pv = _guarded((n_pages, nkv, PAGE, hd), torch.bfloat16, 7.0)
+    ops.rope_cache_write(qkv, q, table, positions, positions, kc, vc, nh, nkv, hd, PAGE)
+    assert _guards_intact(bq, pq, 7.0) and _guards_intact(bk, pk, 7.0) and _guards_intact(bv, pv, 7.0)
+    # attention of the last token of one sequence of T keys over those pages, and of the whole prompt
+    table_pages = torch.arange(n_pages, device=DEV, dtype=torch.int32).view(1, n_pages)
+    kv_len = torch.tensor([T], device=DEV, dtype=torch.int32)
+    bo, out, po = _guarded((1, nh * hd), torch.bfloat16, 7.0)
+    ops.attention_bf16_decode(q[T - 1:].contiguous(), kc, vc, out, table_pages, kv_len, nh, nkv, hd, PAGE, 0,
+                              1 / math.sqrt(hd), _WS(), T, n_splits=3)
+    assert _guards_intact(bo, po, 7.0)
+    q_start = torch.tensor([0, T], device=DEV, dtype=torch.int32)
+    bo, out, po = _guarded((T, nh * hd), torch.bfloat16, 7.0)
+    ops.attention_bf16_prefill(q, kc, vc, out, table_pages, q_start, kv_len, 1, T, nh, nkv, hd, PAGE, 0, 1 / math.sqrt(hd))
+    assert _guards_intact(bo, po, 7.0)
+    ops.check_kernel_status(torch.device(DEV))
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take(ops):
     x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
     w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)
