@@ -340,7 +340,11 @@ def run_kernels():
 
     def product(name, T, N, K, mode, copies=6):
         rows = 2 * N if mode == "swiglu" else N
-        ws = [(torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16) for _ in range(copies)]
+        def weight():
+            w = (torch.randn(rows, K, device=dev) * 0.02).to(torch.bfloat16)
+            return ops.pack_gated(w[:N].contiguous(), w[N:].contiguous()) if mode == "swiglu" else ops.pack_weight(w)
+
+        ws = [weight() for _ in range(copies)]
         x = torch.randn(T, K, device=dev).to(torch.bfloat16)
         y = torch.zeros(T, N, device=dev, dtype=torch.bfloat16 if mode == "swiglu" else torch.float32)
         turn = [0]

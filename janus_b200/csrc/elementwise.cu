@@ -243,3 +243,40 @@ JB_EXPORT int jb_zero_f32(float* p, long long n, cudaStream_t stream) {
   jb::Launch cfg(dim3((unsigned)((n4 + 255) / 256)), dim3(256), 0, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, zero_f32_kernel, (float4*)p, n4);
 }
+
+// ---------------------------------------------------------------------------
+// Weights of the bfloat16 products, laid out for streaming: the row-major [N, K] matrix is cut into tiles
+// of 128 rows x 64 columns (16 KB, zero-padded at the edges), stored one after another as
+// [row tile][k tile][128 rows][128 bytes], and inside a tile the 16-byte chunk c of row r lies at chunk
+// position c ^ (r & 7): the 128-byte swizzle the tensor core reads from shared memory.  A product then
+// fetches a tile as ONE contiguous 16 KB block (a TMA box over rows of 128 bytes, no swizzle in the copy)
+// instead of 128 row pieces that lie 2 K bytes apart: contiguous blocks stream 6 - 9 % faster from HBM.
+// ---------------------------------------------------------------------------
+namespace {
+__global__ void pack_weight_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int N, int K, int k_tiles,
+                                   size_t n_chunks) {
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;   // destination chunk
+  if (i >= n_chunks) return;
+  const int p = (int)(i & 7), r = (int)((i >> 3) & 127);
+  const size_t tile = i >> 10;
+  const int kt = (int)(tile % k_tiles);
+  const size_t rt = tile / k_tiles;
+  const int c = p ^ (r & 7);
+  const size_t row = rt * 128 + r;
+  const int col = kt * 64 + c * 8;
+  uint4 v = make_uint4(0u, 0u, 0u, 0u);
+  if (row < (size_t)N && col < K) v = src[(row * K + col) >> 3];
+  dst[i] = v;
+}
+}  // namespace
+
+// src: [N, K] bf16 row-major, K a multiple of 8, 16-byte aligned; dst: ceil(N/128) * ceil(K/64) tiles of 16 KB.
+JB_EXPORT int jb_pack_weight_bf16(const void* src, int N, int K, void* dst, cudaStream_t stream) {
+  if (N <= 0 || K <= 0) return 0;
+  JB_REFUSE(K % 8 != 0 || (((uintptr_t)src | (uintptr_t)dst) & 15), "pack_weight: K = %d must be a multiple of 8 and the tensors 16-byte aligned", K);
+  const int k_tiles = (K + 63) / 64;
+  const size_t n_chunks = (size_t)((N + 127) / 128) * k_tiles * 1024;
+  pack_weight_kernel<<<(unsigned)((n_chunks + 255) / 256), 256, 0, stream>>>((const uint4*)src, (uint4*)dst, N, K, k_tiles,
+                                                                             n_chunks);
+  return (int)cudaGetLastError();
+}

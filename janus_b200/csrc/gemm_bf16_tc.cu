@@ -1,5 +1,7 @@
 // bfloat16 matrix product on the 5th-generation tensor cores (tcgen05) of sm_100a:
 //   D[f, t] = sum_k W[f, k] * X[t, k]      (W: weights [N, K], X: tokens [T, K], both K-major)
+// The weights come packed (jb_pack_weight_bf16 in elementwise.cu): tiles of 128 rows x 64 columns, each one
+// contiguous, already swizzled 16 KB block, so that a stage's weights are one sequential read of HBM.
 // The weights are the M side of the MMA (128 rows per tile, one TMEM lane per
 // output feature), the tokens the N side (16..256 per tile), so the same kernel
 // serves prefill (many tokens) and decode (a handful) without wasting the M side.
@@ -18,9 +20,7 @@
 // an error code in `*status`, skips its remaining work, frees its TMEM and returns.
 // The kernel may start while its predecessor in the stream still runs (programmatic
 // dependent launch): before it waits for the predecessor it sets up its barriers and
-// TMEM, loads the weight tiles of its first stages (weights depend on no kernel) and
-// can ask for further weight tiles to be brought into L2 (JANUS_L2_PREFETCH=n; off by default:
-// it measured slower than leaving the ring to pull them).
+// TMEM and loads the weight tiles of its first stages (weights depend on no kernel).
 //
 // The reference computes the same product on scalar cores with f32
 // accumulation (crates/janus-engine/src/compute/shaders/gemm.wgsl:58-147).
@@ -96,9 +96,6 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, int* st
 
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
-}
-__device__ __forceinline__ void tma_prefetch_2d(const CUtensorMap* map, int x, int y) {
-  asm volatile("cp.async.bulk.prefetch.tensor.2d.L2.global [%0, {%1, %2}];" ::"l"(map), "r"(x), "r"(y) : "memory");
 }
 __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int x, int y) {
   asm volatile(
@@ -192,7 +189,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                                           const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                           int T, int N_out, int ldy, int k_tiles, int k_tiles_per_split,
                                                           int n_tiles, int n_tok_tiles, int n_w_tiles,
-                                                          int up_row_offset, int atomic_add, int l2_prefetch_tiles,
+                                                          int up_tile_offset, int atomic_add,
                                                           int* __restrict__ status) {
   using C = Cfg<BN, MODE>;
   extern __shared__ uint8_t smem_raw[];
@@ -243,15 +240,10 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           for (int i = 0; i < early; ++i) {
             const uint32_t stage = smem_base + i * C::STAGE_BYTES, bar = full0 + 8 * i;
             mbar_expect_tx(bar, C::STAGE_BYTES);
-            const int kx = (tc.kt_begin + i) * BK;
-            tma_load_2d(stage, &map_w, bar, kx, tc.m0);
-            if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, kx, up_row_offset + tc.m0);
-          }
-          const int ahead = min(tc.n_kt, early + l2_prefetch_tiles);
-          for (int i = early; i < ahead; ++i) {
-            const int kx = (tc.kt_begin + i) * BK;
-            tma_prefetch_2d(&map_w, kx, tc.m0);
-            if (MODE == SWIGLU) tma_prefetch_2d(&map_w, kx, up_row_offset + tc.m0);
+            // weight tile (row tile, k tile) = rows [.. * 128, +128) of the packed matrix: one contiguous 16 KB
+            const int wy = ((tc.m0 / BM) * k_tiles + tc.kt_begin + i) * BM;
+            tma_load_2d(stage, &map_w, bar, 0, wy);
+            if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, 0, wy + up_tile_offset * k_tiles * BM);
           }
           jb::pdl_wait();
           waited = true;
@@ -267,8 +259,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           const uint32_t stage = smem_base + s * C::STAGE_BYTES, bar = full0 + 8 * s;
           mbar_expect_tx(bar, C::STAGE_BYTES);
           const int kx = (tc.kt_begin + i) * BK;
-          tma_load_2d(stage, &map_w, bar, kx, tc.m0);
-          if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, kx, up_row_offset + tc.m0);
+          const int wy = ((tc.m0 / BM) * k_tiles + tc.kt_begin + i) * BM;
+          tma_load_2d(stage, &map_w, bar, 0, wy);
+          if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, 0, wy + up_tile_offset * k_tiles * BM);
           tma_load_2d(stage + C::A_TILES * C::A_BYTES, &map_x, bar, kx, tc.t0);
         }
       }
@@ -412,6 +405,19 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uin
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Map of packed weights (see jb_pack_weight_bf16): `tiles` blocks of 128 rows x 128 bytes, already swizzled.
+bool make_packed_map(CUtensorMap* map, const void* base, uint64_t tiles) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)BK, tiles * BM};
+  const cuuint64_t strides[1] = {(cuuint64_t)BK * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -425,7 +431,7 @@ int sm_count() {
 
 template <int BN, int MODE, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_out, int ldy, int k_tiles,
-           int split_k, int up_row_offset, int* status, cudaStream_t stream) {
+           int split_k, int up_tile_offset, int* status, cudaStream_t stream) {
   using C = Cfg<BN, MODE>;
   constexpr int smem = STAGES * C::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static int ctas_per_sm = 0;
@@ -445,28 +451,20 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_o
   const long long n_tiles = (long long)n_tok_tiles * n_w_tiles * splits;
   JB_REFUSE(n_tiles > 0x7fffffffLL, "gemm_bf16: too many tiles (%lld)", n_tiles);
   const int grid = (int)min(n_tiles, (long long)sm_count() * ctas_per_sm);
-  // a weight-streaming product (few tokens) asks L2 for the weight tiles beyond its first stages
-  static int prefetch_depth = -1;  // JANUS_L2_PREFETCH overrides the default depth (0 turns it off)
-  if (prefetch_depth < 0) {
-    const char* e = getenv("JANUS_L2_PREFETCH");
-    prefetch_depth = e ? max(0, atoi(e)) : 0;
-  }
-  const int l2_prefetch_tiles = BN <= 64 ? prefetch_depth : 0;
   jb::Launch cfg(dim3(grid), dim3(THREADS), smem, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, gemm_tc_kernel<BN, MODE, STAGES>, mw, mx, Y, T, N_out, ldy, k_tiles, per,
-                                 (int)n_tiles, n_tok_tiles, n_w_tiles, up_row_offset, splits > 1 ? 1 : 0,
-                                 l2_prefetch_tiles, status);
+                                 (int)n_tiles, n_tok_tiles, n_w_tiles, up_tile_offset, splits > 1 ? 1 : 0, status);
 }
 
 template <int MODE>
 int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, int K, int ldy, int split_k,
-             int up_row_offset, int* status, cudaStream_t stream) {
+             int up_tile_offset, int* status, cudaStream_t stream) {
   const int k_tiles = (K + BK - 1) / BK;
   CUtensorMap mx;
 #define JB_GO(BN_, ST_)                                                                                 \
   {                                                                                                     \
     if (!make_map(&mx, X, (uint64_t)T, (uint64_t)K, BN_)) return JB_ERR_TENSORMAP;                      \
-    return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_row_offset, status,    \
+    return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_tile_offset, status,    \
                                   stream);                                                              \
   }
   // Decode-sized token counts: small stages so that two or more CTAs share an SM
@@ -485,25 +483,29 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
 
 }  // namespace
 
-// Y (+)= X . W^T.  X: [T, K] bf16, W: [N, K] bf16 (for mode SWIGLU: [2*N_out, K],
-// gate rows over up rows), Y: [T, ldy] with N_out columns used.
+// Y (+)= X . W^T.  X: [T, K] bf16 row-major; W: the [N_out, K] matrix packed by jb_pack_weight_bf16
+// (`w_tiles` tiles of 16 KB in all; for mode SWIGLU the gate rows' tiles first and the up rows' tiles from row
+// tile `up_tile_offset` on); Y: [T, ldy] with N_out columns used.
 // mode: 0 store bf16, 1 store f32, 2 add into f32, 3 silu(gate)*up -> bf16.
 // split_k > 1 only with mode 2 (partial sums meet in Y through atomic adds).
 // `status` is a device int that a timed-out wait sets to 1 (producer), 2 (MMA) or 3 (epilogue).
-JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, void* Y, int T, int N_out, int K, int ldy, int mode,
-                           int split_k, int* status, cudaStream_t stream) {
+JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
+                           int N_out, int K, int ldy, int mode, int split_k, int* status, cudaStream_t stream) {
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16: operands must be 16-byte aligned");
   JB_REFUSE(mode < 0 || mode > 3, "gemm_bf16: unknown mode %d", mode);
   JB_REFUSE(split_k < 1 || (split_k > 1 && mode != ADD_F32), "gemm_bf16: K can be split only in mode 2");
+  const long long k_tiles = (K + BK - 1) / BK, row_tiles = (N_out + BM - 1) / BM;
+  const long long need = mode == SWIGLU ? (up_tile_offset + row_tiles) * k_tiles : row_tiles * k_tiles;
+  JB_REFUSE(w_tiles < need || (mode == SWIGLU && up_tile_offset < row_tiles) || w_tiles * BM > 0x7fffffffLL,
+            "gemm_bf16: the packed weight holds %lld tiles, the product needs %lld", w_tiles, need);
   CUtensorMap mw;
-  const uint64_t w_rows = mode == SWIGLU ? 2ull * N_out : (uint64_t)N_out;
-  if (!make_map(&mw, W, w_rows, (uint64_t)K, BM)) return JB_ERR_TENSORMAP;
+  if (!make_packed_map(&mw, W, (uint64_t)w_tiles)) return JB_ERR_TENSORMAP;
   switch (mode) {
     case STORE_BF16: return dispatch<STORE_BF16>(mw, X, Y, T, N_out, K, ldy, 1, 0, status, stream);
     case STORE_F32: return dispatch<STORE_F32>(mw, X, Y, T, N_out, K, ldy, 1, 0, status, stream);
     case ADD_F32: return dispatch<ADD_F32>(mw, X, Y, T, N_out, K, ldy, split_k, 0, status, stream);
-    default: return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, N_out, status, stream);
+    default: return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, up_tile_offset, status, stream);
   }
 }

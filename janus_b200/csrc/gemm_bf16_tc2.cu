@@ -175,7 +175,7 @@ template <int MODE>
 __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w,
                                                            const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                            int T, int N_out, int ldy, int k_tiles, int n_tiles,
-                                                           int n_tok_tiles, int up_row_offset, RopeOut rope, int* __restrict__ status) {
+                                                           int n_tok_tiles, int up_tile_offset, RopeOut rope, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -221,7 +221,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
         const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles);
         // rows of this CTA's two loads: its 128 rows of the pair's M side, its half of the column operand
-        const int w_row = MODE == SWIGLU ? (rank ? up_row_offset + tc.f0 : tc.f0) : tc.f0 + (int)rank * BM;
+        // this CTA's weight row tile (the weights are packed: a tile is one contiguous 16 KB block)
+        const int w_tile = MODE == SWIGLU ? (rank ? up_tile_offset + tc.f0 / BM : tc.f0 / BM) : tc.f0 / BM + (int)rank;
         constexpr bool TOK_ROWS = tokens_on_rows(MODE);
         const int x_row = tc.t0 + (int)rank * BM;
         for (int i = 0; i < k_tiles; ++i, ++it) {
@@ -231,8 +232,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
           const uint32_t bar = (full0 + 8 * s) & PEER_MASK;   // the first CTA's barrier collects both CTAs' bytes
           mbar_expect_tx_cluster(bar, STAGE_BYTES);
           const int kx = i * BK;
-          tma_load_2d_pair(stage, TOK_ROWS ? &map_x : &map_w, bar, kx, TOK_ROWS ? x_row : w_row);
-          tma_load_2d_pair(stage + A_BYTES, TOK_ROWS ? &map_w : &map_x, bar, kx, TOK_ROWS ? w_row : x_row);
+          const int wy = (w_tile * k_tiles + i) * BM;   // beyond the packed matrix: filled with zeros
+          if (TOK_ROWS) {
+            tma_load_2d_pair(stage, &map_x, bar, kx, x_row);
+            tma_load_2d_pair(stage + A_BYTES, &map_w, bar, 0, wy);
+          } else {
+            tma_load_2d_pair(stage, &map_w, bar, 0, wy);
+            tma_load_2d_pair(stage + A_BYTES, &map_x, bar, kx, x_row);
+          }
         }
       }
     }
@@ -437,6 +444,19 @@ bool make_map(CUtensorMap* map, const void* base, uint64_t rows, uint64_t K, uin
             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
+// Map of packed weights (jb_pack_weight_bf16): `tiles` blocks of 128 rows x 128 bytes, already swizzled.
+bool make_packed_map(CUtensorMap* map, const void* base, uint64_t tiles) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)BK, tiles * BM};
+  const cuuint64_t strides[1] = {(cuuint64_t)BK * 2};
+  const cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+  const cuuint32_t elem[2] = {1, 1};
+  return fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+            CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 int sm_count() {
   static int n = 0;
   if (n == 0) {
@@ -449,8 +469,8 @@ int sm_count() {
 }
 
 template <int MODE>
-int launch(const void* X, const void* W, void* Y, int T, int N_out, int K, int ldy, const RopeOut& rope, int* status,
-           cudaStream_t stream) {
+int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T, int N_out, int K, int ldy,
+           const RopeOut& rope, int* status, cudaStream_t stream) {
   constexpr int smem = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -459,8 +479,13 @@ int launch(const void* X, const void* W, void* Y, int T, int N_out, int K, int l
     configured = true;
   }
   CUtensorMap mw, mx;
-  const uint64_t w_rows = MODE == SWIGLU ? 2ull * N_out : (uint64_t)N_out;
-  if (!make_map(&mw, W, w_rows, (uint64_t)K, BM)) return JB_ERR_TENSORMAP;
+  {
+    const long long kt = (K + BK - 1) / BK, rt = (N_out + BM - 1) / BM;
+    const long long need = MODE == SWIGLU ? (up_tile_offset + rt) * kt : rt * kt;
+    JB_REFUSE(w_tiles < need || (MODE == SWIGLU && up_tile_offset < rt) || w_tiles * BM > 0x7fffffffLL,
+              "gemm_bf16_pair: the packed weight holds %lld tiles, the product needs %lld", w_tiles, need);
+  }
+  if (!make_packed_map(&mw, W, (uint64_t)w_tiles)) return JB_ERR_TENSORMAP;
   if (!make_map(&mx, X, (uint64_t)T, (uint64_t)K, BM)) return JB_ERR_TENSORMAP;
   const int k_tiles = (K + BK - 1) / BK;
   constexpr int F_TILE = MODE == SWIGLU ? 128 : 256;
@@ -485,23 +510,23 @@ int launch(const void* X, const void* W, void* Y, int T, int N_out, int K, int l
     cfg.numAttrs = 2;
   }
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, Y, T, N_out, ldy, k_tiles, n_tiles,
-                                 n_tok_tiles, MODE == SWIGLU ? N_out : 0, rope, status);
+                                 n_tok_tiles, MODE == SWIGLU ? up_tile_offset : 0, rope, status);
 }
 
 }  // namespace
 
-// Same contract as jb_gemm_bf16 (without split-K): Y (+)= X . W^T with X [T, K], W [N, K] (SWIGLU: [2 N_out, K]).
+// Same contract as jb_gemm_bf16 (without split-K): Y (+)= X . W^T with X [T, K] and W packed (jb_pack_weight_bf16).
 // Meant for T >= 256.  status codes of a timed-out wait: 21 producer, 22 MMA, 23 epilogue.
-JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, void* Y, int T, int N_out, int K, int ldy, int mode,
-                                int* status, cudaStream_t stream) {
+JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
+                                int N_out, int K, int ldy, int mode, int* status, cudaStream_t stream) {
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16_pair: operands must be 16-byte aligned");
   switch (mode) {
-    case STORE_BF16: return launch<STORE_BF16>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
-    case STORE_F32: return launch<STORE_F32>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
-    case ADD_F32: return launch<ADD_F32>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
-    case SWIGLU: return launch<SWIGLU>(X, W, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case STORE_BF16: return launch<STORE_BF16>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case STORE_F32: return launch<STORE_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case ADD_F32: return launch<ADD_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case SWIGLU: return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     default: JB_REFUSE(true, "gemm_bf16_pair: unknown mode %d", mode);
   }
 }
@@ -509,7 +534,7 @@ JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, void* Y, int T, in
 // The stacked q/k/v projection of prompt tokens with its consumers fused in: X [T, K] . W [(nh + 2 nkv) hd, K]^T,
 // q and k rotated by cos_sin[positions[t]] (pairs i, i + hd/2), q written to q_out [T, nh hd] and k, v to the
 // paged cache at row dest[t], all bfloat16.  hd must divide 256 and hd/2 be a multiple of 16 (32, 64, 128, 256).
-JB_EXPORT int jb_gemm_bf16_pair_qkv_rope(const void* X, const void* W, int T, int K, void* q_out, void* k_cache,
+JB_EXPORT int jb_gemm_bf16_pair_qkv_rope(const void* X, const void* W, long long w_tiles, int T, int K, void* q_out, void* k_cache,
                                          void* v_cache, const float* cos_sin, const int* positions, const int* dest,
                                          int nh, int nkv, int hd, int page_size, int* status, cudaStream_t stream) {
   if (T <= 0) return 0;
@@ -521,5 +546,5 @@ JB_EXPORT int jb_gemm_bf16_pair_qkv_rope(const void* X, const void* W, int T, in
   JB_REFUSE(nh <= 0 || nkv <= 0 || page_size <= 0 || !cos_sin || !positions || !dest, "gemm_bf16_pair_qkv_rope: bad arguments");
   RopeOut rope{(__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, cos_sin, positions, dest,
                nh, nkv, hd, page_size};
-  return launch<QKV_ROPE>(X, W, nullptr, T, (nh + 2 * nkv) * hd, K, 0, rope, status, stream);
+  return launch<QKV_ROPE>(X, W, w_tiles, 0, nullptr, T, (nh + 2 * nkv) * hd, K, 0, rope, status, stream);
 }

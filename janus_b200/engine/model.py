@@ -62,7 +62,7 @@ class DecoderModel:
         emb = named[spec.embedding_weight]
         self.embedding = emb.to(device=self.device, dtype=self.dtype).contiguous()
         if spec.head_weight is None:
-            self.head.weight = self.embedding
+            self.head.load_row_major(self.embedding)
         else:
             self.head.load([named[spec.head_weight]])
         self.final_norm.load(**{k: named[v] for k, v in spec.final_norm.weights.items()})

@@ -205,6 +205,54 @@ def check_kernel_status(device: torch.device) -> None:
         raise KernelError(f"a tensor-core kernel timed out waiting on an mbarrier ({who}, code {code})")
 
 
+class PackedWeight:
+    """A [rows, cols] bfloat16 matrix laid out for the tensor-core products: tiles of 128 rows x 64 columns,
+    each one contiguous, zero-padded and already swizzled 16 KB block, stored [row tile][k tile]
+    (`pack_weight`).  A stage of a product then reads its weights as one sequential block of HBM.
+    `up_tile_offset` > 0 marks a gated pair: the gate matrix's row tiles first, the up matrix's row tiles
+    from there on (`rows` counts one of the two)."""
+
+    def __init__(self, tiles: torch.Tensor, rows: int, cols: int, up_tile_offset: int = 0):
+        self.tiles, self.rows, self.cols, self.up_tile_offset = tiles, int(rows), int(cols), int(up_tile_offset)
+
+    @property
+    def n_tiles(self) -> int:
+        return self.tiles.shape[0] * self.tiles.shape[1]
+
+    @property
+    def device(self):
+        return self.tiles.device
+
+    def nbytes(self) -> int:
+        return self.tiles.numel() * 2
+
+    def first_rows(self, rows: int) -> "PackedWeight":
+        """The matrix of the first `rows` rows (shares storage; a last tile may hold further rows, which
+        the product's epilogue leaves out)."""
+        if rows > self.rows or self.up_tile_offset:
+            raise KernelError(f"first_rows({rows}) of a packed matrix of {self.rows} rows")
+        return PackedWeight(self.tiles[: (rows + 127) // 128], rows, self.cols)
+
+
+def pack_weight(w: torch.Tensor) -> PackedWeight:
+    """Row-major bfloat16 [N, K] (K a multiple of 8) -> PackedWeight."""
+    _need(w, "weight to pack", torch.bfloat16)
+    if w.dim() != 2 or w.shape[1] % 8:
+        raise KernelError(f"pack_weight: a matrix whose width is a multiple of 8 is needed, got {tuple(w.shape)}")
+    N, K = w.shape
+    tiles = torch.empty(((N + 127) // 128, (K + 63) // 64, 128, 64), dtype=torch.bfloat16, device=w.device)
+    _check(library("elementwise").jb_pack_weight_bf16(_ptr(w), N, K, _ptr(tiles), _stream()), "pack_weight")
+    return PackedWeight(tiles, N, K)
+
+
+def pack_gated(gate: torch.Tensor, up: torch.Tensor) -> PackedWeight:
+    """Gate and up matrices of equal shape as one PackedWeight (gate tiles, then up tiles)."""
+    if gate.shape != up.shape:
+        raise KernelError(f"pack_gated: shapes {tuple(gate.shape)} and {tuple(up.shape)} differ")
+    g, u = pack_weight(gate), pack_weight(up)
+    return PackedWeight(torch.cat([g.tiles, u.tiles], dim=0), gate.shape[0], gate.shape[1], g.tiles.shape[0])
+
+
 def split_k_for(T: int, N: int, K: int) -> int:
     """How many slices of K a weight-streaming product (few tokens) is cut into
     so that enough CTAs are in flight; 1 for prefill-sized T."""
@@ -238,25 +286,27 @@ def _pair_defines():
     return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "store",
+def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "store",
               split_k: Optional[int] = None, pair: Optional[bool] = None) -> None:
-    """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation.
+    """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation; w packed (`pack_weight`).
     mode "store": y[T, N] = result (bf16 or float32 by y's dtype);
     mode "add":   y[T, N] += result, y float32 (K may be split, sums meet by atomic adds);
-    mode "swiglu": w = [2N, K] (gate rows over up rows), y[T, N] = silu(gate) * up in bf16."""
+    mode "swiglu": w a gated pair (`pack_gated`), y[T, N] = silu(gate) * up in bf16."""
     T, K = x.shape
     _need(x, "gemm x", torch.bfloat16)
-    _need(w, "gemm w", torch.bfloat16)
     _need(y, "gemm y")
+    if not isinstance(w, PackedWeight):
+        raise KernelError("gemm: the weight must be packed (ops.pack_weight / ops.pack_gated)")
+    if w.cols != K:
+        raise KernelError(f"gemm: weight of {w.rows} x {w.cols} does not fit K = {K}")
+    N = w.rows
     if mode == "swiglu":
-        N = w.shape[0] // 2
         code, want = 3, torch.bfloat16
-        if w.shape != (2 * N, K):
-            raise KernelError(f"gemm swiglu: weight {tuple(w.shape)} is not [2N, {K}]")
+        if not w.up_tile_offset:
+            raise KernelError("gemm swiglu: the weight is no gated pair (ops.pack_gated)")
     else:
-        N = w.shape[0]
-        if w.shape != (N, K):
-            raise KernelError(f"gemm: weight {tuple(w.shape)} does not fit K = {K}")
+        if w.up_tile_offset:
+            raise KernelError(f"gemm {mode}: the weight is a gated pair")
         if mode == "add":
             code, want = 2, torch.float32
         elif mode == "store":
@@ -269,14 +319,14 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, mode: str = "st
         pair = _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS and split_k in (None, 1)
     if pair:
         _check(library("gemm_bf16_tc2", _pair_defines()).jb_gemm_bf16_pair(
-            _ptr(x), _ptr(w), _ptr(y), T, N, K, N, code, _ptr(kernel_status(x.device)), _stream()),
-            "gemm_bf16_pair")
+            _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
+            _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
     if split_k is None:
         split_k = split_k_for(T, N, K) if code == 2 else 1
     _check(library("gemm_bf16_tc", _gemm_defines()).jb_gemm_bf16(
-        _ptr(x), _ptr(w), _ptr(y), T, N, K, N, code, int(split_k), _ptr(kernel_status(x.device)), _stream()),
-        "gemm_bf16")
+        _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
+        int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
 
 
 def gemm_qkv_rope_supported(T: int, hd: int) -> bool:
@@ -288,7 +338,7 @@ def gemm_qkv_rope_supported(T: int, hd: int) -> bool:
 _QKV_FUSED = os.environ.get("JANUS_QKV_FUSED", "1") != "0"   # 0: projection, then rotation and cache append apart
 
 
-def gemm_qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, cos_sin: torch.Tensor,
+def gemm_qkv_rope_cache(x: torch.Tensor, w: PackedWeight, q_out: torch.Tensor, cos_sin: torch.Tensor,
                         positions: torch.Tensor, dest: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
                         nh: int, nkv: int, hd: int, page_size: int) -> None:
     """The stacked q/k/v projection x[T, K] . w[(nh + 2 nkv) hd, K]^T on CTA pairs with its consumers fused
@@ -296,7 +346,8 @@ def gemm_qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, c
     cache at rows dest, all bfloat16 from the float32 accumulators."""
     T, K = x.shape
     _need(x, "qkv x", torch.bfloat16)
-    _need(w, "qkv w", torch.bfloat16, ((nh + 2 * nkv) * hd, K))
+    if not isinstance(w, PackedWeight) or (w.rows, w.cols) != ((nh + 2 * nkv) * hd, K) or w.up_tile_offset:
+        raise KernelError(f"qkv: a packed weight of {(nh + 2 * nkv) * hd} x {K} is needed")
     _need(q_out, "q_out", torch.bfloat16, (T, nh * hd))
     _need(cos_sin, "rope table", torch.float32)
     if cos_sin.shape[1:] != (hd // 2, 2):
@@ -308,7 +359,8 @@ def gemm_qkv_rope_cache(x: torch.Tensor, w: torch.Tensor, q_out: torch.Tensor, c
     if k_cache.shape[1:] != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
         raise KernelError(f"qkv: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
     _check(library("gemm_bf16_tc2", _pair_defines()).jb_gemm_bf16_pair_qkv_rope(
-        _ptr(x), _ptr(w), T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache), _ptr(cos_sin), _ptr(positions), _ptr(dest),
+        _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+        _ptr(cos_sin), _ptr(positions), _ptr(dest),
         nh, nkv, hd, page_size, _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair_qkv_rope")
 
 

@@ -54,8 +54,7 @@ class GQAttention(Mixer):
     def load(self, q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, o: torch.Tensor) -> None:
         self.qkv.load([q, k, v])
         self.o.load([o])
-        self.q_only = Linear(self.hidden_size, self.q_width, self.dtype, self.device)
-        self.q_only.weight = self.qkv.weight[: self.q_width]
+        self.q_only = self.qkv.first_rows(self.q_width)
 
     def scratch_to_clear(self, ctx, tokens: int, writes_cache: bool = True) -> Optional[torch.Tensor]:
         """The q/k/v buffer, if this step's projection adds K slices into it (decode-sized

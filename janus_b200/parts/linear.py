@@ -35,7 +35,7 @@ class Linear:
         _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
-        self.weight: Optional[torch.Tensor] = None
+        self.weight = None   # float32: [out, in] row-major; bfloat16: ops.PackedWeight
 
     def load(self, tensors: Sequence[torch.Tensor]) -> None:
         parts = [_to_engine(t, self.dtype, self.device) for t in tensors]
@@ -43,11 +43,21 @@ class Linear:
         if tuple(w.shape) != (self.out_features, self.in_features):
             raise ValueError(f"weight of shape {tuple(w.shape)} does not fit "
                              f"({self.out_features}, {self.in_features})")
-        self.weight = w
+        # bfloat16 products stream their weights as packed tiles (ops.PackedWeight); float32 stays row-major
+        self.weight = ops.pack_weight(w) if self.dtype == torch.bfloat16 else w
 
-    def share(self, other: "Linear") -> None:
-        """Use another product's storage (a head tied to the embedding)."""
-        self.weight = other.weight
+    def load_row_major(self, w: torch.Tensor) -> None:
+        """A matrix that is already on the device in the engine dtype (a head tied to the embedding: the
+        float32 engine uses the embedding's storage as it is, the bfloat16 engine a packed copy)."""
+        if tuple(w.shape) != (self.out_features, self.in_features):
+            raise ValueError(f"weight of shape {tuple(w.shape)} does not fit ({self.out_features}, {self.in_features})")
+        self.weight = ops.pack_weight(w) if self.dtype == torch.bfloat16 else w
+
+    def first_rows(self, rows: int) -> "Linear":
+        """The product with the first `rows` output features only (shares storage)."""
+        sub = Linear(self.in_features, rows, self.dtype, self.device)
+        sub.weight = self.weight.first_rows(rows) if self.dtype == torch.bfloat16 else self.weight[:rows]
+        return sub
 
     def meets_by_adds(self, tokens: int, y_dtype: torch.dtype) -> bool:
         """Whether `forward` into a float32 `y` for this many tokens cuts K into slices that
@@ -87,14 +97,15 @@ class GatedLinear:
         _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
-        self.weight: Optional[torch.Tensor] = None   # [2 * out, in]
+        self.weight = None   # float32: [2 * out, in] row-major; bfloat16: a packed gated pair
 
     def load(self, gate: torch.Tensor, up: torch.Tensor) -> None:
-        w = torch.cat([_to_engine(gate, self.dtype, self.device), _to_engine(up, self.dtype, self.device)], dim=0)
-        if tuple(w.shape) != (2 * self.out_features, self.in_features):
-            raise ValueError(f"gate/up weights of shape {tuple(w.shape)} do not fit "
-                             f"(2*{self.out_features}, {self.in_features})")
-        self.weight = w
+        g, u = _to_engine(gate, self.dtype, self.device), _to_engine(up, self.dtype, self.device)
+        for t in (g, u):
+            if tuple(t.shape) != (self.out_features, self.in_features):
+                raise ValueError(f"gate/up weight of shape {tuple(t.shape)} does not fit "
+                                 f"({self.out_features}, {self.in_features})")
+        self.weight = ops.pack_gated(g, u) if self.dtype == torch.bfloat16 else torch.cat([g, u], dim=0)
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, ctx) -> None:
         if self.dtype == torch.float32:

@@ -284,6 +284,7 @@ def bf16_inputs(T, N, K, seed):
 def test_gemm_bf16_store_and_add(ops, T, N, K):
     x, w = bf16_inputs(T, N, K, T + N)
     ref = x.double().cpu() @ w.double().cpu().T
+    w = ops.pack_weight(w)
     y16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
     ops.gemm_bf16(x, w, y16)
     close(y16, ref, 6e-3)
@@ -304,7 +305,7 @@ def test_gemm_bf16_swiglu(ops, T, I, K):
     x, w = bf16_inputs(T, 2 * I, K, T + I)
     w = (w.float() * 3).to(torch.bfloat16)
     y = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
-    ops.gemm_bf16(x, w, y, mode="swiglu")
+    ops.gemm_bf16(x, ops.pack_gated(w[:I].contiguous(), w[I:].contiguous()), y, mode="swiglu")
     ref = P.swiglu_ffn(x.double().cpu(), w[:I].double().cpu(), w[I:].double().cpu(), torch.eye(I, dtype=torch.float64))
     close(y, ref, 6e-3)
     ops.check_kernel_status(torch.device(DEV))
@@ -317,6 +318,7 @@ def test_gemm_bf16_cta_pairs(ops, T, N, K):
     ragged token counts, widths that are no multiple of 256, a K tail, several tiles per pair."""
     x, w = bf16_inputs(T, N, K, T + N + 1)
     ref = x.double().cpu() @ w.double().cpu().T
+    w = ops.pack_weight(w)
     y16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
     ops.gemm_bf16(x, w, y16, pair=True)
     close(y16, ref, 6e-3)
@@ -336,7 +338,7 @@ def test_gemm_bf16_cta_pairs_swiglu(ops, T, I, K):
     x, w = bf16_inputs(T, 2 * I, K, T + I + 1)
     w = (w.float() * 3).to(torch.bfloat16)
     y = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
-    ops.gemm_bf16(x, w, y, mode="swiglu", pair=True)
+    ops.gemm_bf16(x, ops.pack_gated(w[:I].contiguous(), w[I:].contiguous()), y, mode="swiglu", pair=True)
     ref = P.swiglu_ffn(x.double().cpu(), w[:I].double().cpu(), w[I:].double().cpu(), torch.eye(I, dtype=torch.float64))
     close(y, ref, 6e-3)
     ops.check_kernel_status(torch.device(DEV))
@@ -357,7 +359,7 @@ def test_gemm_qkv_with_rotation_and_cache_append(ops, T, nh, nkv, hd, K):
     kc = torch.zeros(n_pages, nkv, PAGE, hd, device=DEV, dtype=torch.bfloat16)
     vc = torch.zeros_like(kc)
     q = torch.full((T, nh * hd), float("nan"), device=DEV, dtype=torch.bfloat16)
-    ops.gemm_qkv_rope_cache(x, w, q, table, positions, dest, kc, vc, nh, nkv, hd, PAGE)
+    ops.gemm_qkv_rope_cache(x, ops.pack_weight(w), q, table, positions, dest, kc, vc, nh, nkv, hd, PAGE)
     ops.check_kernel_status(torch.device(DEV))
     y = x.double().cpu() @ w.double().cpu().T
     c, s_ = P.rope_cos_sin(positions.cpu(), inv)
@@ -393,11 +395,13 @@ def test_kernels_write_nothing_outside_their_outputs(ops, T):
     widths that leave the last tile of every kernel partly empty."""
     N, K, I, nh, nkv, hd = 200, 120, 104, 5, 5, 40
     x, w = bf16_inputs(T, N, K, T)
+    w = ops.pack_weight(w)
     for dtype, mode in ((torch.bfloat16, "store"), (torch.float32, "store"), (torch.float32, "add")):
         buf, y, pad = _guarded((T, N), dtype, 7.0)
         ops.gemm_bf16(x, w, y, mode=mode)
         assert _guards_intact(buf, pad, 7.0), (T, dtype, mode)
     _, wg = bf16_inputs(T, 2 * I, K, T + 1)
+    wg = ops.pack_gated(wg[:I].contiguous(), wg[I:].contiguous())
     buf, act, pad = _guarded((T, I), torch.bfloat16, 7.0)
     ops.gemm_bf16(x, wg, act, mode="swiglu")
     assert _guards_intact(buf, pad, 7.0)
@@ -440,10 +444,34 @@ def test_kernels_write_nothing_outside_their_outputs(ops, T):
 
 
 def test_gemm_bf16_refuses_what_it_cannot_take(ops):
-    x = torch.zeros(4, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
-    w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)
-    with pytest.raises(Exception, match="size not supported"):
-        ops.gemm_bf16(x, w, torch.empty(4, 16, device=DEV, dtype=torch.bfloat16))
+    w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
+    with pytest.raises(Exception, match="multiple of 8"):
+        ops.pack_weight(w)
+    x = torch.zeros(4, 104, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(Exception, match="packed"):                    # a row-major matrix is no weight of a product
+        ops.gemm_bf16(x, torch.zeros(16, 104, device=DEV, dtype=torch.bfloat16),
+                      torch.empty(4, 16, device=DEV, dtype=torch.bfloat16))
+    with pytest.raises(Exception, match="does not fit"):
+        ops.gemm_bf16(x, ops.pack_weight(torch.zeros(16, 96, device=DEV, dtype=torch.bfloat16)),
+                      torch.empty(4, 16, device=DEV, dtype=torch.bfloat16))
+
+
+@pytest.mark.parametrize("N, K", [(1, 8), (200, 120), (128, 64), (300, 4096)])
+def test_pack_weight_layout(ops, N, K):
+    """Tiles of 128 x 64, zero-padded, [row tile][k tile]; chunk c (8 values) of row r at chunk c ^ (r & 7)."""
+    w = torch.randn(N, K, device=DEV).to(torch.bfloat16)
+    packed = ops.pack_weight(w)
+    rt, kt = (N + 127) // 128, (K + 63) // 64
+    assert tuple(packed.tiles.shape) == (rt, kt, 128, 64) and (packed.rows, packed.cols) == (N, K)
+    padded = torch.zeros(rt * 128, kt * 64, dtype=torch.bfloat16)
+    padded[:N, :K] = w.cpu()
+    tiles = padded.view(rt, 128, kt, 8, 8).permute(0, 2, 1, 3, 4)            # [rt, kt, row, chunk, 8]
+    r = torch.arange(128) & 7
+    src = torch.arange(8)[None, :] ^ r[:, None]                               # chunk stored at position p
+    want = torch.gather(tiles, 3, src[None, None, :, :, None].expand(rt, kt, 128, 8, 8)).reshape(rt, kt, 128, 64)
+    assert torch.equal(packed.tiles.cpu(), want)
+    sub = packed.first_rows(min(N, 130))
+    assert sub.tiles.data_ptr() == packed.tiles.data_ptr() and sub.rows == min(N, 130)
 
 
 # ---------------------------------------------------------------- sampling
