@@ -3,23 +3,29 @@
 // (-DJB_HEAD_DIM = 64 or 128); other head sizes and group sizes that are no
 // power of two take the mma.sync kernel of attention_bf16.cu.
 //
-// One CTA owns 128 rows = (token, query head of one kv group) pairs of one
-// sequence and walks the causal range of 64-key pages:
-//   warp 0     TMA producer: the Q tile once (4-D tensor map: dim, group head, kv head, token),
+// One CTA owns one or two tiles of 128 rows = (token, query head of one kv group) pairs of one sequence (two:
+// next to each other in the sequence) and walks their causal range of 64-key pages once: a page that TMA has
+// brought in then serves both tiles' products (the copy engine's rate per SM, about 80 GB/s for such boxes,
+// is what the one-tile CTA waits for most: 750 of 900 cycles per page).  Two tiles are taken when that still
+// leaves CTAs enough to fill the SMs three times over.
+//   warp 0     TMA producer: the two Q tiles once (4-D tensor map: dim, group head, kv head, token),
 //              then K and V pages into a 3-stage ring (128-byte swizzle)
-//   warp 1     one lane issues tcgen05.mma:  S_j = Q . K_j^T  into one of two TMEM buffers,
-//              O += P_j . V_j  into a float32 accumulator in TMEM; V is the MN-major operand (its rows are keys)
-//   warps 2-5  one thread per row: read S_j from TMEM, mask, softmax in float32 (exp2) against a
+//   warp 1     one lane issues tcgen05.mma:  S_j = Q . K_j^T  of each tile into one of its two TMEM buffers,
+//              O += P_j . V_j  into each tile's float32 accumulator in TMEM; V is the MN-major operand
+//   warps 2-5 (first tile), 6-9 (second tile)
+//              one thread per row: read S_j from TMEM, mask, softmax in float32 (exp2) against a
 //              reference maximum, write P_j as bf16 into swizzled shared memory.  The reference maximum
 //              is raised, and O in TMEM rescaled, only when a row's maximum has grown by more than 2^8
 //              since it was set (P then stays below 256, exact enough in bf16 and harmless in float32).
-// so that the tensor core computes S_{j+1} and the P.V product of block j-1 while the softmax of block j runs.
+// The tensor core computes S_{j+1} of both tiles and the P.V products of block j while the two groups of
+// softmax warps work, each on its own tile.  TMEM per tile: 2 x 64 columns of S and 128 of O.
 // Every mbarrier wait is bounded in time and reports through `*status` (codes 11-13).
 // Formulas: crates/janus-engine/src/compute/shaders/attention.wgsl:96-115,170-185,
 // softmax.wgsl:29-50; kv head of query head h is floor(h * nkv / nh).
 #include <cuda.h>
 #include <math_constants.h>
 #include <stdio.h>
+#include <stdlib.h>
 
 #include "common.cuh"
 
@@ -37,16 +43,20 @@ constexpr int NH64 = HD / 64;          // 64-column halves of a row
 constexpr int BM = 128;                // rows per CTA = TMEM lanes
 constexpr int PAGE = 64;               // keys per block
 constexpr int STAGES = 3;
-constexpr int THREADS = 192;
+constexpr int MAX_NT = 2;              // row tiles per CTA: 1 or 2 (template parameter NT of the kernel)
+constexpr int threads_for(int nt) { return 64 + nt * 128; }
 constexpr int Q_BYTES = NH64 * BM * 128;
 constexpr int K_BYTES = NH64 * PAGE * 128, V_BYTES = K_BYTES;
 constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
 constexpr int P_BYTES = BM * 128;      // 128 rows x 64 keys bf16
-constexpr int TMEM_S0 = 0, TMEM_O0 = 128;
-constexpr int TMEM_COLS = 256;         // S: 2 x 64 columns, O: HD <= 128 columns
+// TMEM: S of tile w, buffer b at w * 128 + b * 64; O of tile w at NT * 128 + w * 128 (256 columns per tile)
 constexpr float RESCALE_LOG2 = 8.0f;   // the reference maximum follows a row's maximum when it has grown by 2^8
-constexpr int N_BARS = 1 + 2 * STAGES + 2 + 2 + 2 + 1;
-constexpr int SMEM_BYTES = Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES + N_BARS * 8 + 16 + 1024;
+constexpr int TILE_BARS = 2 + 2 + 2 + 1 + 1;   // per tile: s_full[2], s_free[2], p_full[2], o_full, o_done
+constexpr int bars_for(int nt) { return 1 + 2 * STAGES + nt * TILE_BARS; }
+constexpr int smem_for(int nt) {
+  return nt * Q_BYTES + STAGES * STAGE_BYTES + nt * 2 * P_BYTES + bars_for(nt) * 8 + 16 + 1024;
+}
+static_assert(smem_for(MAX_NT) <= 232448, "shared memory of one CTA");
 constexpr float LOG2E = 1.4426950408889634f;
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;
 
@@ -171,21 +181,31 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
-__global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
+template <int NT>
+__global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window,
     float scale_log2, int* __restrict__ status) {
+  constexpr int N_BARS = bars_for(NT), TMEM_COLS = NT * 256, TMEM_S0 = 0, TMEM_O0 = NT * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  const uint32_t q_s = smem_u32(smem);
-  const uint32_t kv_s = q_s + Q_BYTES;
-  const uint32_t p_s = kv_s + STAGES * STAGE_BYTES;
-  uint64_t* bars = (uint64_t*)(smem + Q_BYTES + STAGES * STAGE_BYTES + 2 * P_BYTES);
+  const uint32_t q_s = smem_u32(smem);                       // [NT] Q tiles
+  const uint32_t kv_s = q_s + NT * Q_BYTES;                  // ring of K/V pages
+  const uint32_t p_s = kv_s + STAGES * STAGE_BYTES;          // P tiles: tile w, buffer b at (w * 2 + b) * P_BYTES
+  uint64_t* bars = (uint64_t*)(smem + NT * Q_BYTES + STAGES * STAGE_BYTES + NT * 2 * P_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + N_BARS);
   const uint32_t bar0 = smem_u32(bars);
-  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * STAGES, s_full = kv_empty + 8 * STAGES,
-                 s_free = s_full + 16, p_full = s_free + 16, o_full = p_full + 16;
+  const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * STAGES, tile_bars = kv_empty + 8 * STAGES;
+  // barriers of tile w: s_full[b], s_free[b], p_full[b], o_full
+  auto s_full = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + b); };
+  auto s_free = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + 2 + b); };
+  auto p_full = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + 4 + b); };
+  auto o_full = [&](int w) { return tile_bars + 8 * (w * TILE_BARS + 6); };
+  // o_full completes a phase per block, and a thread that never had to rescale has watched none of them: by
+  // parity alone it cannot tell the last block's phase from the one two blocks earlier.  The end of a tile's
+  // last P.V product has a barrier of its own.
+  auto o_done = [&](int w) { return tile_bars + 8 * (w * TILE_BARS + 7); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   jb::pdl_launch_dependents();
@@ -195,12 +215,15 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
       mbar_init(kv_full + 8 * s, 1);
       mbar_init(kv_empty + 8 * s, 1);
     }
-    for (int b = 0; b < 2; ++b) {
-      mbar_init(s_full + 8 * b, 1);
-      mbar_init(s_free + 8 * b, 128);
-      mbar_init(p_full + 8 * b, 128);
+    for (int w = 0; w < NT; ++w) {
+      for (int b = 0; b < 2; ++b) {
+        mbar_init(s_full(w, b), 1);
+        mbar_init(s_free(w, b), 128);
+        mbar_init(p_full(w, b), 128);
+      }
+      mbar_init(o_full(w), 1);
+      mbar_init(o_done(w), 1);
     }
-    mbar_init(o_full, 1);
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {
@@ -219,22 +242,26 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
   const int G = nh / nkv;
   const int tpt = BM / G;  // tokens per tile
   const int seq = blockIdx.z, kvh = blockIdx.y;
-  const int tile = gridDim.x - 1 - blockIdx.x;  // the longest key ranges start first
+  const int pair = gridDim.x - 1 - blockIdx.x;  // the longest key ranges start first
   const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
-  const int tok0 = tile * tpt;
-  const bool active = tok0 < q_len;  // uniform for the CTA
-  const int n_tok = active ? min(tpt, q_len - tok0) : 0;
+  const int tok_first = pair * NT * tpt;        // first token of the first tile
+  const bool active = tok_first < q_len;        // uniform for the CTA
   const int len = kv_len[seq];
-  const int pos0 = len - q_len + tok0;
-  const int kb_end = active ? (pos0 + n_tok - 1) / PAGE : -1;
-  const int kb_start = (active && window > 0) ? max(0, pos0 - window + 1) / PAGE : 0;
+  const int n_tok_all = active ? min(NT * tpt, q_len - tok_first) : 0;   // tokens of both tiles together
+  const int pos_first = len - q_len + tok_first;
+  // both tiles walk the same pages, from the first page any of their rows sees to the last; rows mask what is
+  // not theirs (the first tile's rows see nothing of the last page or two)
+  const int kb_end = active ? (pos_first + n_tok_all - 1) / PAGE : -1;
+  const int kb_start = (active && window > 0) ? max(0, pos_first - window + 1) / PAGE : 0;
   const int nb = kb_end - kb_start + 1;
 
   if (active && warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(q_full, Q_BYTES);
-      for (int h = 0; h < NH64; ++h) tma_load_4d(q_s + h * BM * 128, &map_q, q_full, h * 64, 0, kvh, qs + tok0);
+      mbar_expect_tx(q_full, NT * Q_BYTES);
+      for (int w = 0; w < NT; ++w)   // a tile past the sequence's end reads rows that no one uses (or zeros past the tensor)
+        for (int h = 0; h < NH64; ++h)
+          tma_load_4d(q_s + w * Q_BYTES + h * BM * 128, &map_q, q_full, h * 64, 0, kvh, qs + tok_first + w * tpt);
       const int* pages = block_table + (size_t)seq * max_pages;
       for (int j = 0; j < nb; ++j) {
         const int s = j % STAGES;
@@ -256,16 +283,19 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
       auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES, b = j & 1;
         if (!mbar_wait(kv_full + 8 * s, (j / STAGES) & 1, status, 12)) return false;
-        if (!mbar_wait(s_free + 8 * b, ((j >> 1) & 1) ^ 1, status, 12)) return false;
-        tc_fence_after();
         const uint32_t stage = kv_s + s * STAGE_BYTES;
+        for (int w = 0; w < NT; ++w) {
+          if (!mbar_wait(s_free(w, b), ((j >> 1) & 1) ^ 1, status, 12)) return false;
+          tc_fence_after();
 #pragma unroll
-        for (int h = 0; h < NH64; ++h) {
-          const uint64_t a = desc_k_sw128(q_s + h * BM * 128), k = desc_k_sw128(stage + h * PAGE * 128);
+          for (int h = 0; h < NH64; ++h) {
+            const uint64_t a = desc_k_sw128(q_s + w * Q_BYTES + h * BM * 128), k = desc_k_sw128(stage + h * PAGE * 128);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma(tmem + TMEM_S0 + b * 64, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
+            for (int ks = 0; ks < 4; ++ks)
+              umma(tmem + TMEM_S0 + w * 128 + b * 64, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
+          }
+          umma_commit(s_full(w, b));   // a tile's softmax starts while the other tile's scores are computed
         }
-        umma_commit(s_full + 8 * b);
         return true;
       };
       if (ok) ok = issue_s(0);
@@ -273,40 +303,46 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
         if (j + 1 < nb) ok = issue_s(j + 1);  // the tensor core works on S_{j+1} while the softmax of block j runs
         if (!ok) break;
         const int s = j % STAGES, b = j & 1;
-        ok = mbar_wait(p_full + 8 * b, (j >> 1) & 1, status, 12);  // P_j is written and O is rescaled if it had to be
-        if (!ok) break;
-        tc_fence_after();
         const uint32_t v_base = kv_s + s * STAGE_BYTES + K_BYTES;
-        const uint64_t p = desc_k_sw128(p_s + b * P_BYTES);
+        for (int w = 0; w < NT && ok; ++w) {
+          ok = mbar_wait(p_full(w, b), (j >> 1) & 1, status, 12);  // P_j is written and O is rescaled if it had to be
+          if (!ok) break;
+          tc_fence_after();
+          const uint64_t p = desc_k_sw128(p_s + (w * 2 + b) * P_BYTES);
 #pragma unroll
-        for (int ks = 0; ks < 4; ++ks)  // 16 keys per step = two 8-key atoms of 1024 bytes
-          umma(tmem + TMEM_O0, p + 2 * ks, desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o, (j | ks) ? 1u : 0u);
-        umma_commit(o_full);
-        umma_commit(kv_empty + 8 * s);
+          for (int ks = 0; ks < 4; ++ks)  // 16 keys per step = two 8-key atoms of 1024 bytes
+            umma(tmem + TMEM_O0 + w * 128, p + 2 * ks, desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o,
+                 (j | ks) ? 1u : 0u);
+          umma_commit(o_full(w));
+          if (j == nb - 1) umma_commit(o_done(w));
+        }
+        if (ok) umma_commit(kv_empty + 8 * s);   // both tiles' products have read the stage
       }
     }
   } else if (active) {
-    // ---------------- softmax, one thread per row ----------------
-    const int quarter = warp & 3;
+    // ---------------- softmax, one thread per row, four warps per tile ----------------
+    const int w = (warp - 2) >> 2;             // tile of this warp
+    const int quarter = warp & 3;              // the 32 TMEM lanes this warp may touch
     const int row = quarter * 32 + lane;
-    const int tl = row / G;
-    const bool valid = tl < n_tok;
-    const int row_pos = valid ? pos0 + tl : -1;
+    const int tl = w * tpt + row / G;          // token within the pair
+    const bool valid = tl < n_tok_all;
+    const int row_pos = valid ? pos_first + tl : -1;
     const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_col = TMEM_S0 + w * 128, o_col = TMEM_O0 + w * 128;
     float m_ref = -CUDART_INF_F, l = 0.0f;   // l is the row sum relative to m_ref
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
       const int b = j & 1;
-      ok = mbar_wait(s_full + 8 * b, (j >> 1) & 1, status, 13);
+      ok = mbar_wait(s_full(w, b), (j >> 1) & 1, status, 13);
       if (!ok) break;
       tc_fence_after();
       uint32_t sr[64];
 #pragma unroll
-      for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(lane_addr + TMEM_S0 + b * 64 + c0, sr + c0);
+      for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(lane_addr + s_col + b * 64 + c0, sr + c0);
       tmem_ld_wait();
       tc_fence_before();
-      mbar_arrive(s_free + 8 * b);
+      mbar_arrive(s_free(w, b));
       const int key0 = (kb_start + j) * PAGE;
       if (key0 + PAGE - 1 > row_pos || key0 < row_lo) {   // only blocks that touch the causal edge or the window
 #pragma unroll
@@ -324,18 +360,18 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mx);
         if (j > 0) {
-          ok = mbar_wait(o_full, (j - 1) & 1, status, 13);  // the P.V product of block j-1 has landed in O
+          ok = mbar_wait(o_full(w), (j - 1) & 1, status, 13);  // the P.V product of block j-1 has landed in O
           if (!ok) break;
           tc_fence_after();
           const float corr = m_new == -CUDART_INF_F ? 1.0f : exp2f(m_ref - m_new);  // 0 if nothing was seen before
 #pragma unroll
           for (int c0 = 0; c0 < HD; c0 += 16) {
             uint32_t r[16];
-            tmem_ld16(lane_addr + TMEM_O0 + c0, r);
+            tmem_ld16(lane_addr + o_col + c0, r);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
-            tmem_st16(lane_addr + TMEM_O0 + c0, r);
+            tmem_st16(lane_addr + o_col + c0, r);
           }
           tmem_st_wait();
           l *= corr;
@@ -345,35 +381,35 @@ __global__ void __launch_bounds__(THREADS, 1) prefill_tc_kernel(
       const float neg_ref = m_ref == -CUDART_INF_F ? 0.0f : -m_ref;
       float sum = 0.0f;
       // P_j as bf16 into the swizzled tile: 16-byte chunk c of row r lies at r*128 + ((c ^ (r & 7)) * 16)
-      const uint32_t p_row = p_s + b * P_BYTES + row * 128;
+      const uint32_t p_row = p_s + (w * 2 + b) * P_BYTES + row * 128;
 #pragma unroll
       for (int c = 0; c < 8; ++c) {
-        uint32_t w[4];
+        uint32_t pk[4];
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
           const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c * 8 + 2 * e]), scale_log2, neg_ref));
           const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c * 8 + 2 * e + 1]), scale_log2, neg_ref));
           sum += p0 + p1;
-          w[e] = pack_bf16(p0, p1);
+          pk[e] = pack_bf16(p0, p1);
         }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c ^ (row & 7)) << 4)), "r"(w[0]),
-                     "r"(w[1]), "r"(w[2]), "r"(w[3])
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c ^ (row & 7)) << 4)), "r"(pk[0]),
+                     "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
                      : "memory");
       }
       l += sum;
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
       tc_fence_before();
-      mbar_arrive(p_full + 8 * b);
+      mbar_arrive(p_full(w, b));
     }
-    if (ok && nb > 0) ok = mbar_wait(o_full, (nb - 1) & 1, status, 13);
+    if (ok && nb > 0) ok = mbar_wait(o_done(w), 0, status, 13);
     if (ok) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      bf16* dst = out + ((size_t)(qs + tok0 + (valid ? tl : 0)) * nh + kvh * G + row % G) * HD;
+      bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * HD;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 16) {
         uint32_t r[16];
-        tmem_ld16(lane_addr + TMEM_O0 + c0, r);   // warp-wide: rows without a token load too and store nothing
+        tmem_ld16(lane_addr + o_col + c0, r);   // warp-wide: rows without a token load too and store nothing
         tmem_ld_wait();
         if (valid) {
           uint4 w0, w1;
@@ -456,14 +492,33 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return JB_ERR_TENSORMAP;
   }
+  // Two row tiles per CTA share every page they load, which pays when there are CTAs enough to fill the SMs
+  // several times over; with fewer the finer one-tile CTAs balance the causal triangle better.
+  const int n_tiles = (max_q_len + tpt - 1) / tpt;
+  const long long ctas_of_pairs = (long long)((n_tiles + 1) / 2) * nkv * n_seqs;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  bool pairs = ctas_of_pairs >= 3LL * sms;
+  if (const char* e = getenv("JANUS_ATTN_TC_TILES")) {   // 1 or 2: tiles per CTA whatever the size (for tests and measurements)
+    if (e[0] == '1') pairs = false;
+    if (e[0] == '2') pairs = true;
+  }
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+    cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_for(1));
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_for(2));
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
-  dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_seqs);
-  jb::Launch cfg(grid, dim3(THREADS), SMEM_BYTES, stream);
-  return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
+  if (pairs) {
+    dim3 grid((n_tiles + 1) / 2, nkv, n_seqs);
+    jb::Launch cfg(grid, dim3(threads_for(2)), smem_for(2), stream);
+    return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<2>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
+                                   nkv, max_pages, window, scale * LOG2E, status);
+  }
+  dim3 grid(n_tiles, nkv, n_seqs);
+  jb::Launch cfg(grid, dim3(threads_for(1)), smem_for(1), stream);
+  return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<1>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
                                  nkv, max_pages, window, scale * LOG2E, status);
 }
