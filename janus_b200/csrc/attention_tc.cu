@@ -11,10 +11,12 @@
 //   warp 0     TMA producer: the two Q tiles once (4-D tensor map: dim, group head, kv head, token),
 //              then K and V pages into a 3-stage ring (128-byte swizzle)
 //   warp 1     one lane issues tcgen05.mma:  S_j = Q . K_j^T  of each tile into one of its two TMEM buffers,
-//              O += P_j . V_j  into each tile's float32 accumulator in TMEM; V is the MN-major operand
+//              O += P_j . V_j  into each tile's float32 accumulator in TMEM, with P_j read from TMEM (the A
+//              operand of the product) and V as the MN-major operand from shared memory
 //   warps 2-5 (first tile), 6-9 (second tile)
 //              one thread per row: read S_j from TMEM, mask, softmax in float32 (exp2) against a
-//              reference maximum, write P_j as bf16 into swizzled shared memory.  The reference maximum
+//              reference maximum, write P_j as bf16 pairs over the first half of the S buffer it came from
+//              (lane = row, a 32-bit column = two consecutive keys): no tile in shared memory.  The reference maximum
 //              is raised, and O in TMEM rescaled, only when a row's maximum has grown by more than 2^8
 //              since it was set (P then stays below 256, exact enough in bf16 and harmless in float32).
 // The tensor core computes S_{j+1} of both tiles and the P.V products of block j while the two groups of
@@ -48,13 +50,12 @@ constexpr int threads_for(int nt) { return 64 + nt * 128; }
 constexpr int Q_BYTES = NH64 * BM * 128;
 constexpr int K_BYTES = NH64 * PAGE * 128, V_BYTES = K_BYTES;
 constexpr int STAGE_BYTES = K_BYTES + V_BYTES;
-constexpr int P_BYTES = BM * 128;      // 128 rows x 64 keys bf16
 // TMEM: S of tile w, buffer b at w * 128 + b * 64; O of tile w at NT * 128 + w * 128 (256 columns per tile)
 constexpr float RESCALE_LOG2 = 8.0f;   // the reference maximum follows a row's maximum when it has grown by 2^8
-constexpr int TILE_BARS = 2 + 2 + 2 + 1 + 1;   // per tile: s_full[2], s_free[2], p_full[2], o_full, o_done
+constexpr int TILE_BARS = 2 + 2 + 1 + 1;   // per tile: s_full[2], p_full[2], o_full, o_done
 constexpr int bars_for(int nt) { return 1 + 2 * STAGES + nt * TILE_BARS; }
 constexpr int smem_for(int nt) {
-  return nt * Q_BYTES + STAGES * STAGE_BYTES + nt * 2 * P_BYTES + bars_for(nt) * 8 + 16 + 1024;
+  return nt * Q_BYTES + STAGES * STAGE_BYTES + bars_for(nt) * 8 + 16 + 1024;
 }
 static_assert(smem_for(MAX_NT) <= 232448, "shared memory of one CTA");
 constexpr float LOG2E = 1.4426950408889634f;
@@ -120,6 +121,15 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
       "setp.ne.b32 p, %4, 0;\n\t"
       "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
       ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(acc)
+      : "memory");
+}
+// A operand from tensor memory (lane = row, one 32-bit column = two consecutive bf16 of K)
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t acc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(acc)
       : "memory");
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
@@ -192,20 +202,18 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_s = smem_u32(smem);                       // [NT] Q tiles
   const uint32_t kv_s = q_s + NT * Q_BYTES;                  // ring of K/V pages
-  const uint32_t p_s = kv_s + STAGES * STAGE_BYTES;          // P tiles: tile w, buffer b at (w * 2 + b) * P_BYTES
-  uint64_t* bars = (uint64_t*)(smem + NT * Q_BYTES + STAGES * STAGE_BYTES + NT * 2 * P_BYTES);
+  uint64_t* bars = (uint64_t*)(smem + NT * Q_BYTES + STAGES * STAGE_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + N_BARS);
   const uint32_t bar0 = smem_u32(bars);
   const uint32_t q_full = bar0, kv_full = bar0 + 8, kv_empty = kv_full + 8 * STAGES, tile_bars = kv_empty + 8 * STAGES;
-  // barriers of tile w: s_full[b], s_free[b], p_full[b], o_full
+  // barriers of tile w: s_full[b], p_full[b], o_full, o_done
   auto s_full = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + b); };
-  auto s_free = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + 2 + b); };
-  auto p_full = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + 4 + b); };
-  auto o_full = [&](int w) { return tile_bars + 8 * (w * TILE_BARS + 6); };
+  auto p_full = [&](int w, int b) { return tile_bars + 8 * (w * TILE_BARS + 2 + b); };
+  auto o_full = [&](int w) { return tile_bars + 8 * (w * TILE_BARS + 4); };
   // o_full completes a phase per block, and a thread that never had to rescale has watched none of them: by
   // parity alone it cannot tell the last block's phase from the one two blocks earlier.  The end of a tile's
   // last P.V product has a barrier of its own.
-  auto o_done = [&](int w) { return tile_bars + 8 * (w * TILE_BARS + 7); };
+  auto o_done = [&](int w) { return tile_bars + 8 * (w * TILE_BARS + 5); };
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   jb::pdl_launch_dependents();
@@ -218,7 +226,6 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     for (int w = 0; w < NT; ++w) {
       for (int b = 0; b < 2; ++b) {
         mbar_init(s_full(w, b), 1);
-        mbar_init(s_free(w, b), 128);
         mbar_init(p_full(w, b), 128);
       }
       mbar_init(o_full(w), 1);
@@ -285,7 +292,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
         if (!mbar_wait(kv_full + 8 * s, (j / STAGES) & 1, status, 12)) return false;
         const uint32_t stage = kv_s + s * STAGE_BYTES;
         for (int w = 0; w < NT; ++w) {
-          if (!mbar_wait(s_free(w, b), ((j >> 1) & 1) ^ 1, status, 12)) return false;
+          // (P lies over S in TMEM: the buffer is rewritten only by MMAs issued after the P.V product that read it)
           tc_fence_after();
 #pragma unroll
           for (int h = 0; h < NH64; ++h) {
@@ -308,11 +315,10 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
           ok = mbar_wait(p_full(w, b), (j >> 1) & 1, status, 12);  // P_j is written and O is rescaled if it had to be
           if (!ok) break;
           tc_fence_after();
-          const uint64_t p = desc_k_sw128(p_s + (w * 2 + b) * P_BYTES);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks)  // 16 keys per step = two 8-key atoms of 1024 bytes
-            umma(tmem + TMEM_O0 + w * 128, p + 2 * ks, desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o,
-                 (j | ks) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks)  // P lies over the first 32 columns of its S buffer: 8 columns per 16 keys
+            umma_ts(tmem + TMEM_O0 + w * 128, tmem + TMEM_S0 + w * 128 + b * 64 + ks * 8,
+                    desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o, (j | ks) ? 1u : 0u);
           umma_commit(o_full(w));
           if (j == nb - 1) umma_commit(o_done(w));
         }
@@ -341,8 +347,6 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
 #pragma unroll
       for (int c0 = 0; c0 < 64; c0 += 16) tmem_ld16(lane_addr + s_col + b * 64 + c0, sr + c0);
       tmem_ld_wait();
-      tc_fence_before();
-      mbar_arrive(s_free(w, b));
       const int key0 = (kb_start + j) * PAGE;
       if (key0 + PAGE - 1 > row_pos || key0 < row_lo) {   // only blocks that touch the causal edge or the window
 #pragma unroll
@@ -381,23 +385,18 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
       const float neg_ref = m_ref == -CUDART_INF_F ? 0.0f : -m_ref;
       float sum = 0.0f;
       // P_j as bf16 into the swizzled tile: 16-byte chunk c of row r lies at r*128 + ((c ^ (r & 7)) * 16)
-      const uint32_t p_row = p_s + (w * 2 + b) * P_BYTES + row * 128;
+      // P_j as bf16 pairs over the first 32 columns of this S buffer (its scores are in registers by now)
 #pragma unroll
-      for (int c = 0; c < 8; ++c) {
-        uint32_t pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float p0 = fast_exp2(fmaf(__uint_as_float(sr[c * 8 + 2 * e]), scale_log2, neg_ref));
-          const float p1 = fast_exp2(fmaf(__uint_as_float(sr[c * 8 + 2 * e + 1]), scale_log2, neg_ref));
-          sum += p0 + p1;
-          pk[e] = pack_bf16(p0, p1);
-        }
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(p_row + ((c ^ (row & 7)) << 4)), "r"(pk[0]),
-                     "r"(pk[1]), "r"(pk[2]), "r"(pk[3])
-                     : "memory");
+      for (int c = 0; c < 32; ++c) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), scale_log2, neg_ref));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, neg_ref));
+        sum += p0 + p1;
+        sr[c] = pack_bf16(p0, p1);
       }
       l += sum;
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic-proxy stores -> visible to the tensor core
+      tmem_st16(lane_addr + s_col + b * 64, sr);
+      tmem_st16(lane_addr + s_col + b * 64 + 16, sr + 16);
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(p_full(w, b));
     }

@@ -483,6 +483,13 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
 
 
 # -- tcgen05 prefill attention (head sizes 64 and 128, power-of-two groups) ------------------
+def _attention_tc_defines():
+    """Build-time overrides of the tcgen05 attention for experiments, e.g. JANUS_ATTN_TC_DEFINES="JB_TC_P_IN_TMEM=1";
+    none by default."""
+    text = os.environ.get("JANUS_ATTN_TC_DEFINES", "")
+    return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
+
+
 def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
     import os
     g = nh // max(nkv, 1)
@@ -505,7 +512,7 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
         raise KernelError(f"attention_tc: cache shape {tuple(k_cache.shape)} does not fit [pages, {nkv}, {page_size}, {hd}]")
-    _check(library("attention_tc", {"JB_HEAD_DIM": int(hd)}).jb_attention_tc_prefill(
+    _check(library("attention_tc", dict({"JB_HEAD_DIM": int(hd)}, **_attention_tc_defines())).jb_attention_tc_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
         ctypes.c_float(scale), _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")
