@@ -3,24 +3,22 @@
 // (-DJB_HEAD_DIM = 64 or 128); other head sizes and group sizes that are no
 // power of two take the mma.sync kernel of attention_bf16.cu.
 //
-// One CTA owns one or two tiles of 128 rows = (token, query head of one kv group) pairs of one sequence (two:
-// next to each other in the sequence) and walks their causal range of 64-key pages once: a page that TMA has
-// brought in then serves both tiles' products (the copy engine's rate per SM, about 80 GB/s for such boxes,
-// is what the one-tile CTA waits for most: 750 of 900 cycles per page).  Two tiles are taken when that still
-// leaves CTAs enough to fill the SMs three times over.
-//   warp 0     TMA producer: the two Q tiles once (4-D tensor map: dim, group head, kv head, token),
+// Two kernels.  prefill_tc_kernel: one CTA owns a tile of 128 rows = (token, query head of one kv group)
+// pairs of one sequence and walks its causal range of 64-key pages:
+//   warp 0     TMA producer: the Q tile once (4-D tensor map: dim, group head, kv head, token),
 //              then K and V pages into a 3-stage ring (128-byte swizzle)
-//   warp 1     one lane issues tcgen05.mma:  S_j = Q . K_j^T  of each tile into one of its two TMEM buffers,
-//              O += P_j . V_j  into each tile's float32 accumulator in TMEM, with P_j read from TMEM (the A
+//   warp 1     one lane issues tcgen05.mma:  S_j = Q . K_j^T  into one of two TMEM buffers,
+//              O += P_j . V_j  into a float32 accumulator in TMEM, with P_j read from TMEM (the A
 //              operand of the product) and V as the MN-major operand from shared memory
-//   warps 2-5 (first tile), 6-9 (second tile)
-//              one thread per row: read S_j from TMEM, mask, softmax in float32 (exp2) against a
+//   warps 2-5  one thread per row: read S_j from TMEM, mask, softmax in float32 (exp2) against a
 //              reference maximum, write P_j as bf16 pairs over the first half of the S buffer it came from
 //              (lane = row, a 32-bit column = two consecutive keys): no tile in shared memory.  The reference maximum
 //              is raised, and O in TMEM rescaled, only when a row's maximum has grown by more than 2^8
 //              since it was set (P then stays below 256, exact enough in bf16 and harmless in float32).
-// The tensor core computes S_{j+1} of both tiles and the P.V products of block j while the two groups of
-// softmax warps work, each on its own tile.  TMEM per tile: 2 x 64 columns of S and 128 of O.
+// The tensor core computes S_{j+1} and the P.V product of block j-1 while the softmax of block j runs.
+// Its MMA lane waits 750 of 900 cycles per page for K and V (the copy engine gives about 80 GB/s per SM for
+// such boxes), so prefill_tc128_kernel (below) lets two tiles share what is loaded and takes two pages at a
+// time; it runs whenever it has CTAs enough for every SM.
 // Every mbarrier wait is bounded in time and reports through `*status` (codes 11-13).
 // Formulas: crates/janus-engine/src/compute/shaders/attention.wgsl:96-115,170-185,
 // softmax.wgsl:29-50; kv head of query head h is floor(h * nkv / nh).
@@ -45,7 +43,7 @@ constexpr int NH64 = HD / 64;          // 64-column halves of a row
 constexpr int BM = 128;                // rows per CTA = TMEM lanes
 constexpr int PAGE = 64;               // keys per block
 constexpr int STAGES = 3;
-constexpr int MAX_NT = 2;              // row tiles per CTA: 1 or 2 (template parameter NT of the kernel)
+constexpr int MAX_NT = 1;              // row tiles per CTA of prefill_tc_kernel<NT> (written for 1 or 2; 1 is what runs)
 constexpr int threads_for(int nt) { return 64 + nt * 128; }
 constexpr int Q_BYTES = NH64 * BM * 128;
 constexpr int K_BYTES = NH64 * PAGE * 128, V_BYTES = K_BYTES;
@@ -434,6 +432,259 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   }
 }
 
+// ---------------------------------------------------------------------------
+// Two row tiles per CTA over blocks of 128 keys (two pages): every MMA has N = 128 (an MMA of N = 64 takes as
+// long), S has one 128-column buffer per tile and P lies over its first half, so the two tiles take turns on
+// the tensor core: while one tile's softmax runs, the other's S and P.V products are computed.
+//   tensor core order:  S_A(0) S_B(0) | PV_A(0) S_A(1) | PV_B(0) S_B(1) | PV_A(1) S_A(2) | ...
+// K and V have rings of their own (2 stages of 128 keys each): a K stage is free as soon as both tiles' S
+// products have read it, so the next keys arrive a whole block ahead.
+// TMEM: S of tile w at w * 128, O at 256 + w * 128 (all 512 columns).
+// ---------------------------------------------------------------------------
+constexpr int KB = 2 * PAGE;                       // keys per block
+constexpr int K128_BYTES = NH64 * KB * 128;        // one K (or V) stage
+constexpr int T2_BARS = 1 + 8 + 2 * 4;             // q_full; k_full/k_empty/v_full/v_empty x 2; per tile s_full, p_full, o_full, o_done
+constexpr int T2_SMEM = 2 * Q_BYTES + 4 * K128_BYTES + T2_BARS * 8 + 16 + 1024;
+constexpr int T2_THREADS = 64 + 2 * 128;
+static_assert(T2_SMEM <= 232448, "shared memory of one CTA");
+
+__global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
+    const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+    const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
+    const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window,
+    float scale_log2, int* __restrict__ status) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+  const uint32_t q_s = smem_u32(smem);
+  const uint32_t k_s = q_s + 2 * Q_BYTES, v_s = k_s + 2 * K128_BYTES;
+  uint64_t* bars = (uint64_t*)(smem + 2 * Q_BYTES + 4 * K128_BYTES);
+  uint32_t* tmem_slot = (uint32_t*)(bars + T2_BARS);
+  const uint32_t bar0 = smem_u32(bars);
+  const uint32_t q_full = bar0, k_full = bar0 + 8, k_empty = bar0 + 24, v_full = bar0 + 40, v_empty = bar0 + 56;
+  auto s_full = [&](int w) { return bar0 + 72 + 32 * w; };
+  auto p_full = [&](int w) { return bar0 + 80 + 32 * w; };
+  auto o_full = [&](int w) { return bar0 + 88 + 32 * w; };
+  auto o_done = [&](int w) { return bar0 + 96 + 32 * w; };
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  jb::pdl_launch_dependents();
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < 2; ++s) {
+      mbar_init(k_full + 8 * s, 1);
+      mbar_init(k_empty + 8 * s, 1);
+      mbar_init(v_full + 8 * s, 1);
+      mbar_init(v_empty + 8 * s, 1);
+    }
+    for (int w = 0; w < 2; ++w) {
+      mbar_init(s_full(w), 1);
+      mbar_init(p_full(w), 128);
+      mbar_init(o_full(w), 1);
+      mbar_init(o_done(w), 1);
+    }
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(512)
+                 : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem = *tmem_slot;
+  jb::pdl_wait();
+
+  const int G = nh / nkv;
+  const int tpt = BM / G;
+  const int seq = blockIdx.z, kvh = blockIdx.y;
+  const int pair = gridDim.x - 1 - blockIdx.x;  // the longest key ranges start first
+  const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
+  const int tok_first = pair * 2 * tpt;
+  const bool active = tok_first < q_len;
+  const int len = kv_len[seq];
+  const int n_tok_all = active ? min(2 * tpt, q_len - tok_first) : 0;
+  const int pos_first = len - q_len + tok_first;
+  const int last_page = (len - 1) / PAGE;
+  const int kb_end = active ? (pos_first + n_tok_all - 1) / KB : -1;                       // in blocks of 128 keys
+  const int kb_start = (active && window > 0) ? max(0, pos_first - window + 1) / KB : 0;
+  const int nb = kb_end - kb_start + 1;
+
+  if (active && warp == 0) {
+    // ---------------- producer ----------------
+    if (lane == 0) {
+      mbar_expect_tx(q_full, 2 * Q_BYTES);
+      for (int w = 0; w < 2; ++w)
+        for (int h = 0; h < NH64; ++h)
+          tma_load_4d(q_s + w * Q_BYTES + h * BM * 128, &map_q, q_full, h * 64, 0, kvh, qs + tok_first + w * tpt);
+      const int* pages = block_table + (size_t)seq * max_pages;
+      for (int j = 0; j < nb; ++j) {
+        const int st = j & 1;
+        // a block's second page may lie past the sequence's end: its keys are masked, any finite data will do
+        int row0[2];
+        for (int half = 0; half < 2; ++half)
+          row0[half] = (pages[min(2 * (kb_start + j) + half, last_page)] * nkv + kvh) * PAGE;
+        if (j >= 2 && !mbar_wait(k_empty + 8 * st, ((j >> 1) - 1) & 1, status, 11)) break;
+        mbar_expect_tx(k_full + 8 * st, K128_BYTES);
+        for (int half = 0; half < 2; ++half)
+          for (int h = 0; h < NH64; ++h)
+            tma_load_2d(k_s + st * K128_BYTES + h * KB * 128 + half * PAGE * 128, &map_k, k_full + 8 * st, h * 64, row0[half]);
+        if (j >= 2 && !mbar_wait(v_empty + 8 * st, ((j >> 1) - 1) & 1, status, 11)) break;
+        mbar_expect_tx(v_full + 8 * st, K128_BYTES);
+        for (int half = 0; half < 2; ++half)
+          for (int h = 0; h < NH64; ++h)
+            tma_load_2d(v_s + st * K128_BYTES + h * KB * 128 + half * PAGE * 128, &map_v, v_full + 8 * st, h * 64, row0[half]);
+      }
+    }
+  } else if (active && warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc_s = instr_desc(KB, 0), idesc_o = instr_desc(HD, 1);
+      bool ok = mbar_wait(q_full, 0, status, 12);
+      auto issue_s = [&](int w, int j) -> bool {
+        const int st = j & 1;
+        if (!mbar_wait(k_full + 8 * st, (j >> 1) & 1, status, 12)) return false;
+        tc_fence_after();
+#pragma unroll
+        for (int h = 0; h < NH64; ++h) {
+          const uint64_t a = desc_k_sw128(q_s + w * Q_BYTES + h * BM * 128);
+          const uint64_t k = desc_k_sw128(k_s + st * K128_BYTES + h * KB * 128);
+#pragma unroll
+          for (int ks = 0; ks < 4; ++ks) umma(tmem + w * 128, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
+        }
+        umma_commit(s_full(w));
+        if (w == 1) umma_commit(k_empty + 8 * st);   // both tiles' score products have read these keys
+        return true;
+      };
+      if (ok) ok = issue_s(0, 0);
+      if (ok) ok = issue_s(1, 0);
+      for (int j = 0; j < nb && ok; ++j) {
+        const int st = j & 1;
+        for (int w = 0; w < 2 && ok; ++w) {
+          ok = mbar_wait(p_full(w), j & 1, status, 12);   // P_j lies over the first half of S; O is rescaled if it had to be
+          if (ok && w == 0) ok = mbar_wait(v_full + 8 * st, (j >> 1) & 1, status, 12);
+          if (!ok) break;
+          tc_fence_after();
+          const uint32_t v_base = v_s + st * K128_BYTES;
+#pragma unroll
+          for (int ks = 0; ks < KB / 16; ++ks)   // 16 keys per step: 8 TMEM columns of P, two 8-key atoms of V
+            umma_ts(tmem + 256 + w * 128, tmem + w * 128 + ks * 8, desc_mn_sw128(v_base + ks * 2048, KB * 128, 1024), idesc_o,
+                    (j | ks) ? 1u : 0u);
+          umma_commit(o_full(w));
+          if (j == nb - 1) umma_commit(o_done(w));
+          if (w == 1) umma_commit(v_empty + 8 * st);
+          if (j + 1 < nb) ok = issue_s(w, j + 1);   // after the product that read P: S_{j+1} overwrites it
+        }
+      }
+    }
+  } else if (active) {
+    // ---------------- softmax, one thread per row, four warps per tile ----------------
+    const int w = (warp - 2) >> 2;
+    const int quarter = warp & 3;
+    const int row = quarter * 32 + lane;
+    const int tl = w * tpt + row / G;
+    const bool valid = tl < n_tok_all;
+    const int row_pos = valid ? pos_first + tl : -1;
+    const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
+    const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
+    const uint32_t s_col = w * 128, o_col = 256 + w * 128;
+    float m_ref = -CUDART_INF_F, l = 0.0f;
+    bool ok = true;
+    for (int j = 0; j < nb && ok; ++j) {
+      ok = mbar_wait(s_full(w), j & 1, status, 13);
+      if (!ok) break;
+      tc_fence_after();
+      uint32_t sr[KB];
+#pragma unroll
+      for (int c0 = 0; c0 < KB; c0 += 16) tmem_ld16(lane_addr + s_col + c0, sr + c0);
+      tmem_ld_wait();
+      const int key0 = (kb_start + j) * KB;
+      if (key0 + KB - 1 > row_pos || key0 < row_lo) {
+#pragma unroll
+        for (int c = 0; c < KB; ++c) {
+          const int kp = key0 + c;
+          if (!(kp <= row_pos && kp >= row_lo)) sr[c] = 0xff800000u;  // -inf
+        }
+      }
+      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+      for (int c = 0; c < KB; c += 4) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sr[c + e]));
+      }
+      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const bool grow = mx > m_ref + RESCALE_LOG2 || (m_ref == -CUDART_INF_F && mx > -CUDART_INF_F);
+      if (__any_sync(0xffffffffu, grow)) {
+        const float m_new = fmaxf(m_ref, mx);
+        if (j > 0) {
+          ok = mbar_wait(o_full(w), (j - 1) & 1, status, 13);  // the P.V product of block j-1 has landed in O
+          if (!ok) break;
+          tc_fence_after();
+          const float corr = m_new == -CUDART_INF_F ? 1.0f : exp2f(m_ref - m_new);
+#pragma unroll
+          for (int c0 = 0; c0 < HD; c0 += 16) {
+            uint32_t r[16];
+            tmem_ld16(lane_addr + o_col + c0, r);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            tmem_st16(lane_addr + o_col + c0, r);
+          }
+          tmem_st_wait();
+          l *= corr;
+        }
+        m_ref = m_new;
+      }
+      const float neg_ref = m_ref == -CUDART_INF_F ? 0.0f : -m_ref;
+      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+      for (int c = 0; c < KB / 2; ++c) {
+        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), scale_log2, neg_ref));
+        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, neg_ref));
+        sum4[c & 3] += p0 + p1;
+        sr[c] = pack_bf16(p0, p1);
+      }
+      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+#pragma unroll
+      for (int c0 = 0; c0 < KB / 2; c0 += 16) tmem_st16(lane_addr + s_col + c0, sr + c0);
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(p_full(w));
+    }
+    if (ok && nb > 0) ok = mbar_wait(o_done(w), 0, status, 13);
+    if (ok) {
+      tc_fence_after();
+      const float inv = 1.0f / l;
+      bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * HD;
+#pragma unroll
+      for (int c0 = 0; c0 < HD; c0 += 16) {
+        uint32_t r[16];
+        tmem_ld16(lane_addr + o_col + c0, r);
+        tmem_ld_wait();
+        if (valid) {
+          uint4 w0, w1;
+          w0.x = pack_bf16(__uint_as_float(r[0]) * inv, __uint_as_float(r[1]) * inv);
+          w0.y = pack_bf16(__uint_as_float(r[2]) * inv, __uint_as_float(r[3]) * inv);
+          w0.z = pack_bf16(__uint_as_float(r[4]) * inv, __uint_as_float(r[5]) * inv);
+          w0.w = pack_bf16(__uint_as_float(r[6]) * inv, __uint_as_float(r[7]) * inv);
+          w1.x = pack_bf16(__uint_as_float(r[8]) * inv, __uint_as_float(r[9]) * inv);
+          w1.y = pack_bf16(__uint_as_float(r[10]) * inv, __uint_as_float(r[11]) * inv);
+          w1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
+          w1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
+          *reinterpret_cast<uint4*>(dst + c0) = w0;
+          *reinterpret_cast<uint4*>(dst + c0 + 8) = w1;
+        }
+      }
+    }
+    tc_fence_before();
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(512) : "memory");
+  }
+}
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -491,13 +742,13 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
             CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
       return JB_ERR_TENSORMAP;
   }
-  // Two row tiles per CTA share every page they load, which pays when there are CTAs enough to fill the SMs
-  // several times over; with fewer the finer one-tile CTAs balance the causal triangle better.
+  // Two row tiles per CTA over blocks of 128 keys are the faster kernel once there are CTAs enough for every
+  // SM; below that the finer one-tile CTAs spread better.
   const int n_tiles = (max_q_len + tpt - 1) / tpt;
   const long long ctas_of_pairs = (long long)((n_tiles + 1) / 2) * nkv * n_seqs;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  bool pairs = ctas_of_pairs >= 3LL * sms;
+  bool pairs = ctas_of_pairs >= sms;
   if (const char* e = getenv("JANUS_ATTN_TC_TILES")) {   // 1 or 2: tiles per CTA whatever the size (for tests and measurements)
     if (e[0] == '1') pairs = false;
     if (e[0] == '2') pairs = true;
@@ -506,14 +757,14 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_for(1));
     if (e == cudaSuccess)
-      e = cudaFuncSetAttribute(prefill_tc_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_for(2));
+      e = cudaFuncSetAttribute(prefill_tc128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM);
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   if (pairs) {
     dim3 grid((n_tiles + 1) / 2, nkv, n_seqs);
-    jb::Launch cfg(grid, dim3(threads_for(2)), smem_for(2), stream);
-    return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<2>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
+    jb::Launch cfg(grid, dim3(T2_THREADS), T2_SMEM, stream);
+    return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc128_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
                                    nkv, max_pages, window, scale * LOG2E, status);
   }
   dim3 grid(n_tiles, nkv, n_seqs);

@@ -199,7 +199,8 @@ def test_attention_bf16_prefill(ops, nh, nkv, hd, window):
                                                  (2, 1, 64, 0), (64, 1, 128, 0)])
 def test_attention_tc_prefill(ops, nh, nkv, hd, window, tiles, monkeypatch):
     """The tcgen05 kernel against the plain attention: ragged batch, chunked prompts
-    (queries are the last q_len positions), a far key that stands out; one and two row tiles per CTA.
+    (queries are the last q_len positions), a far key that stands out; the one-tile kernel and the
+    two-tile kernel over blocks of 128 keys.
     With a window the first page of a tile holds a few keys for some warps and none for the others, so
     warps of one CTA run far apart: repeated, since a wait that mistakes one block's completion for
     another's shows only now and then."""
