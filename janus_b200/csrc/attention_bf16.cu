@@ -203,7 +203,9 @@ __global__ void __launch_bounds__(THREADS) prefill_kernel(
   bf16* kv_s = q_s + 64 * LD;                     // [2 stages][K, V][64][LD]
   const int G = nh / nkv;
   const int tpt = 64 / G;                         // tokens per tile
-  const int seq = blockIdx.z, kvh = blockIdx.y, tile = blockIdx.x;
+  // kv heads run fastest in the order CTAs are handed out and tiles go backwards: across all heads the
+  // longest key ranges start first
+  const int seq = blockIdx.z, kvh = blockIdx.x, tile = gridDim.y - 1 - blockIdx.y;
   const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
   const int tok0 = tile * tpt;
   if (tok0 >= q_len) return;
@@ -539,7 +541,7 @@ JB_EXPORT int jb_attention_bf16_prefill(const void* q, const void* k_cache, cons
     configured = true;
   }
   const int tpt = 64 / G;
-  dim3 grid((max_q_len + tpt - 1) / tpt, nkv, n_seqs);
+  dim3 grid(nkv, (max_q_len + tpt - 1) / tpt, n_seqs);
   jb::Launch cfg(grid, dim3(THREADS), PREFILL_SMEM, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_kernel, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
                                  (bf16*)out, block_table, q_start, kv_len, nh, nkv, max_pages, window,

@@ -246,8 +246,9 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   // ---- which rows, which keys ----
   const int G = nh / nkv;
   const int tpt = BM / G;  // tokens per tile
-  const int seq = blockIdx.z, kvh = blockIdx.y;
-  const int pair = gridDim.x - 1 - blockIdx.x;  // the longest key ranges start first
+  // kv heads run fastest in the order CTAs are handed out, so that across all heads the longest key ranges start first
+  const int seq = blockIdx.z, kvh = blockIdx.x;
+  const int pair = gridDim.y - 1 - blockIdx.y;
   const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
   const int tok_first = pair * NT * tpt;        // first token of the first tile
   const bool active = tok_first < q_len;        // uniform for the CTA
@@ -497,8 +498,9 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
 
   const int G = nh / nkv;
   const int tpt = BM / G;
-  const int seq = blockIdx.z, kvh = blockIdx.y;
-  const int pair = gridDim.x - 1 - blockIdx.x;  // the longest key ranges start first
+  // kv heads run fastest in the order CTAs are handed out, so that across all heads the longest key ranges start first
+  const int seq = blockIdx.z, kvh = blockIdx.x;
+  const int pair = gridDim.y - 1 - blockIdx.y;
   const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
   const int tok_first = pair * 2 * tpt;
   const bool active = tok_first < q_len;
@@ -762,12 +764,12 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
     configured = true;
   }
   if (pairs) {
-    dim3 grid((n_tiles + 1) / 2, nkv, n_seqs);
+    dim3 grid(nkv, (n_tiles + 1) / 2, n_seqs);
     jb::Launch cfg(grid, dim3(T2_THREADS), T2_SMEM, stream);
     return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc128_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
                                    nkv, max_pages, window, scale * LOG2E, status);
   }
-  dim3 grid(n_tiles, nkv, n_seqs);
+  dim3 grid(nkv, n_tiles, n_seqs);
   jb::Launch cfg(grid, dim3(threads_for(1)), smem_for(1), stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<1>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
                                  nkv, max_pages, window, scale * LOG2E, status);
