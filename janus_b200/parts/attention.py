@@ -23,7 +23,6 @@ from .linear import Linear
 
 # JANUS_FUSED_DECODE=0 keeps rotation and cache append in a kernel of their own for decode steps too
 _FUSED_DECODE = os.environ.get("JANUS_FUSED_DECODE", "1") != "0"
-_FUSED_DECODE_MAX_PAIRS = int(os.environ.get("JANUS_FUSED_DECODE_MAX_PAIRS", "148"))      # (sequence, kv head) pairs up to which the fused decode kernel is used
 
 
 class GQAttention(Mixer):
@@ -90,10 +89,9 @@ class GQAttention(Mixer):
                 self.position.apply(qkv[:, self.q_width: self.q_width + self.kv_width], self.nkv, self.hd,
                                     ctx.positions)
         attn = ws.get("attn_out", (T, self.q_width), self.dtype)
-        if (ctx.is_decode and self.dtype == torch.bfloat16 and _FUSED_DECODE and not custom_positions
-                and ctx.n_seqs * self.nkv <= _FUSED_DECODE_MAX_PAIRS):
-            # a few sequences, one token each: rotation and cache append happen inside the attention
-            # kernel (one launch less; with many sequences the rotation kernel of its own is faster)
+        if ctx.is_decode and self.dtype == torch.bfloat16 and _FUSED_DECODE and not custom_positions:
+            # one token per sequence: rotation and cache append happen inside the attention kernel
+            # (one launch and one round trip of q less)
             ops.attention_bf16_decode(None, cache_view.k, cache_view.v, attn, group.block_table, ctx.kv_len,
                                       self.nh, self.nkv, self.hd, group.page_size, self.window, self.scale,
                                       ctx.workspace, ctx.max_kv_len_bound, qkv=qkv, cos_sin=table,
