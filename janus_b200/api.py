@@ -96,6 +96,13 @@ class Model:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.engine.step(entries)
 
+    def check(self) -> None:
+        """Waits for the device and raises if a tensor-core kernel gave up on a wait (its result would
+        be incomplete).  `generate` calls it before it returns; a caller of `step` calls it when it
+        reads results."""
+        from .kernels import ops
+        ops.check_kernel_status(self.device)
+
     # -- generation ------------------------------------------------------------
     def generate(self, prompts: Sequence[Sequence[int]], max_tokens: int = 128, temperature: float = 0.0,
                  top_k: int = 0, top_p: float = 1.0, repetition_penalty: float = 1.0, seed: int = 0,
@@ -125,6 +132,7 @@ class Model:
             _EngineBackend(self.engine, sampler), [list(map(int, p)) for p in prompts], max_tokens, stop,
             batch_size or cache.n_slots, cache.n_pages * PAGE_SIZE, self.engine.max_seq_len,
             cache.n_free_slots, PAGE_SIZE, callback)
+        self.check()
         if return_reasons:
             return outputs, reasons, stats
         return outputs, stats

@@ -43,13 +43,12 @@ def main(argv=None) -> int:
             entries.append(StepEntry(slots[rid], e["tokens"], e.get("want", [])))
         if entries:
             logits = model.step(entries)
+            model.check()   # waits for the step; no file is written from a step whose kernel gave up
             if logits.shape[0] > 0:
                 arr = logits.detach().to("cpu", torch.float32).numpy().astype("<f4", copy=False)
                 tmp = os.path.join(args.out, f".{step}.f32.tmp")
                 arr.tofile(tmp)
                 os.replace(tmp, os.path.join(args.out, f"{step}.f32"))
-            else:
-                torch.cuda.synchronize()
         for rid in rec.get("end", []):
             rid = str(rid)
             if rid in slots:
