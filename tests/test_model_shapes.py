@@ -77,3 +77,49 @@ def test_long_prompt_runs_the_pair_products(big_model):
     out = model.step([StepEntry(a, ids[2], range(600))]).cpu().numpy()
     assert rel_err(out, ref[2]) < tol_for("bfloat16")
     ops.check_kernel_status(model.device)
+
+
+# A context of several thousand keys: 71 pages a sequence, so that decode attention cuts its keys into
+# splits that meet in the combine kernel, prompts run the products that work in CTA pairs and many row
+# tiles of the tensor-core attention, and the llama3 frequency regions all occur among the positions.
+LONG_CONTEXT = dict(
+    architectures=["LlamaForCausalLM"], hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+    num_key_value_heads=2, head_dim=64, intermediate_size=512, vocab_size=512, max_position_embeddings=8192,
+    rms_norm_eps=1e-5, rope_theta=500000.0,
+    rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                      original_max_position_embeddings=1024),
+    tie_word_embeddings=True)
+LONG_PROMPT, LONG_DECODED = 4500, 40
+
+
+@pytest.fixture(scope="module")
+def long_model(tmp_path_factory):
+    d = make_model_dir(LONG_CONTEXT, str(tmp_path_factory.mktemp("long") / "m"), seed=5, dtype="bfloat16", sharpen=6.0)
+    cfg, w = P.read_model_dir(d)
+    ids = random_tokens(LONG_PROMPT + LONG_DECODED, LONG_CONTEXT["vocab_size"], 9)
+    return d, ids, P.forward(cfg, w, ids).numpy()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_context_of_thousands_of_keys(long_model, dtype):
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    d, ids, ref = long_model
+    model = janus_b200.load(d, dtype=dtype, max_tokens=2 * 4608)
+    tol = tol_for(dtype)
+    a, b = model.alloc_slot(), model.alloc_slot()
+    # the second sequence is a prefix of the first: its logits are the first's at the same places
+    short = 1000
+    want_a = list(range(0, LONG_PROMPT, 97)) + [LONG_PROMPT - 1]
+    want_b = list(range(0, short, 89)) + [short - 1]
+    out = model.step([StepEntry(a, ids[:LONG_PROMPT], want_a), StepEntry(b, ids[:short], want_b)]).cpu().numpy()
+    assert rel_err(out[:len(want_a)], ref[want_a]) < tol
+    assert rel_err(out[len(want_a):], ref[want_b]) < tol
+    rows_a, rows_b = [], []
+    for j in range(LONG_DECODED):
+        got = model.step([StepEntry(a, [ids[LONG_PROMPT + j]], [0]), StepEntry(b, [ids[short + j]], [0])]).cpu().numpy()
+        rows_a.append(got[0:1])
+        rows_b.append(got[1:2])
+    assert rel_err(np.concatenate(rows_a), ref[LONG_PROMPT:LONG_PROMPT + LONG_DECODED]) < tol
+    assert rel_err(np.concatenate(rows_b), ref[short:short + LONG_DECODED]) < tol
+    model.check()
