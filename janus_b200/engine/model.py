@@ -74,6 +74,10 @@ class DecoderModel:
     def forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
         """Run the tokens of `ctx` through every place of the schedule and write
         the logits of the rows `want_rows` (indices into the step's tokens)."""
+        with ops.stream_scope():         # every launch of the pass goes to the stream that is current now
+            self._forward(ctx, want_rows, logits)
+
+    def _forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
         T = ctx.n_tokens
         residual = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
         ops.embed_gather(self.embedding, ctx.token_ids, residual, ctx.feedback,

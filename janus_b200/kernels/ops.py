@@ -4,9 +4,11 @@ a non-zero return.  Nothing here computes; there is no other code path.
 """
 from __future__ import annotations
 
+import contextlib
 import ctypes
+import functools
 import os
-from typing import Optional
+from typing import Optional, Tuple
 
 import torch
 
@@ -27,8 +29,36 @@ def dtype_code(dtype: torch.dtype) -> int:
     raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dtype}")
 
 
+_scope_stream = [None]
+
+
 def _stream() -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    s = _scope_stream[0]
+    return s if s is not None else ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+@contextlib.contextmanager
+def stream_scope():
+    """Within the scope every launch goes to the stream that was current on entry: the question is asked
+    once for a whole forward pass instead of once per kernel."""
+    before = _scope_stream[0]
+    _scope_stream[0] = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    try:
+        yield
+    finally:
+        _scope_stream[0] = before
+
+
+_libs = {}
+
+
+def _lib(stem: str, key=None, defines=None) -> ctypes.CDLL:
+    """The built library `stem` (variant `key`, compiled with `defines(key)` or the dict `defines`);
+    asked for on every launch, so the answer is remembered here."""
+    lib = _libs.get((stem, key))
+    if lib is None:
+        lib = _libs[(stem, key)] = library(stem, defines(key) if callable(defines) else defines)
+    return lib
 
 
 def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
@@ -75,7 +105,7 @@ def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,
     _need(out, "embed out", torch.float32)
     if table.shape[1] != H:
         raise KernelError(f"embed: table width {table.shape[1]} != output width {H}")
-    _check(library("elementwise").jb_embed_gather(
+    _check(_lib("elementwise").jb_embed_gather(
         _ptr(table), dtype_code(table.dtype), _ptr(ids), _ptr(out), T, H, _ptr(feedback), _ptr(token_slot),
         _stream()), "embed_gather")
 
@@ -96,7 +126,7 @@ def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, out: torch.Tensor,
         _need(row_index, "rmsnorm row_index", torch.int32, (rows,))
     elif x.shape[0] < rows:
         raise KernelError("rmsnorm: fewer input rows than output rows")
-    _check(library("elementwise").jb_rmsnorm(
+    _check(_lib("elementwise").jb_rmsnorm(
         _ptr(x), _ptr(row_index), _ptr(gamma), dtype_code(gamma.dtype), ctypes.c_float(eps), _ptr(out),
         dtype_code(out.dtype), rows, H, _ptr(clear), ctypes.c_longlong(0 if clear is None else clear.numel()),
         _stream()), "rmsnorm")
@@ -106,7 +136,7 @@ def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     """residual += float32(delta), elementwise, in place"""
     _need(residual, "residual", torch.float32)
     _need(delta, "delta", None, residual.shape)
-    _check(library("elementwise").jb_residual_add(
+    _check(_lib("elementwise").jb_residual_add(
         _ptr(residual), _ptr(delta), dtype_code(delta.dtype), ctypes.c_longlong(residual.numel()), _stream()),
         "residual_add")
 
@@ -116,14 +146,14 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
     T, I = out.shape
     _need(gate_up, "swiglu input", out.dtype, (T, 2 * I))
     _need(out, "swiglu out")
-    _check(library("elementwise").jb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()),
+    _check(_lib("elementwise").jb_swiglu(_ptr(gate_up), _ptr(out), dtype_code(out.dtype), T, I, _stream()),
            "swiglu")
 
 
 def zero_f32(t: torch.Tensor) -> None:
     """Fill a float32 tensor with zeros (whole 16-byte vectors)."""
     _need(t, "zero target", torch.float32)
-    _check(library("elementwise").jb_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), _stream()), "zero_f32")
+    _check(_lib("elementwise").jb_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), _stream()), "zero_f32")
 
 
 # -- rotary positions + cache append --------------------------------------------
@@ -147,7 +177,7 @@ def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[t
         _need(dest, "cache rows", torch.int32, (T,))
         _need(k_cache, "k cache", q_out.dtype)
         _need(v_cache, "v cache", q_out.dtype)
-    _check(library("rope_cache").jb_rope_cache_write(
+    _check(_lib("rope_cache").jb_rope_cache_write(
         _ptr(qkv), qkv.shape[1], dtype_code(qkv.dtype), _ptr(q_out), dtype_code(q_out.dtype), _ptr(cos_sin),
         _ptr(positions), _ptr(dest), _ptr(k_cache), _ptr(v_cache),
         T, nh, nkv, hd, page_size, int(rotate), int(write_kv), _stream()), "rope_cache_write")
@@ -161,7 +191,7 @@ def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool
     _need(x, "gemm x", torch.float32)
     _need(w, "gemm w", torch.float32, (N, K))
     _need(y, "gemm y", torch.float32, (T, N))
-    _check(library("gemm_f32").jb_gemm_f32(_ptr(x), _ptr(w), _ptr(y), T, N, K, K, N, int(accumulate), _stream()),
+    _check(_lib("gemm_f32").jb_gemm_f32(_ptr(x), _ptr(w), _ptr(y), T, N, K, K, N, int(accumulate), _stream()),
            "gemm_f32")
 
 
@@ -176,7 +206,7 @@ def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(block_table, "block table", torch.int32)
     _need(token_slot, "token slots", torch.int32, (T,))
     _need(positions, "positions", torch.int32, (T,))
-    _check(library("attention_f32").jb_attention_f32(
+    _check(_lib("attention_f32").jb_attention_f32(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(token_slot), _ptr(positions),
         T, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale), _stream()),
         "attention_f32")
@@ -190,10 +220,11 @@ SM_COUNT_TARGET = 296      # CTAs wanted in flight for a weight-streaming produc
 
 def kernel_status(device: torch.device) -> torch.Tensor:
     """Device int that a kernel sets when one of its bounded waits ran out."""
-    key = str(device)
-    if key not in _status:
-        _status[key] = torch.zeros(1, dtype=torch.int32, device=device)
-    return _status[key]
+    st = _status.get(device)
+    if st is None:
+        st = torch.zeros(1, dtype=torch.int32, device=device)
+        _status[device] = _status[st.device] = st       # "cuda" and "cuda:0" name the same word
+    return st
 
 
 def check_kernel_status(device: torch.device) -> None:
@@ -241,7 +272,7 @@ def pack_weight(w: torch.Tensor) -> PackedWeight:
         raise KernelError(f"pack_weight: a matrix whose width is a multiple of 8 is needed, got {tuple(w.shape)}")
     N, K = w.shape
     tiles = torch.empty(((N + 127) // 128, (K + 63) // 64, 128, 64), dtype=torch.bfloat16, device=w.device)
-    _check(library("elementwise").jb_pack_weight_bf16(_ptr(w), N, K, _ptr(tiles), _stream()), "pack_weight")
+    _check(_lib("elementwise").jb_pack_weight_bf16(_ptr(w), N, K, _ptr(tiles), _stream()), "pack_weight")
     return PackedWeight(tiles, N, K)
 
 
@@ -254,36 +285,87 @@ def pack_gated(gate: torch.Tensor, up: torch.Tensor) -> PackedWeight:
 
 
 def split_k_for(T: int, N: int, K: int) -> int:
-    """How many slices of K a weight-streaming product (few tokens) is cut into
-    so that enough CTAs are in flight; 1 for prefill-sized T."""
-    if T > 64:
-        return 1
-    tiles = (N + 127) // 128
-    k_tiles = (K + 63) // 64
-    return max(1, min(SM_COUNT_TARGET // max(tiles, 1), k_tiles // 4))
+    """How many slices of K an adding product (mode "add", or a float32 "store" run as clear + add) is cut
+    into; 1 when it is not cut or runs on CTA pairs."""
+    pair, split = gemm_plan(T, N, K, "add")
+    return 1 if pair else split
 
 
-def _gemm_defines():
-    """Build-time overrides of the product kernel's tuning macros for experiments, e.g.
-    JANUS_GEMM_DEFINES="JB_RING_KB=104,JB_MAX_STAGES=6"; none by default."""
-    import os
-    text = os.environ.get("JANUS_GEMM_DEFINES", "")
-    if not text:
-        return None
-    return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
-
-
-# token counts from which the CTA-pair kernel (cta_group::2, 256-row weight tiles) runs the product;
+# token counts from which the CTA-pair kernel (cta_group::2, 256-row weight tiles) may run a product;
 # JANUS_GEMM_PAIR=0 keeps every product on the single-CTA kernel
-GEMM_PAIR_MIN_TOKENS = int(os.environ.get("JANUS_GEMM_PAIR_MIN_TOKENS", "512"))
+GEMM_PAIR_MIN_TOKENS = int(os.environ.get("JANUS_GEMM_PAIR_MIN_TOKENS", "65"))
 _GEMM_PAIR = os.environ.get("JANUS_GEMM_PAIR", "1") != "0"
+# token counts from which the q/k/v projection with rotation and cache append in its epilogue runs
+QKV_FUSED_MIN_TOKENS = int(os.environ.get("JANUS_QKV_FUSED_MIN_TOKENS", "512"))
+
+# Constants of the cost estimate in `gemm_plan`.  They were fitted so that the estimate picks the fastest
+# of the alternatives (CTA pairs; the single-CTA kernel with K in 1, 2, 3, 4, 6 or 8 slices) as measured on
+# a B200 for the four products of 1B-, 8B-, 13B- and 70B-sized layers at 72 to 4096 tokens: the pick is
+# 0.5 % slower than the best alternative on average and 13 % at worst.  They rank alternatives; they are
+# no forecast of a time.
+_PLAN_SM_FLOPS_PER_US = 9.68e6      # tensor-core rate of one SM on single-CTA tiles, flop per microsecond
+_PLAN_SM_FILL_BYTES_PER_US = 0.89e5  # operand bytes one SM takes in per microsecond
+_PLAN_TILE_US = 2.19                # per tile of the single-CTA kernel: first loads, epilogue
+_PLAN_PAIR_STEP_US = 0.50           # one 256 x 256 x 64 step of a CTA pair
+_PLAN_PAIR_TILE_US = 3.1            # per tile of a CTA pair
+_PLAN_HBM_BYTES_PER_US = 7.0e6      # the weight stream
+_PLAN_US_PER_ADD = 5e-7             # one float32 add of a slice of K into the output
+_PLAN_SPLITS = (1, 2, 3, 4, 6, 8)
 
 
-def _pair_defines():
-    text = os.environ.get("JANUS_GEMM_PAIR_DEFINES", "")
-    if not text:
-        return None
+@functools.lru_cache(maxsize=4096)
+def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tuple[bool, int]:
+    """Which kernel runs x[T, K] . w[N, K]^T and into how many slices of K it is cut: (CTA pairs?, slices).
+
+    Up to 64 tokens the product streams its weights: the single-CTA kernel, with K cut so that about two
+    tiles per SM are in flight (only a product that adds can be cut; its slices meet by atomic adds).
+    Above, the choice is by an estimate of the time: waves of tiles over the SMs x (steps along K x the
+    time of a step, tensor-core bound or bound by what an SM takes in per step, + a tile's fixed cost), not
+    below the time of the weight stream, plus the atomic adds of a cut K.  Few output tiles (a 4096 x 4096 matrix and 256
+    tokens make 32) leave most SMs idle unless K is cut; CTA pairs halve the operand bytes per flop and win
+    once their 256 x 256 tiles fill the SMs."""
+    tiles_w = (N + 127) // 128
+    k_tiles = (K + 63) // 64
+    if T <= 64:
+        if mode != "add":
+            return False, 1
+        return False, max(1, min(SM_COUNT_TARGET // max(tiles_w, 1), k_tiles // 4))
+    sms = SM_COUNT_TARGET // 2
+    gated = mode == "swiglu"
+    w_rows = 2 * N if gated else N
+    stream = w_rows * K * 2 / _PLAN_HBM_BYTES_PER_US
+    bn = 128 if (T <= 128 or gated) else 256               # token tile of the single-CTA kernel
+    stage_rows = 256 if gated else 128                      # weight rows a step brings in
+    step = max(2.0 * stage_rows * bn * 64 / _PLAN_SM_FLOPS_PER_US,
+               (stage_rows + bn) * 64 * 2 / _PLAN_SM_FILL_BYTES_PER_US)
+    best = (float("inf"), False, 1)
+    for split in (_PLAN_SPLITS if mode == "add" else (1,)):
+        if split > 1 and split > k_tiles // 4:
+            break
+        tiles = tiles_w * ((T + bn - 1) // bn) * split
+        waves = (tiles + sms - 1) // sms
+        cost = max(waves * (((k_tiles + split - 1) // split) * step + _PLAN_TILE_US), stream)
+        if split > 1:
+            cost += _PLAN_US_PER_ADD * T * N * split
+        best = min(best, (cost, False, split))
+    if allow_pairs and _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS:
+        clusters = ((T + 255) // 256) * (tiles_w if gated else (N + 255) // 256)
+        waves = (clusters + sms // 2 - 1) // (sms // 2)
+        best = min(best, (max(waves * (k_tiles * _PLAN_PAIR_STEP_US + _PLAN_PAIR_TILE_US), stream), True, 1))
+    return best[1], best[2]
+
+
+def _defines_from_env(name: str) -> dict:
+    """Build-time overrides of a kernel's tuning macros for experiments, read once when this module loads,
+    e.g. JANUS_GEMM_DEFINES="JB_RING_KB=104,JB_MAX_STAGES=6"; none by default."""
+    text = os.environ.get(name, "")
     return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
+
+
+_GEMM_DEFINES = _defines_from_env("JANUS_GEMM_DEFINES") or None
+_PAIR_DEFINES = _defines_from_env("JANUS_GEMM_PAIR_DEFINES") or None
+_ATTN_TC_DEFINES = _defines_from_env("JANUS_ATTN_TC_DEFINES")
+_ATTN_TC = os.environ.get("JANUS_ATTN_TC", "1") != "0"     # 0: prompts attend on the mma.sync kernel
 
 
 def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "store",
@@ -315,16 +397,18 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
             raise KernelError(f"gemm: unknown mode {mode!r}")
     if y.dtype != want or tuple(y.shape) != (T, N):
         raise KernelError(f"gemm {mode}: output must be {want} [{T}, {N}], got {y.dtype} {tuple(y.shape)}")
-    if pair is None:
-        pair = _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS and split_k in (None, 1)
+    if split_k is None:
+        pair, split_k = gemm_plan(T, N, K, mode, allow_pairs=pair is not False) if pair is not True else (True, 1)
+        if code != 2:
+            split_k = 1          # a storing product cut along K is the caller's clear + "add"
+    elif pair is None:
+        pair = False
     if pair:
-        _check(library("gemm_bf16_tc2", _pair_defines()).jb_gemm_bf16_pair(
+        _check(_lib("gemm_bf16_tc2", None, _PAIR_DEFINES).jb_gemm_bf16_pair(
             _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
             _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
-    if split_k is None:
-        split_k = split_k_for(T, N, K) if code == 2 else 1
-    _check(library("gemm_bf16_tc", _gemm_defines()).jb_gemm_bf16(
+    _check(_lib("gemm_bf16_tc", None, _GEMM_DEFINES).jb_gemm_bf16(
         _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
         int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
 
@@ -332,7 +416,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
 def gemm_qkv_rope_supported(T: int, hd: int) -> bool:
     """Whether the fused projection below takes this step: prompt-sized token counts and a head size that
     divides the kernel's 256 columns with half-heads of whole 16-column loads."""
-    return _GEMM_PAIR and _QKV_FUSED and T >= GEMM_PAIR_MIN_TOKENS and hd in (32, 64, 128, 256)
+    return _GEMM_PAIR and _QKV_FUSED and T >= QKV_FUSED_MIN_TOKENS and hd in (32, 64, 128, 256)
 
 
 _QKV_FUSED = os.environ.get("JANUS_QKV_FUSED", "1") != "0"   # 0: projection, then rotation and cache append apart
@@ -358,7 +442,7 @@ def gemm_qkv_rope_cache(x: torch.Tensor, w: PackedWeight, q_out: torch.Tensor, c
     _need(v_cache, "v cache", torch.bfloat16)
     if k_cache.shape[1:] != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
         raise KernelError(f"qkv: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
-    _check(library("gemm_bf16_tc2", _pair_defines()).jb_gemm_bf16_pair_qkv_rope(
+    _check(_lib("gemm_bf16_tc2", None, _PAIR_DEFINES).jb_gemm_bf16_pair_qkv_rope(
         _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
         _ptr(cos_sin), _ptr(positions), _ptr(dest),
         nh, nkv, hd, page_size, _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair_qkv_rope")
@@ -381,7 +465,7 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_
         _need(counts, "token counts", torch.int32)
         if counts.shape[1] != V:
             raise KernelError("sample: counts width differs from the vocabulary")
-    _check(library("sampling").jb_sample(
+    _check(_lib("sampling").jb_sample(
         _ptr(logits), B, V, _ptr(out_ids), ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p),
         ctypes.c_float(repetition_penalty), _ptr(counts), _ptr(count_rows),
         ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(seq_ids), _ptr(steps), _ptr(feedback), _stream()),
@@ -392,7 +476,7 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_
 def _attention_lib(hd: int):
     if hd % 8 or not 8 <= hd <= 256:
         raise KernelError(f"attention_bf16: head_dim {hd} is not a multiple of 8 in [8, 256]")
-    return library("attention_bf16", {"JB_HEAD_DIM": int(hd)})
+    return _lib("attention_bf16", int(hd), lambda h: {"JB_HEAD_DIM": h})
 
 
 def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -483,17 +567,9 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
 
 
 # -- tcgen05 prefill attention (head sizes 64 and 128, power-of-two groups) ------------------
-def _attention_tc_defines():
-    """Build-time overrides of the tcgen05 attention for experiments, e.g. JANUS_ATTN_TC_DEFINES="JB_TC_P_IN_TMEM=1";
-    none by default."""
-    text = os.environ.get("JANUS_ATTN_TC_DEFINES", "")
-    return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
-
-
 def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
-    import os
     g = nh // max(nkv, 1)
-    return (os.environ.get("JANUS_ATTN_TC", "1") != "0" and hd in (64, 128) and nkv > 0 and nh % nkv == 0
+    return (_ATTN_TC and hd in (64, 128) and nkv > 0 and nh % nkv == 0
             and g <= 128 and (g & (g - 1)) == 0)
 
 
@@ -512,7 +588,7 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
         raise KernelError(f"attention_tc: cache shape {tuple(k_cache.shape)} does not fit [pages, {nkv}, {page_size}, {hd}]")
-    _check(library("attention_tc", dict({"JB_HEAD_DIM": int(hd)}, **_attention_tc_defines())).jb_attention_tc_prefill(
+    _check(_lib("attention_tc", int(hd), lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES)).jb_attention_tc_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
         ctypes.c_float(scale), _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")

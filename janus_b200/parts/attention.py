@@ -61,8 +61,17 @@ class GQAttention(Mixer):
         proj = self.qkv if writes_cache else self.q_only
         if proj is None or not proj.meets_by_adds(tokens, torch.float32):
             return None
+        if self._projection_writes_cache(ctx, tokens, writes_cache):
+            return None
         qkv = ctx.workspace.get("qkv", (tokens, proj.out_features), torch.float32)
         return qkv if qkv.numel() % 4 == 0 else None
+
+    def _projection_writes_cache(self, ctx, tokens: int, writes_cache: bool) -> bool:
+        """Whether this step's q/k/v projection rotates and appends to the cache in its own epilogue
+        (prompts of bfloat16 models whose positions are a rotation by table)."""
+        table = self.position.fused_rotary_table() if self.position is not None else None
+        return (self.dtype == torch.bfloat16 and writes_cache and table is not None and not ctx.is_decode
+                and ops.gemm_qkv_rope_supported(tokens, self.hd))
 
     def forward(self, x: torch.Tensor, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True,
                 scratch_cleared: bool = False) -> None:
@@ -70,8 +79,7 @@ class GQAttention(Mixer):
         ws = ctx.workspace
         group = cache_view.group
         table = self.position.fused_rotary_table() if self.position is not None else None
-        if (self.dtype == torch.bfloat16 and writes_cache and table is not None and not ctx.is_decode
-                and ops.gemm_qkv_rope_supported(T, self.hd)):
+        if self._projection_writes_cache(ctx, T, writes_cache):
             # a prompt: the projection's epilogue rotates q and k and appends k and v to the cache
             q = ws.get("q_rot", (T, self.q_width), self.dtype)
             ops.gemm_qkv_rope_cache(x, self.qkv.weight, q, table, ctx.positions, group.dest_rows, cache_view.k,

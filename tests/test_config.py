@@ -93,3 +93,24 @@ def test_a_width_the_bfloat16_products_cannot_take_is_refused_when_the_model_is_
     with pytest.raises(ValueError, match="multiple of 8"):
         DecoderModel(llama_spec(cfg), torch.bfloat16, torch.device("cpu"))
     DecoderModel(llama_spec(cfg), torch.float32, torch.device("cpu"))     # the 32-bit path has no such limit
+
+
+def test_product_plan_picks_a_kernel_and_slices_that_the_kernels_take():
+    """The cost estimate that picks a product's kernel and its slices of K: decode-sized products are cut so
+    that two tiles per SM stream weights, few output tiles at prompt sizes are cut as well, large prompts run
+    on CTA pairs, and nothing is cut that cannot add."""
+    from janus_b200.kernels import ops
+    for N, K in ((4096, 4096), (4096, 14336), (6144, 4096), (200, 120), (128, 64), (3072, 2048), (128256, 4096)):
+        k_tiles = (K + 63) // 64
+        for T in (1, 8, 64, 65, 128, 129, 200, 256, 511, 512, 1000, 2048, 8192):
+            for mode in ("add", "store", "swiglu"):
+                pair, split = ops.gemm_plan(T, N, K, mode)
+                assert split >= 1 and (split == 1 or (mode == "add" and not pair and split <= max(1, k_tiles // 4)))
+                assert not pair or T >= ops.GEMM_PAIR_MIN_TOKENS
+                assert ops.gemm_plan(T, N, K, mode, allow_pairs=False)[0] is False
+            assert ops.split_k_for(T, N, K) == (1 if ops.gemm_plan(T, N, K, "add")[0] else ops.gemm_plan(T, N, K, "add")[1])
+    assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 9)
+    assert ops.gemm_plan(256, 4096, 4096, "add") == (False, 4)       # 32 output tiles: K in four slices
+    assert ops.gemm_plan(2048, 4096, 14336, "add") == (True, 1)
+    assert ops.gemm_plan(2048, 14336, 4096, "swiglu") == (True, 1)
+    assert ops.gemm_plan(64, 14336, 4096, "swiglu") == (False, 1)

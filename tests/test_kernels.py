@@ -294,16 +294,19 @@ def test_gemm_bf16_store_and_add(ops, T, N, K):
     ref = x.double().cpu() @ w.double().cpu().T
     w = ops.pack_weight(w)
     y16 = torch.empty(T, N, device=DEV, dtype=torch.bfloat16)
-    ops.gemm_bf16(x, w, y16)
+    ops.gemm_bf16(x, w, y16, pair=False)
     close(y16, ref, 6e-3)
     y32 = torch.full((T, N), float("nan"), device=DEV)
-    ops.gemm_bf16(x, w, y32)
+    ops.gemm_bf16(x, w, y32, pair=False)
     close(y32, ref, 2e-5)
     base = torch.randn(T, N, device=DEV)
     for split in (1, None, 4):
         acc = base.clone()
-        ops.gemm_bf16(x, w, acc, mode="add", split_k=split)
+        ops.gemm_bf16(x, w, acc, mode="add", split_k=split, pair=False)
         close(acc, ref + base.double().cpu(), 2e-5)
+    acc = base.clone()
+    ops.gemm_bf16(x, w, acc, mode="add")          # kernel and slices of K as the cost estimate picks them
+    close(acc, ref + base.double().cpu(), 2e-5)
     ops.check_kernel_status(torch.device(DEV))
 
 
@@ -313,13 +316,13 @@ def test_gemm_bf16_swiglu(ops, T, I, K):
     x, w = bf16_inputs(T, 2 * I, K, T + I)
     w = (w.float() * 3).to(torch.bfloat16)
     y = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
-    ops.gemm_bf16(x, ops.pack_gated(w[:I].contiguous(), w[I:].contiguous()), y, mode="swiglu")
+    ops.gemm_bf16(x, ops.pack_gated(w[:I].contiguous(), w[I:].contiguous()), y, mode="swiglu", pair=False)
     ref = P.swiglu_ffn(x.double().cpu(), w[:I].double().cpu(), w[I:].double().cpu(), torch.eye(I, dtype=torch.float64))
     close(y, ref, 6e-3)
     ops.check_kernel_status(torch.device(DEV))
 
 
-@pytest.mark.parametrize("T", [256, 300, 513, 1100])
+@pytest.mark.parametrize("T", [70, 130, 256, 300, 513, 1100])
 @pytest.mark.parametrize("N, K", [(200, 120), (256, 64), (1000, 320), (640, 4096)])
 def test_gemm_bf16_cta_pairs(ops, T, N, K):
     """The cta_group::2 kernel (256 weight rows per CTA pair, each CTA loads half of the token tile):
@@ -340,7 +343,7 @@ def test_gemm_bf16_cta_pairs(ops, T, N, K):
     ops.check_kernel_status(torch.device(DEV))
 
 
-@pytest.mark.parametrize("T", [256, 700])
+@pytest.mark.parametrize("T", [70, 130, 256, 700])
 @pytest.mark.parametrize("I, K", [(192, 64), (320, 96), (1000, 2048)])
 def test_gemm_bf16_cta_pairs_swiglu(ops, T, I, K):
     x, w = bf16_inputs(T, 2 * I, K, T + I + 1)

@@ -71,7 +71,7 @@ def test_long_prompt_runs_the_pair_products(big_model):
     from janus_b200.engine import StepEntry
     from janus_b200.kernels import ops
     d, ids, ref = big_model
-    assert len(ids[2]) >= ops.GEMM_PAIR_MIN_TOKENS
+    assert len(ids[2]) >= ops.QKV_FUSED_MIN_TOKENS
     model = janus_b200.load(d, dtype="bfloat16", max_tokens=1024)
     a = model.alloc_slot()
     out = model.step([StepEntry(a, ids[2], range(600))]).cpu().numpy()
