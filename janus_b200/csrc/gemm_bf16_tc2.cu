@@ -162,12 +162,17 @@ struct RopeOut {
 __host__ __device__ constexpr bool tokens_on_rows(int mode) { return mode == SWIGLU || mode == QKV_ROPE; }
 struct TileCoord {
   int t0, f0;
+  int k_lo, k_hi;   // k-tiles of this tile's slice of K (the whole of K unless an adding product is cut)
 };
 template <int MODE>
-__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles) {
+__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int k_tiles, int k_per, int splits) {
   TileCoord c;
+  const int slice = tile % splits;   // slices of one output tile are neighbours: they run at the same time
+  tile /= splits;
   c.t0 = (tile % n_tok_tiles) * 256;
   c.f0 = (tile / n_tok_tiles) * (MODE == SWIGLU ? 128 : 256);
+  c.k_lo = slice * k_per;
+  c.k_hi = min(k_tiles, c.k_lo + k_per);
   return c;
 }
 
@@ -175,7 +180,8 @@ template <int MODE>
 __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w,
                                                            const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                            int T, int N_out, int ldy, int k_tiles, int n_tiles,
-                                                           int n_tok_tiles, int up_tile_offset, RopeOut rope, int* __restrict__ status) {
+                                                           int n_tok_tiles, int k_per, int splits, int up_tile_offset,
+                                                           RopeOut rope, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -219,13 +225,13 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles);
+        const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
         // rows of this CTA's two loads: its 128 rows of the pair's M side, its half of the column operand
         // this CTA's weight row tile (the weights are packed: a tile is one contiguous 16 KB block)
         const int w_tile = MODE == SWIGLU ? (rank ? up_tile_offset + tc.f0 / BM : tc.f0 / BM) : tc.f0 / BM + (int)rank;
         constexpr bool TOK_ROWS = tokens_on_rows(MODE);
         const int x_row = tc.t0 + (int)rank * BM;
-        for (int i = 0; i < k_tiles; ++i, ++it) {
+        for (int i = tc.k_lo; i < tc.k_hi; ++i, ++it) {
           const int s = it % STAGES;
           if (it >= STAGES && !mbar_wait(empty0 + 8 * s, ((it / STAGES) - 1) & 1, status, 21)) { ok = false; break; }
           const uint32_t stage = smem_base + s * STAGE_BYTES;
@@ -255,7 +261,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
-        for (int i = 0; i < k_tiles; ++i, ++it) {
+        const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
+        for (int i = tc.k_lo; i < tc.k_hi; ++i, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, status, 22);
           if (!ok) break;
@@ -265,7 +272,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
           const uint64_t b_desc = smem_desc_sw128(stage + A_BYTES);
 #pragma unroll
           for (int k = 0; k < BK / UMMA_K; ++k)
-            umma_pair(acc_addr, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
+            umma_pair(acc_addr, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > tc.k_lo || k > 0) ? 1u : 0u);
           umma_commit_pair(empty0 + 8 * s);
         }
         if (ok) umma_commit_pair(acc_full0 + 8 * buf);
@@ -276,7 +283,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     const int quarter = warp & 3;
     int j = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
-      const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles);
+      const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
       const int buf = j & 1;
       if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, status, 23)) break;
       tc_fence_after();
@@ -470,7 +477,7 @@ int sm_count() {
 
 template <int MODE>
 int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T, int N_out, int K, int ldy,
-           const RopeOut& rope, int* status, cudaStream_t stream) {
+           const RopeOut& rope, int* status, cudaStream_t stream, int split_k = 1) {
   constexpr int smem = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -490,7 +497,13 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
   const int k_tiles = (K + BK - 1) / BK;
   constexpr int F_TILE = MODE == SWIGLU ? 128 : 256;
   const int n_tok_tiles = (T + 255) / 256, n_w_tiles = (N_out + F_TILE - 1) / F_TILE;
-  const int n_tiles = n_tok_tiles * n_w_tiles;
+  // only a product that adds can be cut along K: its slices meet by atomic adds (no slice is empty)
+  const int want = MODE == ADD_F32 ? max(1, min(split_k, k_tiles)) : 1;
+  const int k_per = (k_tiles + want - 1) / want;
+  const int splits = (k_tiles + k_per - 1) / k_per;
+  const long long all_tiles = (long long)n_tok_tiles * n_w_tiles * splits;
+  JB_REFUSE(all_tiles > 0x7fffffffLL, "gemm_bf16_pair: too many tiles (%lld)", all_tiles);
+  const int n_tiles = (int)all_tiles;
   const int pairs = n_tiles < sm_count() / 2 ? n_tiles : sm_count() / 2;
   cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
   cudaLaunchAttribute attrs[2];
@@ -510,22 +523,23 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
     cfg.numAttrs = 2;
   }
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, Y, T, N_out, ldy, k_tiles, n_tiles,
-                                 n_tok_tiles, MODE == SWIGLU ? up_tile_offset : 0, rope, status);
+                                 n_tok_tiles, k_per, splits, MODE == SWIGLU ? up_tile_offset : 0, rope, status);
 }
 
 }  // namespace
 
-// Same contract as jb_gemm_bf16 (without split-K): Y (+)= X . W^T with X [T, K] and W packed (jb_pack_weight_bf16).
-// Meant for T >= 256.  status codes of a timed-out wait: 21 producer, 22 MMA, 23 epilogue.
+// Same contract as jb_gemm_bf16: Y (+)= X . W^T with X [T, K] and W packed (jb_pack_weight_bf16); `split_k` > 1
+// cuts K of an adding product (mode ADD_F32) into that many slices, which meet in Y by atomic adds.
+// Meant for prompt-sized T.  status codes of a timed-out wait: 21 producer, 22 MMA, 23 epilogue.
 JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
-                                int N_out, int K, int ldy, int mode, int* status, cudaStream_t stream) {
+                                int N_out, int K, int ldy, int mode, int split_k, int* status, cudaStream_t stream) {
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16_pair: operands must be 16-byte aligned");
   switch (mode) {
     case STORE_BF16: return launch<STORE_BF16>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     case STORE_F32: return launch<STORE_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
-    case ADD_F32: return launch<ADD_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
+    case ADD_F32: return launch<ADD_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, split_k);
     case SWIGLU: return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     default: JB_REFUSE(true, "gemm_bf16_pair: unknown mode %d", mode);
   }

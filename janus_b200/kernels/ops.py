@@ -286,9 +286,8 @@ def pack_gated(gate: torch.Tensor, up: torch.Tensor) -> PackedWeight:
 
 def split_k_for(T: int, N: int, K: int) -> int:
     """How many slices of K an adding product (mode "add", or a float32 "store" run as clear + add) is cut
-    into; 1 when it is not cut or runs on CTA pairs."""
-    pair, split = gemm_plan(T, N, K, "add")
-    return 1 if pair else split
+    into; 1 when it is not cut."""
+    return gemm_plan(T, N, K, "add")[1]
 
 
 # token counts from which the CTA-pair kernel (cta_group::2, 256-row weight tiles) may run a product;
@@ -299,18 +298,20 @@ _GEMM_PAIR = os.environ.get("JANUS_GEMM_PAIR", "1") != "0"
 QKV_FUSED_MIN_TOKENS = int(os.environ.get("JANUS_QKV_FUSED_MIN_TOKENS", "512"))
 
 # Constants of the cost estimate in `gemm_plan`.  They were fitted so that the estimate picks the fastest
-# of the alternatives (CTA pairs; the single-CTA kernel with K in 1, 2, 3, 4, 6 or 8 slices) as measured on
-# a B200 for the four products of 1B-, 8B-, 13B- and 70B-sized layers at 72 to 4096 tokens: the pick is
-# 0.5 % slower than the best alternative on average and 13 % at worst.  They rank alternatives; they are
-# no forecast of a time.
-_PLAN_SM_FLOPS_PER_US = 9.68e6      # tensor-core rate of one SM on single-CTA tiles, flop per microsecond
-_PLAN_SM_FILL_BYTES_PER_US = 0.89e5  # operand bytes one SM takes in per microsecond
-_PLAN_TILE_US = 2.19                # per tile of the single-CTA kernel: first loads, epilogue
-_PLAN_PAIR_STEP_US = 0.50           # one 256 x 256 x 64 step of a CTA pair
-_PLAN_PAIR_TILE_US = 3.1            # per tile of a CTA pair
-_PLAN_HBM_BYTES_PER_US = 7.0e6      # the weight stream
-_PLAN_US_PER_ADD = 5e-7             # one float32 add of a slice of K into the output
+# of the alternatives (the single-CTA kernel with K in 1, 2, 3, 4, 6 or 8 slices; CTA pairs with K in 1, 2,
+# 3, 4 or 6) as measured on a B200 for the four products of 1B-, 8B-, 13B- and 70B-sized layers at 72 to
+# 4096 tokens: the pick is 0.4 % slower than the best alternative on average.  They rank alternatives; they
+# are no forecast of a time.
+_PLAN_SM_FLOPS_PER_US = 6.09e6      # tensor-core rate of one SM on single-CTA tiles, flop per microsecond
+_PLAN_SM_FILL_BYTES_PER_US = 1.99e5  # operand bytes one SM takes in per microsecond
+_PLAN_TILE_US = 0.0                 # per tile of the single-CTA kernel
+_PLAN_PAIR_STEP_US = 0.461          # one 256 x 256 x 64 step of a CTA pair
+_PLAN_PAIR_TILE_US = 4.18           # per tile of a CTA pair: first loads, epilogue
+_PLAN_HBM_BYTES_PER_US = 6.68e6     # the weight stream
+_PLAN_US_PER_ADD = 5.14e-7          # one float32 add of a slice of K into the output, single-CTA kernel
+_PLAN_PAIR_US_PER_ADD = 4.26e-7     # the same, CTA pairs
 _PLAN_SPLITS = (1, 2, 3, 4, 6, 8)
+_PLAN_PAIR_SPLITS = (1, 2, 3, 4, 6)
 
 
 @functools.lru_cache(maxsize=4096)
@@ -321,9 +322,9 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     tiles per SM are in flight (only a product that adds can be cut; its slices meet by atomic adds).
     Above, the choice is by an estimate of the time: waves of tiles over the SMs x (steps along K x the
     time of a step, tensor-core bound or bound by what an SM takes in per step, + a tile's fixed cost), not
-    below the time of the weight stream, plus the atomic adds of a cut K.  Few output tiles (a 4096 x 4096 matrix and 256
-    tokens make 32) leave most SMs idle unless K is cut; CTA pairs halve the operand bytes per flop and win
-    once their 256 x 256 tiles fill the SMs."""
+    below the time of the weight stream, plus the atomic adds of a cut K.  Few output tiles (a 4096 x 4096
+    matrix and 256 tokens make 32) leave most SMs idle unless K is cut; CTA pairs halve the operand bytes
+    per flop and win once their 256 x 256 tiles fill the SMs."""
     tiles_w = (N + 127) // 128
     k_tiles = (K + 63) // 64
     if T <= 64:
@@ -350,8 +351,14 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
         best = min(best, (cost, False, split))
     if allow_pairs and _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS:
         clusters = ((T + 255) // 256) * (tiles_w if gated else (N + 255) // 256)
-        waves = (clusters + sms // 2 - 1) // (sms // 2)
-        best = min(best, (max(waves * (k_tiles * _PLAN_PAIR_STEP_US + _PLAN_PAIR_TILE_US), stream), True, 1))
+        for split in (_PLAN_PAIR_SPLITS if mode == "add" else (1,)):
+            if split > 1 and split > k_tiles // 4:
+                break
+            waves = (clusters * split + sms // 2 - 1) // (sms // 2)
+            cost = max(waves * (((k_tiles + split - 1) // split) * _PLAN_PAIR_STEP_US + _PLAN_PAIR_TILE_US), stream)
+            if split > 1:
+                cost += _PLAN_PAIR_US_PER_ADD * T * N * split
+            best = min(best, (cost, True, split))
     return best[1], best[2]
 
 
@@ -398,7 +405,10 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     if y.dtype != want or tuple(y.shape) != (T, N):
         raise KernelError(f"gemm {mode}: output must be {want} [{T}, {N}], got {y.dtype} {tuple(y.shape)}")
     if split_k is None:
-        pair, split_k = gemm_plan(T, N, K, mode, allow_pairs=pair is not False) if pair is not True else (True, 1)
+        if pair is not True:
+            pair, split_k = gemm_plan(T, N, K, mode, allow_pairs=pair is not False)
+        else:
+            split_k = 1
         if code != 2:
             split_k = 1          # a storing product cut along K is the caller's clear + "add"
     elif pair is None:
@@ -406,7 +416,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     if pair:
         _check(_lib("gemm_bf16_tc2", None, _PAIR_DEFINES).jb_gemm_bf16_pair(
             _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
-            _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
+            int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
     _check(_lib("gemm_bf16_tc", None, _GEMM_DEFINES).jb_gemm_bf16(
         _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,

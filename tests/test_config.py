@@ -105,12 +105,13 @@ def test_product_plan_picks_a_kernel_and_slices_that_the_kernels_take():
         for T in (1, 8, 64, 65, 128, 129, 200, 256, 511, 512, 1000, 2048, 8192):
             for mode in ("add", "store", "swiglu"):
                 pair, split = ops.gemm_plan(T, N, K, mode)
-                assert split >= 1 and (split == 1 or (mode == "add" and not pair and split <= max(1, k_tiles // 4)))
+                assert split >= 1 and (split == 1 or (mode == "add" and split <= max(1, k_tiles // 4)))
                 assert not pair or T >= ops.GEMM_PAIR_MIN_TOKENS
                 assert ops.gemm_plan(T, N, K, mode, allow_pairs=False)[0] is False
-            assert ops.split_k_for(T, N, K) == (1 if ops.gemm_plan(T, N, K, "add")[0] else ops.gemm_plan(T, N, K, "add")[1])
+            assert ops.split_k_for(T, N, K) == ops.gemm_plan(T, N, K, "add")[1]
     assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 9)
     assert ops.gemm_plan(256, 4096, 4096, "add") == (False, 4)       # 32 output tiles: K in four slices
+    assert ops.gemm_plan(512, 4096, 4096, "add") == (True, 2)        # 32 tiles of CTA pairs: K in two
     assert ops.gemm_plan(2048, 4096, 14336, "add") == (True, 1)
     assert ops.gemm_plan(2048, 14336, 4096, "swiglu") == (True, 1)
     assert ops.gemm_plan(64, 14336, 4096, "swiglu") == (False, 1)

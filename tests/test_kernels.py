@@ -340,6 +340,10 @@ def test_gemm_bf16_cta_pairs(ops, T, N, K):
     acc = base.clone()
     ops.gemm_bf16(x, w, acc, mode="add", pair=True)
     close(acc, ref + base.double().cpu(), 2e-5)
+    for split in (2, 5, 1000):                    # slices of K meet by atomic adds; never more slices than k-tiles
+        acc = base.clone()
+        ops.gemm_bf16(x, w, acc, mode="add", pair=True, split_k=split)
+        close(acc, ref + base.double().cpu(), 2e-5)
     ops.check_kernel_status(torch.device(DEV))
 
 
