@@ -296,6 +296,52 @@ def run_workload(name):
                    "vocab": V}}))
 
 
+def run_prompt_lengths(layers):
+    """Prompt steps of 96 to 4,096 tokens at the 8B layer sizes (fewer layers, named in each line): device
+    time of `Model.step` with the logits of the last token, median of 5 after 3 warm-ups.  One JSON line per
+    length; nothing here is the headline."""
+    import torch
+
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers, max_position_embeddings=8192)
+    model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=16384, max_slots=16, norm_std=0.0)
+    g = torch.Generator().manual_seed(0)
+    pk = peaks()
+    for seqs, T in ((1, 96), (1, 128), (1, 256), (1, 384), (1, 512), (1, 768), (1, 1024), (1, 1536), (1, 2048),
+                    (1, 4096), (4, 256), (8, 100)):
+        times = []
+        for _ in range(8):
+            slots = [model.alloc_slot() for _ in range(seqs)]
+            entries = [StepEntry(s, torch.randint(0, cfg["vocab_size"], (T,), generator=g).tolist(), [T - 1])
+                       for s in slots]
+            torch.cuda.synchronize()
+            time.sleep(0.05)
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            model.step(entries)
+            b.record()
+            torch.cuda.synchronize()
+            times.append(a.elapsed_time(b))
+            for s in slots:
+                model.free_slot(s)
+        ms = sorted(times[3:])[2]
+        flops = layers * seqs * (2 * T * layer_weight_elems(cfg) + 2 * 2 * cfg["num_attention_heads"] * cfg["head_dim"]
+                                 * T * (T + 1) / 2)
+        print(json.dumps({"prompt_step": f"{seqs} x {T} tokens", "layers": layers, "layers_of_config": 32,
+                          "ms": round(ms, 3), "tokens_per_s": round(seqs * T / ms * 1e3),
+                          "layer_flops_frac": round(flops / (ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 3),
+                          "peaks": pk.get("source", "fallback")}), flush=True)
+    model.check()
+
+
+def layer_weight_elems(cfg):
+    hd = cfg["head_dim"]
+    qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * hd * cfg["hidden_size"]
+    o = cfg["num_attention_heads"] * hd * cfg["hidden_size"]
+    return qkv + o + 3 * cfg["intermediate_size"] * cfg["hidden_size"]
+
+
 def run_kernels():
     """The step's hot kernels alone at the 8B layer shapes, for the roofline figures under profiles/:
     each is captured 24 times into one CUDA graph (as the engine runs them: back to back, programmatic
@@ -423,6 +469,9 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline batch only")
     ap.add_argument("--workload", default="8b", choices=["8b", "1b", "13b"],
                     help="8b: the headline benchmark; 1b / 13b: the other workloads of BASELINE.json, end to end")
+    ap.add_argument("--prompt-lengths", action="store_true",
+                    help="time prompt steps of 96 to 4,096 tokens at the 8B layer sizes (one JSON line each; "
+                         "--layers, default 8)")
     ap.add_argument("--kernels", action="store_true",
                     help="time the step's hot kernels alone at the 8B layer shapes (one JSON line each)")
     args = ap.parse_args()
@@ -438,6 +487,9 @@ def main():
         args.warmup = 3
     if args.kernels:
         run_kernels()
+        return 0
+    if args.prompt_lengths:
+        run_prompt_lengths(args.layers or 8)
         return 0
     if args.workload != "8b":
         run_workload(args.workload)
