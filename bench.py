@@ -296,7 +296,10 @@ def run_workload(name):
                    "vocab": V}}))
 
 
-def run_prompt_lengths(layers):
+PROMPT_STEPS = "1x96,1x128,1x256,1x384,1x512,1x768,1x1024,1x1536,1x2048,1x4096,4x256,8x100"
+
+
+def run_prompt_lengths(layers, which):
     """Prompt steps of 96 to 4,096 tokens at the 8B layer sizes (fewer layers, named in each line): device
     time of `Model.step` with the logits of the last token, median of 5 after 3 warm-ups.  One JSON line per
     length; nothing here is the headline."""
@@ -308,8 +311,7 @@ def run_prompt_lengths(layers):
     model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=16384, max_slots=16, norm_std=0.0)
     g = torch.Generator().manual_seed(0)
     pk = peaks()
-    for seqs, T in ((1, 96), (1, 128), (1, 256), (1, 384), (1, 512), (1, 768), (1, 1024), (1, 1536), (1, 2048),
-                    (1, 4096), (4, 256), (8, 100)):
+    for seqs, T in (tuple(int(v) for v in item.split("x")) for item in which.split(",")):
         times = []
         for _ in range(8):
             slots = [model.alloc_slot() for _ in range(seqs)]
@@ -469,9 +471,9 @@ def main():
     ap.add_argument("--quick", action="store_true", help="headline batch only")
     ap.add_argument("--workload", default="8b", choices=["8b", "1b", "13b"],
                     help="8b: the headline benchmark; 1b / 13b: the other workloads of BASELINE.json, end to end")
-    ap.add_argument("--prompt-lengths", action="store_true",
-                    help="time prompt steps of 96 to 4,096 tokens at the 8B layer sizes (one JSON line each; "
-                         "--layers, default 8)")
+    ap.add_argument("--prompt-lengths", nargs="?", const=PROMPT_STEPS, default=None, metavar="SEQSxTOKENS,...",
+                    help="time prompt steps at the 8B layer sizes, by default of 96 to 4,096 tokens (one JSON line "
+                         "each; --layers, default 8)")
     ap.add_argument("--kernels", action="store_true",
                     help="time the step's hot kernels alone at the 8B layer shapes (one JSON line each)")
     args = ap.parse_args()
@@ -489,7 +491,7 @@ def main():
         run_kernels()
         return 0
     if args.prompt_lengths:
-        run_prompt_lengths(args.layers or 8)
+        run_prompt_lengths(args.layers or 8, args.prompt_lengths)
         return 0
     if args.workload != "8b":
         run_workload(args.workload)
