@@ -311,6 +311,8 @@ _PLAN_HBM_BYTES_PER_US = 6.68e6     # the weight stream
 _PLAN_US_PER_ADD = 5.14e-7          # one float32 add of a slice of K into the output, single-CTA kernel
 _PLAN_PAIR_US_PER_ADD = 4.26e-7     # the same, CTA pairs
 _PLAN_SPLITS = (1, 2, 3, 4, 6, 8)
+_PLAN_DECODE_MAX_SPLIT = 24
+_PLAN_DECODE_STEPS_PER_ADD = 1e-4   # adds of a 128-row tile's token, in steps along K (fitted: 60 measured cases)
 _PLAN_PAIR_SPLITS = (1, 2, 3, 4, 6)
 
 
@@ -318,8 +320,9 @@ _PLAN_PAIR_SPLITS = (1, 2, 3, 4, 6)
 def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tuple[bool, int]:
     """Which kernel runs x[T, K] . w[N, K]^T and into how many slices of K it is cut: (CTA pairs?, slices).
 
-    Up to 64 tokens the product streams its weights: the single-CTA kernel, with K cut so that about two
-    tiles per SM are in flight (only a product that adds can be cut; its slices meet by atomic adds).
+    Up to 64 tokens the product streams its weights: the single-CTA kernel, with K cut so that the waves of
+    tiles over the SMs x the steps of a slice are fewest (only a product that adds can be cut; its slices
+    meet by atomic adds): 4096 x 4096 makes 32 tiles, and 13 slices of 5 steps in 3 waves beat 9 of 8 in 2.
     Above, the choice is by an estimate of the time: waves of tiles over the SMs x (steps along K x the
     time of a step, tensor-core bound or bound by what an SM takes in per step, + a tile's fixed cost), not
     below the time of the weight stream, plus the atomic adds of a cut K.  Few output tiles (a 4096 x 4096
@@ -327,11 +330,18 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     per flop and win once their 256 x 256 tiles fill the SMs."""
     tiles_w = (N + 127) // 128
     k_tiles = (K + 63) // 64
-    if T <= 64:
-        if mode != "add":
-            return False, 1
-        return False, max(1, min(SM_COUNT_TARGET // max(tiles_w, 1), k_tiles // 4))
     sms = SM_COUNT_TARGET // 2
+    if T <= 64:
+        if mode != "add" or tiles_w >= sms:
+            return False, 1      # a wave of tiles or more streams weights on every SM as it is
+        # the critical path in steps along K: waves of tiles over the SMs x steps of a slice; a little per add
+        best = (float("inf"), 1)
+        for split in range(1, max(1, min(k_tiles // 4, _PLAN_DECODE_MAX_SPLIT)) + 1):
+            waves = (tiles_w * split + sms - 1) // sms
+            cost = waves * ((k_tiles + split - 1) // split) + _PLAN_DECODE_STEPS_PER_ADD * split * T * tiles_w
+            if cost < best[0] - 1e-9:
+                best = (cost, split)
+        return False, best[1]
     gated = mode == "swiglu"
     w_rows = 2 * N if gated else N
     stream = w_rows * K * 2 / _PLAN_HBM_BYTES_PER_US

@@ -109,7 +109,8 @@ def test_product_plan_picks_a_kernel_and_slices_that_the_kernels_take():
                 assert not pair or T >= ops.GEMM_PAIR_MIN_TOKENS
                 assert ops.gemm_plan(T, N, K, mode, allow_pairs=False)[0] is False
             assert ops.split_k_for(T, N, K) == ops.gemm_plan(T, N, K, "add")[1]
-    assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 9)
+    assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 13)      # 416 tiles in 3 waves of 5 steps each
+    assert ops.gemm_plan(64, 4096, 4096, "add") == (False, 4)       # more tokens, more adds: one wave of 16 steps
     assert ops.gemm_plan(256, 4096, 4096, "add") == (False, 4)       # 32 output tiles: K in four slices
     assert ops.gemm_plan(512, 4096, 4096, "add") == (True, 2)        # 32 tiles of CTA pairs: K in two
     assert ops.gemm_plan(2048, 4096, 14336, "add") == (True, 1)
