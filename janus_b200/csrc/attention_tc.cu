@@ -189,6 +189,81 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Two float32 in one 64-bit register pair: sm_100's fma/add/mul .f32x2 work on both halves in one
+// instruction, and max takes three inputs; the softmax rows below are bound by the number of
+// instructions they issue, which these halve.
+__device__ __forceinline__ uint64_t pack2(float lo, float hi) {
+  uint64_t r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void unpack2(uint64_t v, float& lo, float& hi) {
+  asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(v));
+}
+__device__ __forceinline__ uint64_t fma2(uint64_t a, uint64_t b, uint64_t c) {
+  uint64_t r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+__device__ __forceinline__ uint64_t add2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ uint64_t mul2(uint64_t a, uint64_t b) {
+  uint64_t r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float r;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(r) : "f"(a), "f"(b), "f"(c));
+  return r;
+}
+// The largest of N scores (N = 4 + 8 k + 4): four chains of three-input maxima.
+template <int N>
+__device__ __forceinline__ float row_max(const uint32_t* sr) {
+  static_assert(N >= 8 && (N - 8) % 8 == 0, "row_max: N must be 8, 16, 24, ...");
+  float m[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) m[e] = fmaxf(__uint_as_float(sr[e]), __uint_as_float(sr[N - 4 + e]));
+#pragma unroll
+  for (int c = 4; c + 8 <= N - 4; c += 8) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) m[e] = max3(m[e], __uint_as_float(sr[c + 2 * e]), __uint_as_float(sr[c + 2 * e + 1]));
+  }
+  return max3(m[0], m[1], fmaxf(m[2], m[3]));
+}
+// p[c] = 2^(s[c] * scale_log2 + neg_ref) for N scores in sr; the results overwrite the first N / 2 words of
+// sr as bf16 pairs; returns their float32 sum.
+template <int N>
+__device__ __forceinline__ float exp_pack_sum(uint32_t* sr, float scale_log2, float neg_ref) {
+  const uint64_t s2 = pack2(scale_log2, scale_log2), n2 = pack2(neg_ref, neg_ref);
+  uint64_t acc[4] = {0ull, 0ull, 0ull, 0ull};   // the bit pattern of (0.0f, 0.0f)
+#pragma unroll
+  for (int c = 0; c < N / 2; ++c) {
+    float a, b;
+    unpack2(fma2(pack2(__uint_as_float(sr[2 * c]), __uint_as_float(sr[2 * c + 1])), s2, n2), a, b);
+    const float p0 = fast_exp2(a), p1 = fast_exp2(b);
+    acc[c & 3] = add2(acc[c & 3], pack2(p0, p1));
+    sr[c] = pack_bf16(p0, p1);
+  }
+  float lo, hi;
+  unpack2(add2(add2(acc[0], acc[1]), add2(acc[2], acc[3])), lo, hi);
+  return lo + hi;
+}
+// r[0..15] *= f
+__device__ __forceinline__ void scale16(uint32_t* r, float f) {
+  const uint64_t f2 = pack2(f, f);
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    float a, b;
+    unpack2(mul2(pack2(__uint_as_float(r[i]), __uint_as_float(r[i + 1])), f2), a, b);
+    r[i] = __float_as_uint(a);
+    r[i + 1] = __float_as_uint(b);
+  }
+}
+
 template <int NT>
 __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
@@ -354,10 +429,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
           if (!(kp <= row_pos && kp >= row_lo)) sr[c] = 0xff800000u;  // -inf
         }
       }
-      float mx = -CUDART_INF_F;
-#pragma unroll
-      for (int c = 0; c < 64; ++c) mx = fmaxf(mx, __uint_as_float(sr[c]));
-      mx *= scale_log2;  // the scale is positive: the maximum commutes with it
+      const float mx = row_max<64>(sr) * scale_log2;  // the scale is positive: the maximum commutes with it
       // tcgen05.ld/st are warp-wide: the warp rescales together if any of its rows has to
       const bool grow = mx > m_ref + RESCALE_LOG2 || (m_ref == -CUDART_INF_F && mx > -CUDART_INF_F);
       if (__any_sync(0xffffffffu, grow)) {
@@ -372,8 +444,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
             uint32_t r[16];
             tmem_ld16(lane_addr + o_col + c0, r);
             tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            scale16(r, corr);
             tmem_st16(lane_addr + o_col + c0, r);
           }
           tmem_st_wait();
@@ -382,17 +453,8 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
         m_ref = m_new;
       }
       const float neg_ref = m_ref == -CUDART_INF_F ? 0.0f : -m_ref;
-      float sum = 0.0f;
-      // P_j as bf16 into the swizzled tile: 16-byte chunk c of row r lies at r*128 + ((c ^ (r & 7)) * 16)
       // P_j as bf16 pairs over the first 32 columns of this S buffer (its scores are in registers by now)
-#pragma unroll
-      for (int c = 0; c < 32; ++c) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), scale_log2, neg_ref));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, neg_ref));
-        sum += p0 + p1;
-        sr[c] = pack_bf16(p0, p1);
-      }
-      l += sum;
+      l += exp_pack_sum<64>(sr, scale_log2, neg_ref);
       tmem_st16(lane_addr + s_col + b * 64, sr);
       tmem_st16(lane_addr + s_col + b * 64 + 16, sr + 16);
       tmem_st_wait();
@@ -608,13 +670,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
           if (!(kp <= row_pos && kp >= row_lo)) sr[c] = 0xff800000u;  // -inf
         }
       }
-      float mx4[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};
-#pragma unroll
-      for (int c = 0; c < KB; c += 4) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) mx4[e] = fmaxf(mx4[e], __uint_as_float(sr[c + e]));
-      }
-      const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;
+      const float mx = row_max<KB>(sr) * scale_log2;
       const bool grow = mx > m_ref + RESCALE_LOG2 || (m_ref == -CUDART_INF_F && mx > -CUDART_INF_F);
       if (__any_sync(0xffffffffu, grow)) {
         const float m_new = fmaxf(m_ref, mx);
@@ -628,8 +684,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
             uint32_t r[16];
             tmem_ld16(lane_addr + o_col + c0, r);
             tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 16; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) * corr);
+            scale16(r, corr);
             tmem_st16(lane_addr + o_col + c0, r);
           }
           tmem_st_wait();
@@ -638,15 +693,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
         m_ref = m_new;
       }
       const float neg_ref = m_ref == -CUDART_INF_F ? 0.0f : -m_ref;
-      float sum4[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-      for (int c = 0; c < KB / 2; ++c) {
-        const float p0 = fast_exp2(fmaf(__uint_as_float(sr[2 * c]), scale_log2, neg_ref));
-        const float p1 = fast_exp2(fmaf(__uint_as_float(sr[2 * c + 1]), scale_log2, neg_ref));
-        sum4[c & 3] += p0 + p1;
-        sr[c] = pack_bf16(p0, p1);
-      }
-      l += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      l += exp_pack_sum<KB>(sr, scale_log2, neg_ref);
 #pragma unroll
       for (int c0 = 0; c0 < KB / 2; c0 += 16) tmem_st16(lane_addr + s_col + c0, sr + c0);
       tmem_st_wait();
