@@ -98,6 +98,7 @@ class Engine:
         self.workspace = Workspace(self.device)
         self._pinned: Optional[torch.Tensor] = None
         self._graphs: Dict[Tuple, object] = {}
+        self._capture_stream: Optional[torch.cuda.Stream] = None
         self.last_graph_launches = 0       # kernels of this library in the last step
         self.last_step_h2d_bytes = 0       # bytes of the last step's index buffer
         # per slot: the token sampled last by a graph step, so that the next step can
@@ -307,13 +308,23 @@ class Engine:
             graph = torch.cuda.CUDAGraph()
             before = ops.launch_count()
             # No garbage collection while capturing: collecting an older engine would destroy
-            # its CUDA graphs in the middle of this capture, which invalidates it.
-            gc.collect()
+            # its CUDA graphs in the middle of this capture, which invalidates it.  The capture is
+            # begun and ended by hand on a stream of its own: `torch.cuda.graph` would synchronise,
+            # run a full collection (25 ms) and empty the allocator's cache at every new graph.
             gc_was_on = gc.isenabled()
             gc.disable()
             try:
-                with torch.cuda.graph(graph):
-                    rec.run_forward()
+                if self._capture_stream is None:
+                    self._capture_stream = torch.cuda.Stream(device=self.device)
+                side = self._capture_stream
+                side.wait_stream(torch.cuda.current_stream(self.device))
+                with torch.cuda.stream(side):
+                    graph.capture_begin()
+                    try:
+                        rec.run_forward()
+                    finally:
+                        graph.capture_end()
+                torch.cuda.current_stream(self.device).wait_stream(side)
             finally:
                 if gc_was_on:
                     gc.enable()
