@@ -153,6 +153,36 @@ __global__ void swiglu_kernel(const TT* __restrict__ gate_up, TT* __restrict__ o
   out[i] = jb::from_f32<TT>(s * u);
 }
 
+// gate_up: float32 [T, ld], gate of feature c in column c, up in column up_col + c; out: bfloat16 [T, I].
+// VEC = 4: four features a thread (I, ld and up_col multiples of 4, 16-byte aligned rows).
+template <int VEC>
+__global__ void swiglu_f32_bf16_kernel(const float* __restrict__ gate_up, bf16* __restrict__ out, int I, int ld, int up_col,
+                                       size_t n) {
+  jb::pdl_launch_dependents();
+  jb::pdl_wait();
+  const size_t i = ((size_t)blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  if (i >= n) return;
+  const size_t t = i / I, c = i % I;
+  const float* row = gate_up + t * ld + c;
+  float g[VEC], u[VEC];
+  if (VEC == 4) {
+    const float4 g4 = *reinterpret_cast<const float4*>(row), u4 = *reinterpret_cast<const float4*>(row + up_col);
+    g[0] = g4.x; g[1] = g4.y; g[2] = g4.z; g[3] = g4.w;
+    u[0] = u4.x; u[1] = u4.y; u[2] = u4.z; u[3] = u4.w;
+  } else {
+    g[0] = row[0];
+    u[0] = row[up_col];
+  }
+  bf16 y[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) y[e] = __float2bfloat16_rn(g[e] * (1.0f / (1.0f + expf(-g[e]))) * u[e]);
+  if (VEC == 4) {
+    *reinterpret_cast<uint2*>(out + i) = *reinterpret_cast<const uint2*>(y);
+  } else {
+    out[i] = y[0];
+  }
+}
+
 __global__ void zero_f32_kernel(float4* __restrict__ p, size_t n4) {
   jb::pdl_launch_dependents();
   jb::pdl_wait();
@@ -232,6 +262,21 @@ JB_EXPORT int jb_swiglu(const void* gate_up, void* out, int dtype, int T, int I,
   else
     return JB_ERR_BAD_DTYPE;
   return (int)e;
+}
+
+// out[t, c] = silu(gate_up[t, c]) * gate_up[t, up_col + c] with float32 in (rows of ld floats) and bfloat16 out
+// [T, I]: the activation of a gated product that was run as a plain product of the stacked gate and up rows.
+JB_EXPORT int jb_swiglu_f32_to_bf16(const float* gate_up, int ld, int up_col, void* out, int T, int I, cudaStream_t stream) {
+  const size_t n = (size_t)T * I;
+  if (n == 0) return 0;
+  JB_REFUSE(ld < up_col + I || up_col < I, "swiglu: rows of %d floats do not hold %d gate and %d up features from column %d",
+            ld, I, I, up_col);
+  const bool vec = I % 4 == 0 && ld % 4 == 0 && up_col % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
+  const size_t threads_needed = vec ? n / 4 : n;
+  jb::Launch cfg(dim3((unsigned)((threads_needed + 255) / 256)), dim3(256), 0, stream);
+  if (vec)
+    return (int)cudaLaunchKernelEx(&cfg.c, swiglu_f32_bf16_kernel<4>, gate_up, (bf16*)out, I, ld, up_col, n);
+  return (int)cudaLaunchKernelEx(&cfg.c, swiglu_f32_bf16_kernel<1>, gate_up, (bf16*)out, I, ld, up_col, n);
 }
 
 // Fill n floats with zero (n a multiple of 4, p 16-byte aligned): the target of a

@@ -150,6 +150,17 @@ def swiglu(gate_up: torch.Tensor, out: torch.Tensor) -> None:
            "swiglu")
 
 
+def swiglu_f32_to_bf16(gate_up: torch.Tensor, out: torch.Tensor, up_col: int) -> None:
+    """out[t, c] = silu(gate_up[t, c]) * gate_up[t, up_col + c]; float32 in, bfloat16 out."""
+    T, I = out.shape
+    _need(gate_up, "swiglu input", torch.float32)
+    _need(out, "swiglu out", torch.bfloat16)
+    if gate_up.dim() != 2 or gate_up.shape[0] != T:
+        raise KernelError(f"swiglu: input of shape {tuple(gate_up.shape)} does not hold {T} rows")
+    _check(_lib("elementwise").jb_swiglu_f32_to_bf16(_ptr(gate_up), gate_up.shape[1], int(up_col), _ptr(out), T, I,
+                                                      _stream()), "swiglu_f32_to_bf16")
+
+
 def zero_f32(t: torch.Tensor) -> None:
     """Fill a float32 tensor with zeros (whole 16-byte vectors)."""
     _need(t, "zero target", torch.float32)
@@ -264,6 +275,13 @@ class PackedWeight:
             raise KernelError(f"first_rows({rows}) of a packed matrix of {self.rows} rows")
         return PackedWeight(self.tiles[: (rows + 127) // 128], rows, self.cols)
 
+    def stacked(self) -> "PackedWeight":
+        """A gated pair as the plain matrix of its row tiles: the gate rows (padded to whole tiles of 128),
+        then the up rows from row 128 * up_tile_offset on (shares storage)."""
+        if not self.up_tile_offset:
+            raise KernelError("stacked(): the weight is no gated pair")
+        return PackedWeight(self.tiles, self.tiles.shape[0] * 128, self.cols)
+
 
 def pack_weight(w: torch.Tensor) -> PackedWeight:
     """Row-major bfloat16 [N, K] (K a multiple of 8) -> PackedWeight."""
@@ -282,6 +300,18 @@ def pack_gated(gate: torch.Tensor, up: torch.Tensor) -> PackedWeight:
         raise KernelError(f"pack_gated: shapes {tuple(gate.shape)} and {tuple(up.shape)} differ")
     g, u = pack_weight(gate), pack_weight(up)
     return PackedWeight(torch.cat([g.tiles, u.tiles], dim=0), gate.shape[0], gate.shape[1], g.tiles.shape[0])
+
+
+def gated_runs_unfused(T: int, I: int) -> bool:
+    """Whether a SiLU-gated product of I features runs as a plain product of the stacked gate and up rows
+    into float32 and an activation kernel: decode-sized steps of narrow layers, where the fused kernel's
+    tiles (128 features, gate and up rows together) fill less than half of the SMs.  Measured at 8192
+    features (64 tiles): 13.6 us against 15.1 at 8 tokens, 17.6 against 21.5 at 64; at 13824 and 14336
+    features the fused kernel is faster (45.5 against 45.8 to 51.9, 37.1 against 40.0 to 44.6)."""
+    return _GATED_UNFUSED and T <= 64 and 2 * ((I + 127) // 128) <= SM_COUNT_TARGET // 2
+
+
+_GATED_UNFUSED = os.environ.get("JANUS_GATED_UNFUSED", "1") != "0"
 
 
 def split_k_for(T: int, N: int, K: int) -> int:

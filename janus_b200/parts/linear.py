@@ -98,6 +98,7 @@ class GatedLinear:
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
         self.weight = None   # float32: [2 * out, in] row-major; bfloat16: a packed gated pair
+        self._stacked = None  # bfloat16: the same tiles as one plain matrix (gate rows, then up rows)
 
     def load(self, gate: torch.Tensor, up: torch.Tensor) -> None:
         g, u = _to_engine(gate, self.dtype, self.device), _to_engine(up, self.dtype, self.device)
@@ -106,11 +107,19 @@ class GatedLinear:
                 raise ValueError(f"gate/up weight of shape {tuple(t.shape)} does not fit "
                                  f"({self.out_features}, {self.in_features})")
         self.weight = ops.pack_gated(g, u) if self.dtype == torch.bfloat16 else torch.cat([g, u], dim=0)
+        self._stacked = None
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, ctx) -> None:
         if self.dtype == torch.float32:
             gu = ctx.workspace.get("gate_up", (x.shape[0], 2 * self.out_features), torch.float32)
             ops.gemm_f32(x, self.weight, gu, accumulate=False)
             ops.swiglu(gu, out)
+        elif ops.gated_runs_unfused(x.shape[0], self.out_features):
+            # few tokens, narrow layer: twice the tiles stream the weights as a plain product; the gate is applied after
+            if self._stacked is None:
+                self._stacked = self.weight.stacked()
+            gu = ctx.workspace.get("gate_up", (x.shape[0], self._stacked.rows), torch.float32)
+            ops.gemm_bf16(x, self._stacked, gu, mode="store", pair=False)
+            ops.swiglu_f32_to_bf16(gu, out, 128 * self.weight.up_tile_offset)
         else:
             ops.gemm_bf16(x, self.weight, out, mode="swiglu")

@@ -67,6 +67,39 @@ def test_residual_add_and_swiglu(ops):
     close(out, P.silu(gu[:, :I].cpu()) * gu[:, I:].cpu(), 2e-6)
 
 
+@pytest.mark.parametrize("T, I, up_col, ld", [(13, 328, 384, 768), (5, 131, 256, 512), (64, 8192, 8192, 16384)])
+def test_swiglu_of_a_stacked_product(ops, T, I, up_col, ld):
+    """The activation kernel behind a gated product that ran as a plain product: float32 rows with the up
+    features from a column of their own on, bfloat16 out; four features a thread or one."""
+    gu = torch.randn(T, ld, device=DEV) * 2
+    out = torch.full((T, I), float("nan"), device=DEV, dtype=torch.bfloat16)
+    ops.swiglu_f32_to_bf16(gu, out, up_col)
+    ref = (P.silu(gu[:, :I].cpu()) * gu[:, up_col:up_col + I].cpu()).to(torch.bfloat16)
+    close(out, ref.float(), 6e-3)
+
+
+@pytest.mark.parametrize("T", [1, 17, 64])
+@pytest.mark.parametrize("I, K", [(192, 64), (320, 96), (1000, 2048)])
+def test_gated_product_run_as_plain_product_and_activation(ops, T, I, K):
+    """What a narrow layer's gated product does at decode sizes: the packed gated pair read as one stacked
+    matrix (gate tiles, then up tiles), a float32 store product, the activation kernel."""
+    assert ops.gated_runs_unfused(T, I)
+    x, w = bf16_inputs(T, 2 * I, K, T + I + 2)
+    w = (w.float() * 3).to(torch.bfloat16)
+    gated = ops.pack_gated(w[:I].contiguous(), w[I:].contiguous())
+    stacked = gated.stacked()
+    gu = torch.full((T, stacked.rows), float("nan"), device=DEV)
+    ops.gemm_bf16(x, stacked, gu, mode="store", pair=False)
+    y = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
+    ops.swiglu_f32_to_bf16(gu, y, 128 * gated.up_tile_offset)
+    ref = P.swiglu_ffn(x.double().cpu(), w[:I].double().cpu(), w[I:].double().cpu(), torch.eye(I, dtype=torch.float64))
+    close(y, ref, 6e-3)
+    fused = torch.empty(T, I, device=DEV, dtype=torch.bfloat16)
+    ops.gemm_bf16(x, gated, fused, mode="swiglu", pair=False)
+    close(fused, ref, 6e-3)
+    ops.check_kernel_status(torch.device(DEV))
+
+
 # ---------------------------------------------------------------- rope + cache
 @pytest.mark.parametrize("in_dt, out_dt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
                                            (torch.bfloat16, torch.bfloat16)])
