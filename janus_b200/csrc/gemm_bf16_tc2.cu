@@ -19,7 +19,9 @@
 // The stacked q/k/v projection of a prompt lies the same way (tokens on the rows, 256 features = whole heads
 // on the columns): its epilogue rotates q and k by the token's position and writes q as bfloat16 and k, v
 // straight into the paged cache, so the projection's float32 output never goes to memory.
-// The kernel is persistent (pair p computes tiles p, p + pairs, ...) with two accumulator buffers.
+// The kernel is persistent (pair p computes tiles p, p + pairs, ...) with two accumulator buffers.  An adding
+// product may be cut along K: the slices of an output tile are tiles of their own, next to each other in the
+// order, and meet by atomic adds (few output tiles would leave most SMs idle otherwise).
 // Every mbarrier wait is bounded in time (status codes 21-23).  No TMA load uses multicast.
 #include <cuda.h>
 #include <stdio.h>
