@@ -302,6 +302,24 @@ def pack_gated(gate: torch.Tensor, up: torch.Tensor) -> PackedWeight:
     return PackedWeight(torch.cat([g.tiles, u.tiles], dim=0), gate.shape[0], gate.shape[1], g.tiles.shape[0])
 
 
+# JANUS_DETERMINISTIC=1 (or `set_deterministic(True)` before a model is built): no product is cut along K,
+# so no sums meet by atomic adds in an order that differs from run to run, and the same requests give the
+# same bits.  It costs about a third of the decode throughput at the 8B sizes (q/k/v, o and down projections
+# of a few tokens then run on 32 to 48 of the 148 SMs).
+_deterministic = [os.environ.get("JANUS_DETERMINISTIC", "0") == "1"]
+
+
+def set_deterministic(flag: bool) -> None:
+    """Switch cutting of K (atomic adds) off or on for products launched from now on; decode steps that an
+    engine has already captured into CUDA graphs keep what they were captured with."""
+    _deterministic[0] = bool(flag)
+    gemm_plan.cache_clear()
+
+
+def is_deterministic() -> bool:
+    return _deterministic[0]
+
+
 def gated_runs_unfused(T: int, I: int) -> bool:
     """Whether a SiLU-gated product of I features runs as a plain product of the stacked gate and up rows
     into float32 and an activation kernel: decode-sized steps of narrow layers, where the fused kernel's
@@ -361,6 +379,8 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     tiles_w = (N + 127) // 128
     k_tiles = (K + 63) // 64
     sms = SM_COUNT_TARGET // 2
+    if _deterministic[0] and mode == "add":
+        mode = "add uncut"           # the same choice between the kernels, K whole
     if T <= 64:
         if mode != "add" or tiles_w >= sms:
             return False, 1      # a wave of tiles or more streams weights on every SM as it is

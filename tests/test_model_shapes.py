@@ -79,6 +79,32 @@ def test_long_prompt_runs_the_pair_products(big_model):
     ops.check_kernel_status(model.device)
 
 
+def test_deterministic_mode_gives_the_same_bits_twice(big_model):
+    """With no product cut along K nothing is summed by atomic adds in an order of the day: two engines built
+    one after the other give bitwise equal logits for a prompt and for decoded tokens."""
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    from janus_b200.kernels import ops
+    d, ids, ref = big_model
+    assert ops.split_k_for(8, 4096, 4096) > 1
+    ops.set_deterministic(True)
+    try:
+        assert ops.split_k_for(8, 4096, 4096) == 1 and ops.split_k_for(300, 4096, 14336) == 1
+        runs = []
+        for _ in range(2):
+            model = janus_b200.load(d, dtype="bfloat16", max_tokens=1024)
+            a = model.alloc_slot()
+            rows = [model.step([StepEntry(a, ids[0][:300], range(300))]).cpu()]
+            for j in range(300, 312):
+                rows.append(model.step([StepEntry(a, [ids[0][j]], [0])]).cpu())
+            runs.append(torch.cat(rows))
+            model.check()
+        assert torch.equal(runs[0], runs[1])
+        assert rel_err(runs[0].numpy(), ref[0][:312]) < tol_for("bfloat16")
+    finally:
+        ops.set_deterministic(False)
+
+
 # A context of several thousand keys: 71 pages a sequence, so that decode attention cuts its keys into
 # splits that meet in the combine kernel, prompts run the products that work in CTA pairs and many row
 # tiles of the tensor-core attention, and the llama3 frequency regions all occur among the positions.
