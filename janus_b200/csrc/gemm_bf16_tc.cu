@@ -190,6 +190,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                                           int T, int N_out, int ldy, int k_tiles, int k_tiles_per_split,
                                                           int n_tiles, int n_tok_tiles, int n_w_tiles,
                                                           int up_tile_offset, int atomic_add,
+                                                          float* __restrict__ partials, int* __restrict__ tickets,
                                                           int* __restrict__ status) {
   using C = Cfg<BN, MODE>;
   extern __shared__ uint8_t smem_raw[];
@@ -197,6 +198,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * C::STAGE_BYTES);
   uint32_t* tmem_slot = (uint32_t*)(bars + 2 * STAGES + 4);
+  volatile int* last_flag = (volatile int*)(tmem_slot + 1);   // ordered sums: "this CTA's slice arrived last"
   const uint32_t smem_base = smem_u32(smem);
   const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * STAGES;
   const uint32_t acc_full0 = full0 + 16 * STAGES, acc_empty0 = acc_full0 + 16;
@@ -320,6 +322,61 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       const int f = tc.m0 + quarter * 32 + lane;
       const bool f_ok = f < N_out;
       const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
+      if (MODE == ADD_F32 && atomic_add && partials != nullptr) {
+        // Slices of K summed in a fixed order (the same bits every run): every slice leaves its tile in
+        // scratch, [output tile][slice][column][128 rows], and takes a ticket of the output tile; the slice
+        // that arrives last adds all of them up in slice order and adds the sum to Y.  Nobody waits.
+        const int out_tiles = n_tok_tiles * n_w_tiles;
+        const int out_tile = tile % out_tiles, slice = tile / out_tiles, slices = n_tiles / out_tiles;
+        const int row = quarter * 32 + lane;
+        float* mine = partials + ((size_t)(out_tile * slices + slice) * BN) * BM + row;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += 16) {
+          if (tc.t0 + c0 >= T) break;  // uniform
+          uint32_t r[16];
+          tmem_ld16(lane_base + c0, r);
+          tmem_ld_wait();
+#pragma unroll
+          for (int jj = 0; jj < 16; ++jj)
+            if (tc.t0 + c0 + jj < T) mine[(size_t)(c0 + jj) * BM] = __uint_as_float(r[jj]);
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);   // the MMA warp may go on with this buffer
+        __threadfence();
+        asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps
+        if (warp == 2 && lane == 0) {
+          const int before = atomicAdd(tickets + out_tile, 1);
+          const int last = before == slices - 1;
+          if (last) tickets[out_tile] = 0;                 // every slice has arrived: ready for the next launch
+          *last_flag = last;
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");
+        if (*last_flag) {
+          __threadfence();
+          const float* all = partials + ((size_t)out_tile * slices * BN) * BM + row;
+          const int cols = min(BN, T - tc.t0);
+          // eight columns at a time: their loads are in flight together; each column's slices are added in
+          // slice order; the sum goes to Y by a reduction that nobody else adds to (so its order is fixed too)
+#pragma unroll 1
+          for (int c0 = 0; c0 < cols; c0 += 8) {
+            float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll 4
+            for (int sl = 0; sl < slices; ++sl) {
+              const float* p = all + ((size_t)sl * BN + c0) * BM;
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj)
+                if (c0 + jj < cols) sum[jj] += __ldcg(p + (size_t)jj * BM);
+            }
+            if (f_ok) {
+#pragma unroll
+              for (int jj = 0; jj < 8; ++jj)
+                if (c0 + jj < cols) atomicAdd((float*)Y + (size_t)(tc.t0 + c0 + jj) * ldy + f, sum[jj]);
+            }
+          }
+        }
+        continue;
+      }
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (tc.t0 + c0 >= T) break;  // uniform
@@ -429,9 +486,17 @@ int sm_count() {
   return n;
 }
 
+// Scratch of a product whose slices of K are summed in a fixed order (null pointers: atomic adds).
+struct Ordered {
+  float* partials;
+  long long partial_floats;
+  int* tickets;      // zero before the first use; every launch leaves them zero
+  int n_tickets;
+};
+
 template <int BN, int MODE, int STAGES>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_out, int ldy, int k_tiles,
-           int split_k, int up_tile_offset, int* status, cudaStream_t stream) {
+           int split_k, int up_tile_offset, const Ordered& ordered, int* status, cudaStream_t stream) {
   using C = Cfg<BN, MODE>;
   constexpr int smem = STAGES * C::STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static int ctas_per_sm = 0;
@@ -450,22 +515,33 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_o
   const int n_tok_tiles = (T + BN - 1) / BN, n_w_tiles = (N_out + BM - 1) / BM;
   const long long n_tiles = (long long)n_tok_tiles * n_w_tiles * splits;
   JB_REFUSE(n_tiles > 0x7fffffffLL, "gemm_bf16: too many tiles (%lld)", n_tiles);
+  const bool in_order = splits > 1 && ordered.partials != nullptr;
+  if (in_order) {
+    const long long out_tiles = (long long)n_tok_tiles * n_w_tiles;
+    JB_REFUSE(ordered.tickets == nullptr || out_tiles > ordered.n_tickets ||
+                  n_tiles * (long long)BN * BM > ordered.partial_floats,
+              "gemm_bf16: ordered sums of %lld tiles of %d x %d need %lld floats of scratch and %lld tickets "
+              "(given: %lld, %d)", n_tiles, BM, BN, n_tiles * (long long)BN * BM, out_tiles, ordered.partial_floats,
+              ordered.n_tickets);
+  }
   const int grid = (int)min(n_tiles, (long long)sm_count() * ctas_per_sm);
   jb::Launch cfg(dim3(grid), dim3(THREADS), smem, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, gemm_tc_kernel<BN, MODE, STAGES>, mw, mx, Y, T, N_out, ldy, k_tiles, per,
-                                 (int)n_tiles, n_tok_tiles, n_w_tiles, up_tile_offset, splits > 1 ? 1 : 0, status);
+                                 (int)n_tiles, n_tok_tiles, n_w_tiles, up_tile_offset, splits > 1 ? 1 : 0,
+                                 in_order ? ordered.partials : (float*)nullptr, in_order ? ordered.tickets : (int*)nullptr,
+                                 status);
 }
 
 template <int MODE>
 int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, int K, int ldy, int split_k,
-             int up_tile_offset, int* status, cudaStream_t stream) {
+             int up_tile_offset, const Ordered& ordered, int* status, cudaStream_t stream) {
   const int k_tiles = (K + BK - 1) / BK;
   CUtensorMap mx;
 #define JB_GO(BN_, ST_)                                                                                 \
   {                                                                                                     \
     if (!make_map(&mx, X, (uint64_t)T, (uint64_t)K, BN_)) return JB_ERR_TENSORMAP;                      \
-    return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_tile_offset, status,    \
-                                  stream);                                                              \
+    return launch<BN_, MODE, ST_>(mw, mx, Y, T, N_out, ldy, k_tiles, split_k, up_tile_offset, ordered,   \
+                                  status, stream);                                                      \
   }
   // Decode-sized token counts: small stages so that two or more CTAs share an SM
   // and keep enough loads in flight; prefill: wide tiles, deep ring.
@@ -487,10 +563,15 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
 // (`w_tiles` tiles of 16 KB in all; for mode SWIGLU the gate rows' tiles first and the up rows' tiles from row
 // tile `up_tile_offset` on); Y: [T, ldy] with N_out columns used.
 // mode: 0 store bf16, 1 store f32, 2 add into f32, 3 silu(gate)*up -> bf16.
-// split_k > 1 only with mode 2 (partial sums meet in Y through atomic adds).
+// split_k > 1 only with mode 2: partial sums meet in Y through atomic adds, or, if `partials` (room for
+// `partial_floats` floats) and `tickets` (`n_tickets` ints, zero) are given, in the fixed order of the slices:
+// tiles x slices x 128 x token tile floats and one ticket per output tile are needed (token tile: 16, 32, 64,
+// 128 or 256, the smallest that holds T).
 // `status` is a device int that a timed-out wait sets to 1 (producer), 2 (MMA) or 3 (epilogue).
 JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
-                           int N_out, int K, int ldy, int mode, int split_k, int* status, cudaStream_t stream) {
+                           int N_out, int K, int ldy, int mode, int split_k, float* partials, long long partial_floats,
+                           int* tickets, int n_tickets, int* status, cudaStream_t stream) {
+  const Ordered ordered{partials, partial_floats, tickets, n_tickets}, none{nullptr, 0, nullptr, 0};
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16: operands must be 16-byte aligned");
@@ -503,9 +584,9 @@ JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, long long w_tiles, int 
   CUtensorMap mw;
   if (!make_packed_map(&mw, W, (uint64_t)w_tiles)) return JB_ERR_TENSORMAP;
   switch (mode) {
-    case STORE_BF16: return dispatch<STORE_BF16>(mw, X, Y, T, N_out, K, ldy, 1, 0, status, stream);
-    case STORE_F32: return dispatch<STORE_F32>(mw, X, Y, T, N_out, K, ldy, 1, 0, status, stream);
-    case ADD_F32: return dispatch<ADD_F32>(mw, X, Y, T, N_out, K, ldy, split_k, 0, status, stream);
-    default: return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, up_tile_offset, status, stream);
+    case STORE_BF16: return dispatch<STORE_BF16>(mw, X, Y, T, N_out, K, ldy, 1, 0, none, status, stream);
+    case STORE_F32: return dispatch<STORE_F32>(mw, X, Y, T, N_out, K, ldy, 1, 0, none, status, stream);
+    case ADD_F32: return dispatch<ADD_F32>(mw, X, Y, T, N_out, K, ldy, split_k, 0, ordered, status, stream);
+    default: return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, up_tile_offset, none, status, stream);
   }
 }

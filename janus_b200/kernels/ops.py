@@ -302,10 +302,10 @@ def pack_gated(gate: torch.Tensor, up: torch.Tensor) -> PackedWeight:
     return PackedWeight(torch.cat([g.tiles, u.tiles], dim=0), gate.shape[0], gate.shape[1], g.tiles.shape[0])
 
 
-# JANUS_DETERMINISTIC=1 (or `set_deterministic(True)` before a model is built): no product is cut along K,
-# so no sums meet by atomic adds in an order that differs from run to run, and the same requests give the
-# same bits.  It costs about a third of the decode throughput at the 8B sizes (q/k/v, o and down projections
-# of a few tokens then run on 32 to 48 of the 148 SMs).
+# JANUS_DETERMINISTIC=1 (or `set_deterministic(True)` before a model is built): the slices of a cut K are
+# summed in the fixed order of the slices instead of by atomic adds in the order they happen to finish, so the
+# same requests give the same bits.  Every slice leaves its tile in scratch; the one that arrives last at the
+# output tile's ticket adds them up (single-CTA kernel; CTA pairs then run uncut).
 _deterministic = [os.environ.get("JANUS_DETERMINISTIC", "0") == "1"]
 
 
@@ -318,6 +318,28 @@ def set_deterministic(flag: bool) -> None:
 
 def is_deterministic() -> bool:
     return _deterministic[0]
+
+
+ORDERED_SCRATCH_MAX_BYTES = 256 << 20
+_ORDERED_TICKETS = 1 << 16
+_ordered_scratch = {}     # device -> (partials, tickets); outgrown buffers stay alive for captured graphs
+_ordered_retired = []
+
+
+def _ordered_buffers(device: torch.device, floats: int):
+    """Scratch for ordered sums of `floats` floats on `device` (None if that is more than the cap)."""
+    if floats * 4 > ORDERED_SCRATCH_MAX_BYTES:
+        return None
+    have = _ordered_scratch.get(device)
+    if have is None or have[0].numel() < floats:
+        size = max(floats, 2 * have[0].numel() if have is not None else (8 << 20) // 4)
+        size = min(size, ORDERED_SCRATCH_MAX_BYTES // 4)
+        tickets = have[1] if have is not None else torch.zeros(_ORDERED_TICKETS, dtype=torch.int32, device=device)
+        if have is not None:
+            _ordered_retired.append(have[0])
+        have = (torch.empty(size, dtype=torch.float32, device=device), tickets)
+        _ordered_scratch[device] = have
+    return have
 
 
 def gated_runs_unfused(T: int, I: int) -> bool:
@@ -362,6 +384,7 @@ _PLAN_SPLITS = (1, 2, 3, 4, 6, 8)
 _PLAN_DECODE_MAX_SPLIT = 24
 _PLAN_DECODE_STEPS_PER_ADD = 1e-4   # adds of a 128-row tile's token, in steps along K (fitted: 60 measured cases)
 _PLAN_PAIR_SPLITS = (1, 2, 3, 4, 6)
+_PLAN_ORDERED_TILE_US = 3.0         # deterministic mode: fence, ticket and ordered sum of a tile of a cut K
 
 
 @functools.lru_cache(maxsize=4096)
@@ -379,8 +402,7 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     tiles_w = (N + 127) // 128
     k_tiles = (K + 63) // 64
     sms = SM_COUNT_TARGET // 2
-    if _deterministic[0] and mode == "add":
-        mode = "add uncut"           # the same choice between the kernels, K whole
+    ordered = _deterministic[0]     # slices are summed in a fixed order: the single-CTA kernel can, CTA pairs cannot
     if T <= 64:
         if mode != "add" or tiles_w >= sms:
             return False, 1      # a wave of tiles or more streams weights on every SM as it is
@@ -388,6 +410,8 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
         best = (float("inf"), 1)
         for split in range(1, max(1, min(k_tiles // 4, _PLAN_DECODE_MAX_SPLIT)) + 1):
             waves = (tiles_w * split + sms - 1) // sms
+            if ordered and split > 1 and waves > 1:
+                break     # an ordered sum costs a tile a fence and a ticket (about 3 us): one tile per SM at most
             cost = waves * ((k_tiles + split - 1) // split) + _PLAN_DECODE_STEPS_PER_ADD * split * T * tiles_w
             if cost < best[0] - 1e-9:
                 best = (cost, split)
@@ -407,11 +431,11 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
         waves = (tiles + sms - 1) // sms
         cost = max(waves * (((k_tiles + split - 1) // split) * step + _PLAN_TILE_US), stream)
         if split > 1:
-            cost += _PLAN_US_PER_ADD * T * N * split
+            cost += _PLAN_US_PER_ADD * T * N * split + (_PLAN_ORDERED_TILE_US * waves if ordered else 0.0)
         best = min(best, (cost, False, split))
     if allow_pairs and _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS:
         clusters = ((T + 255) // 256) * (tiles_w if gated else (N + 255) // 256)
-        for split in (_PLAN_PAIR_SPLITS if mode == "add" else (1,)):
+        for split in (_PLAN_PAIR_SPLITS if mode == "add" and not ordered else (1,)):
             if split > 1 and split > k_tiles // 4:
                 break
             waves = (clusters * split + sms // 2 - 1) // (sms // 2)
@@ -478,9 +502,22 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
             _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
             int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
+    partials = tickets = None
+    if split_k > 1 and _deterministic[0]:
+        bn = 16 if T <= 16 else 32 if T <= 32 else 64 if T <= 64 else 128 if T <= 128 else 256
+        k_tiles = (K + 63) // 64
+        per = (k_tiles + split_k - 1) // split_k
+        slices = (k_tiles + per - 1) // per
+        out_tiles = ((N + 127) // 128) * ((T + bn - 1) // bn)
+        scratch = _ordered_buffers(x.device, out_tiles * slices * bn * 128) if out_tiles <= _ORDERED_TICKETS else None
+        if scratch is None:
+            split_k = 1          # too much scratch: K whole
+        else:
+            partials, tickets = scratch
     _check(_lib("gemm_bf16_tc", None, _GEMM_DEFINES).jb_gemm_bf16(
         _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
-        int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
+        int(split_k), _ptr(partials), ctypes.c_longlong(0 if partials is None else partials.numel()), _ptr(tickets),
+        0 if tickets is None else tickets.numel(), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
 
 
 def gemm_qkv_rope_supported(T: int, hd: int) -> bool:

@@ -116,10 +116,13 @@ def test_product_plan_picks_a_kernel_and_slices_that_the_kernels_take():
     assert ops.gemm_plan(2048, 4096, 14336, "add") == (True, 1)
     assert ops.gemm_plan(2048, 14336, 4096, "swiglu") == (True, 1)
     assert ops.gemm_plan(64, 14336, 4096, "swiglu") == (False, 1)
-    ops.set_deterministic(True)          # no K is cut: nothing meets by atomic adds
+    ops.set_deterministic(True)          # slices are summed in order: only the single-CTA kernel cuts K then
     try:
-        assert all(ops.gemm_plan(T, N, K, "add")[1] == 1
-                   for T in (1, 8, 64, 100, 256, 700, 2048) for N, K in ((4096, 4096), (4096, 14336), (6144, 4096)))
+        for T in (1, 8, 64, 100, 256, 700, 2048):
+            for N, K in ((4096, 4096), (4096, 14336), (6144, 4096)):
+                pair, split = ops.gemm_plan(T, N, K, "add")
+                assert not (pair and split > 1)
+        assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 4)      # one wave: a tile's ordered sum is not free
     finally:
         ops.set_deterministic(False)
     assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 13)

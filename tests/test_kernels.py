@@ -343,6 +343,33 @@ def test_gemm_bf16_store_and_add(ops, T, N, K):
     ops.check_kernel_status(torch.device(DEV))
 
 
+@pytest.mark.parametrize("T", [1, 5, 16, 33, 64, 100, 300])
+@pytest.mark.parametrize("N, K", [(200, 1024), (1000, 640), (384, 4096)])
+def test_gemm_bf16_slices_summed_in_order(ops, T, N, K):
+    """Deterministic mode: every slice of K leaves its tile in scratch and the slice that arrives last sums them
+    in slice order.  Right against the plain product, and the same bits when run again (atomic adds are not)."""
+    x, w = bf16_inputs(T, N, K, T + N + 3)
+    ref = x.double().cpu() @ w.double().cpu().T
+    w = ops.pack_weight(w)
+    base = torch.randn(T, N, device=DEV)
+    ops.set_deterministic(True)
+    try:
+        for split in (2, 3, 7, 1000):
+            got = []
+            for _ in range(3):
+                acc = base.clone()
+                ops.gemm_bf16(x, w, acc, mode="add", split_k=split, pair=False)
+                got.append(acc)
+            close(got[0], ref + base.double().cpu(), 2e-5)
+            assert torch.equal(got[0], got[1]) and torch.equal(got[0], got[2])
+        acc = base.clone()
+        ops.gemm_bf16(x, w, acc, mode="add")              # as the plan picks kernel and slices
+        close(acc, ref + base.double().cpu(), 2e-5)
+    finally:
+        ops.set_deterministic(False)
+    ops.check_kernel_status(torch.device(DEV))
+
+
 @pytest.mark.parametrize("T", [1, 17, 64, 200])
 @pytest.mark.parametrize("I, K", [(192, 64), (320, 96), (1000, 2048)])
 def test_gemm_bf16_swiglu(ops, T, I, K):

@@ -80,8 +80,8 @@ def test_long_prompt_runs_the_pair_products(big_model):
 
 
 def test_deterministic_mode_gives_the_same_bits_twice(big_model):
-    """With no product cut along K nothing is summed by atomic adds in an order of the day: two engines built
-    one after the other give bitwise equal logits for a prompt and for decoded tokens."""
+    """With the slices of a cut K summed in their fixed order nothing depends on the order of the day: two
+    engines built one after the other give bitwise equal logits for a prompt and for decoded tokens."""
     import janus_b200
     from janus_b200.engine import StepEntry
     from janus_b200.kernels import ops
@@ -89,7 +89,7 @@ def test_deterministic_mode_gives_the_same_bits_twice(big_model):
     assert ops.split_k_for(8, 4096, 4096) > 1
     ops.set_deterministic(True)
     try:
-        assert ops.split_k_for(8, 4096, 4096) == 1 and ops.split_k_for(300, 4096, 14336) == 1
+        assert ops.split_k_for(8, 4096, 4096) > 1            # K is still cut; the sums are ordered
         runs = []
         for _ in range(2):
             model = janus_b200.load(d, dtype="bfloat16", max_tokens=1024)
