@@ -49,7 +49,7 @@ constexpr int BK = 64;    // bf16 elements per k-tile = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;
 
-enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3 };
+enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3, ADD_ORDERED = 4 };   // 4: ADD_F32 with K cut, slices summed in order
 
 constexpr unsigned long long WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
@@ -322,7 +322,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       const int f = tc.m0 + quarter * 32 + lane;
       const bool f_ok = f < N_out;
       const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * C::ACC_COLS;
-      if (MODE == ADD_F32 && atomic_add && partials != nullptr) {
+      if constexpr (MODE == ADD_ORDERED) {   // a build of its own: the other epilogues stay as lean as they were
         // Slices of K summed in a fixed order (the same bits every run): every slice leaves its tile in
         // scratch, [output tile][slice][column][128 rows], and takes a ticket of the output tile; the slice
         // that arrives last adds all of them up in slice order and adds the sum to Y.  Nobody waits.
@@ -375,8 +375,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             }
           }
         }
-        continue;
-      }
+      } else {
 #pragma unroll 1
       for (int c0 = 0; c0 < BN; c0 += 16) {
         if (tc.t0 + c0 >= T) break;  // uniform
@@ -422,6 +421,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);
+      }
     }
     tc_fence_before();
   }
@@ -515,7 +515,11 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_o
   const int n_tok_tiles = (T + BN - 1) / BN, n_w_tiles = (N_out + BM - 1) / BM;
   const long long n_tiles = (long long)n_tok_tiles * n_w_tiles * splits;
   JB_REFUSE(n_tiles > 0x7fffffffLL, "gemm_bf16: too many tiles (%lld)", n_tiles);
-  const bool in_order = splits > 1 && ordered.partials != nullptr;
+  if (MODE == ADD_ORDERED && splits == 1) {   // K turned out too short to cut: the plain adding product
+    if constexpr (MODE == ADD_ORDERED)
+      return launch<BN, ADD_F32, STAGES>(mw, mx, Y, T, N_out, ldy, k_tiles, 1, up_tile_offset, ordered, status, stream);
+  }
+  const bool in_order = MODE == ADD_ORDERED;
   if (in_order) {
     const long long out_tiles = (long long)n_tok_tiles * n_w_tiles;
     JB_REFUSE(ordered.tickets == nullptr || out_tiles > ordered.n_tickets ||
@@ -586,7 +590,10 @@ JB_EXPORT int jb_gemm_bf16(const void* X, const void* W, long long w_tiles, int 
   switch (mode) {
     case STORE_BF16: return dispatch<STORE_BF16>(mw, X, Y, T, N_out, K, ldy, 1, 0, none, status, stream);
     case STORE_F32: return dispatch<STORE_F32>(mw, X, Y, T, N_out, K, ldy, 1, 0, none, status, stream);
-    case ADD_F32: return dispatch<ADD_F32>(mw, X, Y, T, N_out, K, ldy, split_k, 0, ordered, status, stream);
+    case ADD_F32:
+      if (split_k > 1 && partials != nullptr)
+        return dispatch<ADD_ORDERED>(mw, X, Y, T, N_out, K, ldy, split_k, 0, ordered, status, stream);
+      return dispatch<ADD_F32>(mw, X, Y, T, N_out, K, ldy, split_k, 0, none, status, stream);
     default: return dispatch<SWIGLU>(mw, X, Y, T, N_out, K, ldy, 1, up_tile_offset, none, status, stream);
   }
 }
