@@ -161,3 +161,49 @@ def test_sampler_config_names_and_checks():
                 dict(repetition_penalty=0.0), dict(beam_width=4), dict(max_tokens=-1)):
         with pytest.raises(ValueError):
             SamplerConfig(**bad).validate()
+
+
+def _expected(script, prompt_len, max_new, stop, max_seq):
+    """What a request must produce: its scripted tokens up to a stop token (not part of the output), its
+    budget, or the longest sequence, whichever comes first."""
+    out = []
+    for tok in script:
+        if tok in stop:
+            return out, "stop"
+        out.append(tok)
+        if len(out) >= max_new or prompt_len + len(out) > max_seq:
+            return out, "length"
+    raise AssertionError("script too short")
+
+
+def test_any_mix_of_requests_is_served_whole_and_every_slot_comes_back():
+    """Property (hypothesis): whatever the prompts, budgets, stop tokens, batch size, slots and cache capacity,
+    both loops give every request exactly its scripted tokens and reason, never hold more sequences than the
+    batch size and the slots allow, never more tokens than the cache has, and give every slot back once."""
+    from hypothesis import given, settings, strategies as st
+
+    @settings(max_examples=150, deadline=None)
+    @given(st.data())
+    def check(data):
+        n = data.draw(st.integers(1, 9))
+        max_new = data.draw(st.integers(1, 12))
+        max_seq = data.draw(st.integers(16, 40))
+        prompts = [[7] * data.draw(st.integers(1, 15)) for _ in range(n)]
+        script = {r: [data.draw(st.sampled_from([1, 2, 3, 4, 5, 99])) for _ in range(max_new + 1)] for r in range(n)}
+        slots = data.draw(st.integers(1, 5))
+        batch = data.draw(st.integers(1, 6))
+        page = 8
+        biggest = max(tokens_held(len(p), max_new, page) for p in prompts)
+        cap = data.draw(st.integers(biggest, 4 * biggest))
+        want = [_expected(script[r], len(prompts[r]), max_new, {99}, max_seq) for r in range(n)]
+        for backend_type in (ScriptedBackend, RunAheadBackend):
+            b = backend_type(script, slots)
+            toks, reasons, stats = run_generation(b, prompts, max_new, [99], batch, cap, max_seq, slots, page, None)
+            assert toks == [w[0] for w in want] and reasons == [w[1] for w in want]
+            assert not b.held and sorted(b.free) == list(range(slots))
+            assert b.max_live <= min(batch, slots)
+            for kind, reqs, _ in b.log:
+                if kind == "prefill":          # what a batch may come to hold fits the cache
+                    assert sum(tokens_held(len(prompts[r]), max_new, page) for r in reqs) <= cap
+            assert stats.requests == n and stats.prefill_tokens == sum(len(p) for p in prompts)
+    check()
