@@ -149,3 +149,27 @@ def test_a_context_of_thousands_of_keys(long_model, dtype):
     assert rel_err(np.concatenate(rows_a), ref[LONG_PROMPT:LONG_PROMPT + LONG_DECODED]) < tol
     assert rel_err(np.concatenate(rows_b), ref[short:short + LONG_DECODED]) < tol
     model.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_batch_of_a_hundred_sequences(tmp_path, dtype):
+    """More sequences than any token tile of the decode products holds (64): a hundred prompts of 3 to 20
+    tokens in one step, then five steps of one token each, every row against the plain implementation."""
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    from helpers import TINY_B
+    d = make_model_dir(TINY_B, str(tmp_path / "m"), seed=3, dtype=dtype)
+    cfg, w = P.read_model_dir(d)
+    B = 100
+    lens = [3 + (7 * i) % 18 for i in range(B)]
+    ids = [random_tokens(n + 5, TINY_B["vocab_size"], 11 + i) for i, n in enumerate(lens)]
+    ref = [P.forward(cfg, w, x).numpy() for x in ids]
+    model = janus_b200.load(d, dtype=dtype, max_tokens=B * 64, max_slots=B)
+    slots = [model.alloc_slot() for _ in range(B)]
+    tol = tol_for(dtype)
+    out = model.step([StepEntry(s, x[:n], [n - 1]) for s, x, n in zip(slots, ids, lens)]).cpu().numpy()
+    assert rel_err(out, np.stack([r[n - 1] for r, n in zip(ref, lens)])) < tol
+    for j in range(5):
+        got = model.step([StepEntry(s, [x[n + j]], [0]) for s, x, n in zip(slots, ids, lens)]).cpu().numpy()
+        assert rel_err(got, np.stack([r[n + j] for r, n in zip(ref, lens)])) < tol
+    model.check()
