@@ -51,6 +51,26 @@ __device__ __forceinline__ void cp_async16(void* dst, const void* src, bool vali
   const int n = valid ? 16 : 0;  // src-size 0 fills the 16 bytes with zeros
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
 }
+#ifndef JB_KV_EVICT_FIRST
+#define JB_KV_EVICT_FIRST 1   // a decode step's K/V pages (read once a step) are the first to leave L2: +1.2 % decode
+#endif
+// 16 bytes of a cached page into shared memory, optionally with an evict-first L2 policy.
+__device__ __forceinline__ void cp_async16_kv(void* dst, const void* src, uint64_t policy) {
+#if JB_KV_EVICT_FIRST
+  asm volatile("cp.async.cg.shared.global.L2::cache_hint [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "l"(policy)
+               : "memory");
+#else
+  (void)policy;
+  cp_async16(dst, src, true);
+#endif
+}
+__device__ __forceinline__ uint64_t kv_policy() {
+  uint64_t p = 0;
+#if JB_KV_EVICT_FIRST
+  asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+#endif
+  return p;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
@@ -344,14 +364,15 @@ __global__ void __launch_bounds__(THREADS) decode_kernel(
   // Every warp loads, waits for and computes ITS OWN 16 keys of each page, so the ring needs no barrier of
   // the whole CTA: a warp asks for its rows of the page after next as soon as it is done with its rows of
   // this one, whatever the other warps are doing.
+  const uint64_t kv_pol = kv_policy();
   auto issue = [&](int kb, int stage) {
     const size_t page = (size_t)pages[kb];
     const size_t off = ((page * nkv + kvh) * PAGE + warp * 16) * HD;
     bf16* k_rows = kv_s + (size_t)stage * 2 * KV_TILE + warp * 16 * LD;
     for (int ch = lane; ch < 16 * CHUNKS; ch += 32) {
       const int row = ch / CHUNKS, col = ch % CHUNKS;
-      cp_async16(k_rows + row * LD + col * 8, k_cache + off + (size_t)row * HD + col * 8, true);
-      cp_async16(k_rows + KV_TILE + row * LD + col * 8, v_cache + off + (size_t)row * HD + col * 8, true);
+      cp_async16_kv(k_rows + row * LD + col * 8, k_cache + off + (size_t)row * HD + col * 8, kv_pol);
+      cp_async16_kv(k_rows + KV_TILE + row * LD + col * 8, v_cache + off + (size_t)row * HD + col * 8, kv_pol);
     }
   };
   // ring of DECODE_STAGES pages: DECODE_STAGES - 1 loads are in flight while one page is computed

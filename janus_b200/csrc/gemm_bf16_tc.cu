@@ -104,6 +104,32 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
       : "memory");
 }
 
+#ifndef JB_W_EVICT_FIRST
+#define JB_W_EVICT_FIRST 1   // weight tiles that are read once (one token tile) are the first to leave L2: +1.3 % decode
+#endif
+// A weight tile: as tma_load_2d, optionally marked as the first to leave L2.
+__device__ __forceinline__ void tma_load_w(uint32_t dst, const CUtensorMap* map, uint32_t bar, int y, uint64_t policy) {
+#if JB_W_EVICT_FIRST
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%3, %4}], [%2], %5;"
+      ::"r"(dst), "l"(map), "r"(bar), "r"(0), "r"(y), "l"(policy)
+      : "memory");
+#else
+  (void)policy;
+  tma_load_2d(dst, map, bar, 0, y);
+#endif
+}
+__device__ __forceinline__ uint64_t weight_policy(bool read_once) {
+  uint64_t p = 0;
+#if JB_W_EVICT_FIRST
+  if (read_once)
+    asm volatile("createpolicy.fractional.L2::evict_first.b64 %0, 1.0;" : "=l"(p));
+  else
+    asm volatile("createpolicy.fractional.L2::evict_normal.b64 %0, 1.0;" : "=l"(p));
+#endif
+  return p;
+}
+
 __device__ __forceinline__ void tmem_alloc(uint32_t dst_smem, uint32_t cols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(cols) : "memory");
 }
@@ -232,6 +258,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
       int it = 0;  // k-tiles loaded so far, over all of this CTA's tiles
       bool ok = true;
       bool waited = false;
+      const uint64_t w_policy = weight_policy(n_tok_tiles == 1);   // several token tiles read a weight tile again
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
         int first = 0;
@@ -244,8 +271,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
             mbar_expect_tx(bar, C::STAGE_BYTES);
             // weight tile (row tile, k tile) = rows [.. * 128, +128) of the packed matrix: one contiguous 16 KB
             const int wy = ((tc.m0 / BM) * k_tiles + tc.kt_begin + i) * BM;
-            tma_load_2d(stage, &map_w, bar, 0, wy);
-            if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, 0, wy + up_tile_offset * k_tiles * BM);
+            tma_load_w(stage, &map_w, bar, wy, w_policy);
+            if (MODE == SWIGLU) tma_load_w(stage + C::A_BYTES, &map_w, bar, wy + up_tile_offset * k_tiles * BM, w_policy);
           }
           jb::pdl_wait();
           waited = true;
@@ -262,8 +289,8 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           mbar_expect_tx(bar, C::STAGE_BYTES);
           const int kx = (tc.kt_begin + i) * BK;
           const int wy = ((tc.m0 / BM) * k_tiles + tc.kt_begin + i) * BM;
-          tma_load_2d(stage, &map_w, bar, 0, wy);
-          if (MODE == SWIGLU) tma_load_2d(stage + C::A_BYTES, &map_w, bar, 0, wy + up_tile_offset * k_tiles * BM);
+          tma_load_w(stage, &map_w, bar, wy, w_policy);
+          if (MODE == SWIGLU) tma_load_w(stage + C::A_BYTES, &map_w, bar, wy + up_tile_offset * k_tiles * BM, w_policy);
           tma_load_2d(stage + C::A_TILES * C::A_BYTES, &map_x, bar, kx, tc.t0);
         }
       }

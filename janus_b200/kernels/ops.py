@@ -456,6 +456,7 @@ def _defines_from_env(name: str) -> dict:
 _GEMM_DEFINES = _defines_from_env("JANUS_GEMM_DEFINES") or None
 _PAIR_DEFINES = _defines_from_env("JANUS_GEMM_PAIR_DEFINES") or None
 _ATTN_TC_DEFINES = _defines_from_env("JANUS_ATTN_TC_DEFINES")
+_ATTN_DEFINES = _defines_from_env("JANUS_ATTN_DEFINES")
 _ATTN_TC = os.environ.get("JANUS_ATTN_TC", "1") != "0"     # 0: prompts attend on the mma.sync kernel
 
 
@@ -583,7 +584,7 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_
 def _attention_lib(hd: int):
     if hd % 8 or not 8 <= hd <= 256:
         raise KernelError(f"attention_bf16: head_dim {hd} is not a multiple of 8 in [8, 256]")
-    return _lib("attention_bf16", int(hd), lambda h: {"JB_HEAD_DIM": h})
+    return _lib("attention_bf16", int(hd), lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_DEFINES))
 
 
 def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
