@@ -7,13 +7,13 @@ the model class by config.json's `architectures`.
 """
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence, Tuple
+from typing import Callable, List, Optional, Sequence
 
 import torch
 
 from .cache import PAGE_SIZE
 from .config import read_config_json, resolve_architecture
-from .engine.generate import GenerationStats, run_generation
+from .engine.generate import run_generation
 from .engine.step import Engine, EngineOptions, StepEntry
 from .sampling import DeviceSampler, SamplerConfig
 from .weights import FolderCheckpoint, RandomCheckpoint, parse_dtype

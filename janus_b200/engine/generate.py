@@ -13,7 +13,7 @@ reasons are "stop" and "length" (generation.rs:421-427).
 from __future__ import annotations
 
 import time
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Callable, List, Optional, Protocol, Sequence, Tuple
 
 

@@ -7,12 +7,12 @@ computes logits only for the rows that are wanted.
 """
 from __future__ import annotations
 
-from typing import Dict, List, Optional, Sequence
+from typing import Dict, List, Optional
 
 import torch
 
 from ..kernels import ops
-from ..parts.base import CacheSpec, KVSpec, LayerSpec, ModelSpec, PartSpec, make_part
+from ..parts.base import CacheSpec, LayerSpec, ModelSpec, make_part
 from ..parts.linear import Linear
 from ..weights.loader import TensorSpec, load_named
 

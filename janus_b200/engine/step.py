@@ -11,7 +11,7 @@ crates/janus-engine/src/model/transformer/forward.rs:25,139-141.)
 from __future__ import annotations
 
 import gc
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Dict, List, Optional, Sequence, Tuple
 
 import numpy as np

@@ -224,7 +224,6 @@ def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
 
 
 # -- bfloat16 tensor-core matrix product --------------------------------------------
-_GEMM_MODES = {"store": None, "add": 2, "swiglu": 3}
 _status = {}
 SM_COUNT_TARGET = 296      # CTAs wanted in flight for a weight-streaming product (two per SM)
 

@@ -8,7 +8,7 @@ and SiLU-gate (for a stacked gate/up weight).
 """
 from __future__ import annotations
 
-from typing import Optional, Sequence
+from typing import Sequence
 
 import torch
 

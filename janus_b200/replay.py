@@ -7,7 +7,6 @@ import os
 import sys
 from typing import Dict
 
-import numpy as np
 
 
 def main(argv=None) -> int:
