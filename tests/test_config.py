@@ -126,3 +126,18 @@ def test_product_plan_picks_a_kernel_and_slices_that_the_kernels_take():
     finally:
         ops.set_deterministic(False)
     assert ops.gemm_plan(8, 4096, 4096, "add") == (False, 13)
+
+
+def test_key_splits_of_decode_attention_stay_within_the_pages():
+    """The split count of decode attention: at least one, never more splits than pages of the longest
+    sequence allow, one split when the batch alone fills the SMs, and the measured picks at 8 kv heads."""
+    from janus_b200.kernels import ops
+    for n_seqs in (1, 2, 3, 8, 16, 37, 64, 100, 500):
+        for nkv in (1, 2, 8, 40):
+            for length in (1, 63, 64, 65, 2080, 4096, 32768, 131072):
+                s = ops.decode_splits_for(n_seqs, nkv, length, 64)
+                pages = (length + 63) // 64
+                assert 1 <= s <= max(1, pages), (n_seqs, nkv, length, s)
+    assert ops.decode_splits_for(8, 8, 4096, 64) == 4
+    assert ops.decode_splits_for(64, 8, 4096, 64) == 1
+    assert ops.decode_splits_for(1, 8, 4096, 64) == 16
