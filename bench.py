@@ -9,9 +9,18 @@ batch 1 and 64.  A "step" is one decode step.
 Prints one JSON line.  `value` is timed on the device with CUDA events around K
 steps of the engine's step function (index buffer copied from pinned host
 memory each step, kernels replayed from a CUDA graph); `e2e` is the same metric
-through `Model.generate` (host token ids in, sampled ids out each step).
-Each step reads every weight once (15 GB, far larger than the 126 MB L2), so no
-L2 flush is needed between steps.
+through `Model.generate` (host token ids in, sampled ids out each step).  Where
+K steps take less than half a second the block of K steps is timed again until
+half a second is covered, and the median block is reported (`config.timed_blocks`).
+Both numbers follow one rule: the device idles 0.5 s after the cache is filled
+(the prompt steps run at the board's power cap), then W untimed steps, then the
+timed blocks.  Each step reads every weight once (15 GB, far larger than the
+126 MB L2), so no L2 flush is needed between steps.  Before anything is timed,
+the bfloat16 model's logits are compared with those of the true 32-bit engine on
+the same weights (`checked`).
+
+Other modes (one JSON line per item, none of them the headline): --kernels,
+--prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline.
 """
 import argparse
 import json
@@ -36,8 +45,11 @@ CONFIG_8B = dict(
 FILL = 2048          # tokens each sequence holds before decoding is timed
 PREFILL_TOKENS = 2048
 SETTLE_S = 0.5       # idle time after the cache is filled, before decode steps are warmed up and timed
-E2E_MIN_WARMUP = 40  # decode steps of the end-to-end generation before its timed window
-FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0)
+MIN_TIMED_S = 0.5    # a timed block of K steps is repeated until this much time is covered
+MAX_BLOCKS = 16
+CHECK_PROMPT = 64    # tokens of the prompt whose logits are compared with the 32-bit engine before timing
+BF16_LAYER_ERR = 1.1e-2   # rms error of the logits a bfloat16 layer may add, as a share of their rms (x sqrt(layers))
+FALLBACK_PEAKS = dict(hbm_gbs=6650.0, bf16_tflops=1590.0, bf16_tflops_sustained=1400.0)
 
 
 def peaks():
@@ -46,7 +58,9 @@ def peaks():
         try:
             with open(path) as f:
                 d = json.load(f)
-            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]), source="measured")
+            return dict(hbm_gbs=float(d["hbm_gbs"]), bf16_tflops=float(d["bf16_tflops"]),
+                        bf16_tflops_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                        source="measured")
         except (OSError, ValueError, KeyError):
             pass
     return dict(FALLBACK_PEAKS, source="fallback")
@@ -108,6 +122,34 @@ def prefill_flops(cfg, layers, T):
     return linear + attention
 
 
+def rms_err(got, ref):
+    import numpy as np
+    got, ref = got.astype(np.float64), ref.astype(np.float64)
+    if not np.isfinite(got).all():
+        return float("inf")
+    return float(np.sqrt(((got - ref) ** 2).mean()) / np.sqrt((ref ** 2).mean()))
+
+
+def check_against_float32(cfg, layers, prompt):
+    """Logits of the bfloat16 model at four rows of a 64-token prompt against the true 32-bit engine on the
+    same weights (the benchmark's: seed 2, stored as bfloat16).  Returns (ok, rms error, bound)."""
+    import torch
+
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    rows = [0, CHECK_PROMPT // 3, 2 * CHECK_PROMPT // 3, CHECK_PROMPT - 1]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        model = janus_b200.load_random(cfg, seed=2, dtype=dtype, max_tokens=128, max_slots=1, norm_std=0.0,
+                                       stored_dtype="bfloat16")
+        outs[dtype] = model.step([StepEntry(model.alloc_slot(), prompt[:CHECK_PROMPT], rows)]).cpu().numpy()
+        model.check()
+        del model
+        torch.cuda.empty_cache()
+    err, bound = rms_err(outs["bfloat16"], outs["float32"]), BF16_LAYER_ERR * layers ** 0.5
+    return err < bound, err, bound
+
+
 def run_ours(args):
     import torch
 
@@ -115,21 +157,34 @@ def run_ours(args):
     from janus_b200.engine import StepEntry
     from janus_b200.kernels import ops
 
+    if args.deterministic:
+        ops.set_deterministic(True)
     layers = args.layers or CONFIG_8B["num_hidden_layers"]
     cfg = dict(CONFIG_8B, num_hidden_layers=layers)
     K, W = args.steps, args.warmup
-    batches = [1, 8, 64] if not args.quick else [8]
+    batches = [1, 8, 64] if not args.quick else [args.batch]
     max_b = max(batches)
-    per_seq = FILL + 2 * (max(W, E2E_MIN_WARMUP) + K) + 128
-    model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max_b * (per_seq + 64),
-                                   max_slots=max_b, norm_std=0.0)
-    eng = model.engine
-    dev = model.device
     g = torch.Generator().manual_seed(0)
     V = cfg["vocab_size"]
 
     def tokens(n):
         return torch.randint(0, V, (n,), generator=g).tolist()
+
+    prompt = tokens(PREFILL_TOKENS)
+    checked, check_err, check_bound = (None, None, None)
+    if not args.no_check:
+        checked, check_err, check_bound = check_against_float32(cfg, layers, prompt)
+        if not checked:
+            print(f"bench: the bfloat16 logits differ from the 32-bit engine's by {check_err:.4f} rms "
+                  f"(bound {check_bound:.4f}); nothing is timed", file=sys.stderr)
+            return 1
+
+    max_steps = W + MAX_BLOCKS * K + 8
+    per_seq = FILL + 2 * max_steps + 128
+    model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max_b * (per_seq + 64),
+                                   max_slots=max_b, norm_std=0.0)
+    eng = model.engine
+    dev = model.device
 
     def timed(fn, reps):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -142,8 +197,6 @@ def run_ours(args):
         return start.elapsed_time(end) / reps
 
     # ---- prefill of 2,048 tokens ------------------------------------------------
-    prompt = tokens(PREFILL_TOKENS)
-
     def one_prefill():
         s = eng.alloc_slot()
         eng.step([StepEntry(s, prompt, (PREFILL_TOKENS - 1,))])
@@ -153,8 +206,10 @@ def run_ours(args):
         one_prefill()
     prefill_ms = timed(one_prefill, 5)
     pk = peaks()
+    flops = prefill_flops(cfg, layers, PREFILL_TOKENS)
     prefill = dict(value=round(PREFILL_TOKENS / prefill_ms * 1e3, 1), tokens=PREFILL_TOKENS, ms=round(prefill_ms, 3),
-                   frac=round(prefill_flops(cfg, layers, PREFILL_TOKENS) / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4))
+                   frac=round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4),
+                   frac_of_sustained=round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4))
 
     # ---- decode at each batch size ----------------------------------------------
     results, launches = {}, {}
@@ -163,8 +218,8 @@ def run_ours(args):
         slots = [eng.alloc_slot() for _ in range(B)]
         for i in range(0, B, 8):                                   # fill the sequences, 8 prompts a step
             eng.step([StepEntry(s, tokens(FILL), ()) for s in slots[i:i + 8]])
-        feed = [[int(t) for t in tokens(B)] for _ in range(W + K)]
-        it = iter(feed)
+        pool = [[int(t) for t in tokens(B)] for _ in range(64)]
+        turn = [0]
         # The fill ran at the board's power cap; the SM clocks take some 150 ms to come back after it
         # (measured: the first ~30 decode steps after a 16k-token prefill take 4.4 - 5.1 ms instead of 3.6).
         # Decoding is timed in its steady state, so the device idles briefly first.
@@ -172,48 +227,58 @@ def run_ours(args):
         time.sleep(SETTLE_S)
 
         def one_step():
-            row = next(it)
+            row = pool[turn[0] % len(pool)]
+            turn[0] += 1
             eng.step([StepEntry(s, (t,), (0,)) for s, t in zip(slots, row)], borrow=True)
 
-        before = ops.launch_count()
         for _ in range(W):
             one_step()
         per_step_launches = eng.last_graph_launches
         sampler = ClockSampler() if B == args.batch else None
         if sampler:
             sampler.start()
-        ms = timed(one_step, K)
+        blocks, covered = [], 0.0
+        while len(blocks) < MAX_BLOCKS and (not blocks or covered < MIN_TIMED_S):
+            blocks.append(timed(one_step, K))
+            covered += blocks[-1] * K * 1e-3
         if sampler:
             clocks = sampler.stop()
         ops.check_kernel_status(dev)
-        results[B] = dict(ms=ms, tok_s=B / ms * 1e3)
+        order = sorted(range(len(blocks)), key=lambda i: blocks[i])
+        mid = order[(len(blocks) - 1) // 2]                         # the median block (the lower of two)
+        ms = blocks[mid]
+        results[B] = dict(ms=ms, tok_s=B / ms * 1e3, blocks=len(blocks), ctx=FILL + W + mid * K + K // 2,
+                          spread=round((max(blocks) - min(blocks)) / ms, 4))
         launches[B] = per_step_launches * K
         for s in slots:
             eng.free_slot(s)
 
     # ---- end to end through the public entry point ----------------------------------
     B = args.batch
+    n_blocks = results[B]["blocks"]
     prompts = [tokens(FILL) for _ in range(B)]
     model.generate(prompts, max_tokens=W + 2, ignore_eos=True)                       # warm-up (graphs are captured)
-    # One generation of e2e_warm + K + 1 tokens; the host clock runs from the arrival of decode step
-    # e2e_warm's tokens to that of step e2e_warm + K's: exactly K steps, each with its index buffer copied
-    # from pinned host memory and its sampled tokens read back.  The steps before are the ones that run at
-    # reduced clocks after the prompts' prefill (see above).
-    e2e_warm = max(W, E2E_MIN_WARMUP)
+    # One generation of W + n_blocks * K + 1 tokens under the same rule as above: when the prefill's tokens
+    # arrive the host idles 0.5 s, then W untimed decode steps, then blocks of K steps on the host clock,
+    # from the arrival of one step's tokens to the arrival of the tokens K steps later: each step with its
+    # index buffer copied from pinned host memory and its sampled tokens read back.  The median block counts.
     arrivals = []
 
     def on_token(request, token):
         if request == 0:
+            if not arrivals:
+                torch.cuda.synchronize(dev)
+                time.sleep(SETTLE_S)
             arrivals.append(time.perf_counter())
         return True
 
-    model.generate(prompts, max_tokens=e2e_warm + K + 1, ignore_eos=True, callback=on_token)
+    model.generate(prompts, max_tokens=W + n_blocks * K + 1, ignore_eos=True, callback=on_token)
     # arrivals[0] is the prefill's token; arrivals[i] that of decode step i
-    e2e_tok_s = B * K / (arrivals[e2e_warm + K] - arrivals[e2e_warm])
+    e2e_blocks = sorted(B * K / (arrivals[W + (i + 1) * K] - arrivals[W + i * K]) for i in range(n_blocks))
+    e2e_tok_s = e2e_blocks[(n_blocks - 1) // 2]
 
     head = results[args.batch]
-    ctx = FILL + W + K // 2
-    nbytes = decode_bytes(cfg, layers, args.batch, ctx)
+    nbytes = decode_bytes(cfg, layers, args.batch, head["ctx"])
     achieved = nbytes / (head["ms"] * 1e-3) / 1e9
     out = {
         "metric": "decode tok/s @ batch 8 (Llama-3-8B shape, bf16, ctx 4096, sequences at 2048)",
@@ -226,19 +291,26 @@ def run_ours(args):
             "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
             "global_batch": args.batch, "seq_len": 4096, "filled_to": FILL, "prefill_tokens": PREFILL_TOKENS,
             "parallelism": "single GPU", "l2": "inputs larger than L2 (15 GB of weights per step)",
-            "peaks": pk["source"],
+            "peaks": pk["source"], "timed_blocks": head["blocks"], "block_spread": head["spread"],
+            "settle_s": SETTLE_S, "deterministic": bool(args.deterministic),
         },
         "e2e": {"value": round(e2e_tok_s, 1), "unit": "tokens/s",
                 "h2d_bytes_per_step": eng.last_step_h2d_bytes + 3 * 4 * B, "d2h_bytes_per_step": 4 * B,
-                "steps": K, "warmup": e2e_warm},
+                "steps": K, "warmup": W, "blocks": n_blocks},
         "gpu_launches": launches[args.batch],
         "prefill": prefill,
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
                      "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": {f"decode_b{b}": round(r["tok_s"], 1) for b, r in results.items() if b != args.batch},
+        "point_fracs": {f"decode_b{b}": round(decode_bytes(cfg, layers, b, r["ctx"]) / (r["ms"] * 1e-3) / 1e9
+                                              / pk["hbm_gbs"], 4) for b, r in results.items() if b != args.batch},
+        "checked": checked,
+        "check": None if checked is None else {"rms_err_vs_float32": round(check_err, 5), "bound": round(check_bound, 5),
+                                               "rows": 4, "prompt_tokens": CHECK_PROMPT},
         "clocks": clocks,
     }
     print(json.dumps(out))
+    return 0
 
 
 # BASELINE.json configs[3] and configs[4]: whole workloads through the public entry point
@@ -282,12 +354,26 @@ def run_workload(name):
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
     new_tokens = sum(len(o) for o in out)
+    # what the decode steps had to read: every weight once per step, and the cached keys and values of the
+    # sequences that were live at the step (request r's j-th decode step reads prompt + j tokens)
+    cfg, L = w["config"], w["config"]["num_hidden_layers"]
+    n = model_numbers(cfg, L)
+    weight_bytes = 2 * (L * n["layer_params"] + n["head_params"]) + n["norm_bytes"]
+    kv_tokens = sum(sum(range(ln + 1, ln + len(o))) for ln, o in zip(lens, out))
+    step_bytes = stats.decode_steps * weight_bytes + kv_tokens * n["kv_bytes_per_token"]
+    pk = peaks()
+    achieved = step_bytes / (stats.decode_ms * 1e-3) / 1e9 if stats.decode_ms > 0 else 0.0
     print(json.dumps({
         "impl": "janus_b200", "workload": name, "metric": "generated tokens/s, whole workload through Model.generate",
         "value": round(new_tokens / wall, 1), "unit": "tokens/s", "wall_s": round(wall, 3),
         "prompt_tokens": sum(lens), "new_tokens": new_tokens, "decode_steps": stats.decode_steps,
         "prefill_tokens_per_s": round(stats.prefill_tokens_per_s, 1),
         "decode_tokens_per_s": round(stats.decode_tokens_per_s, 1), "dtype": "bf16",
+        "decode_ms_per_step": round(stats.decode_ms / max(1, stats.decode_steps), 4),
+        "graph_captures": stats.graph_captures,
+        "roofline": {"bound": "hbm", "what": "decode steps: weights once per step + live sequences' cache",
+                     "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                     "frac": round(achieved / pk["hbm_gbs"], 4), "peaks": pk["source"]},
         "data": f"synthetic token ids, random-init weights (seed {w['seed']})",
         "config": {"batch": w["batch"], "prompt_lengths": f"U[{lo},{hi}]", "context": w["context"],
                    "layers": w["config"]["num_hidden_layers"], "hidden": w["config"]["hidden_size"],
@@ -344,11 +430,12 @@ def layer_weight_elems(cfg):
     return qkv + o + 3 * cfg["intermediate_size"] * cfg["hidden_size"]
 
 
-def run_kernels():
+def run_kernels(contexts=None):
     """The step's hot kernels alone at the 8B layer shapes, for the roofline figures under profiles/:
     each is captured 24 times into one CUDA graph (as the engine runs them: back to back, programmatic
     dependent launch) over several copies of its weights or cache, so that every launch reads from DRAM,
-    and timed with CUDA events around 5 replays.  One line per kernel; nothing here is the headline."""
+    and timed with CUDA events around 5 replays.  One line per kernel; nothing here is the headline.
+    With `contexts` (key counts), decode attention alone at those contexts, for 1 and 8 sequences."""
     import math
 
     import torch
@@ -413,14 +500,15 @@ def run_kernels():
                           "weights_GBps": round(rows * K * 2 / us / 1e3, 1),
                           "TFLOPs": round(2 * T * rows * K / us / 1e6, 1)}), flush=True)
 
-    for T in (8, 64, 2048):
-        product("qkv", T, (NH + 2 * NKV) * HD, H, "store")
-        product("o (add)", T, H, NH * HD, "add")
-        product("gate_up (SiLU gate)", T, I, H, "swiglu")
-        product("down (add)", T, H, I, "add")
-    product("lm_head", 8, V, H, "store", copies=3)
+    if not contexts:
+        for T in (8, 64, 2048):
+            product("qkv", T, (NH + 2 * NKV) * HD, H, "store")
+            product("o (add)", T, H, NH * HD, "add")
+            product("gate_up (SiLU gate)", T, I, H, "swiglu")
+            product("down (add)", T, H, I, "add")
+        product("lm_head", 8, V, H, "store", copies=3)
 
-    for B, ctx in ((1, 2080), (8, 2080), (64, 2080)):
+    for B, ctx in ([(b, c) for c in contexts for b in (1, 8)] if contexts else ((1, 2080), (8, 2080), (64, 2080))):
         pages = (ctx + 63) // 64
         n_pages = B * pages
         copies = max(1, min(8, int(3e9 // (n_pages * NKV * 64 * HD * 4))))
@@ -444,7 +532,7 @@ def run_kernels():
                           "splits": ops.decode_splits_for(B, NKV, cap * 64, 64), "us": round(us, 1),
                           "kv_GBps": round(B * ctx * NKV * HD * 4 / us / 1e3, 1)}), flush=True)
 
-    for B, L in ((1, 2048), (1, 8192)):
+    for B, L in (() if contexts else ((1, 2048), (1, 8192))):
         pages = (L + 63) // 64
         kc = torch.randn(B * pages, NKV, 64, HD, device=dev).to(torch.bfloat16)
         vc = torch.randn_like(kc)
@@ -460,6 +548,109 @@ def run_kernels():
     ops.check_kernel_status(torch.device(dev))
 
 
+def run_plan_check():
+    """The pick of `ops.gemm_plan` against every alternative it ranks (single-CTA kernel and CTA pairs, K in
+    1 to 8 slices) for adding products of three layer sizes at decode and prompt token counts: each variant
+    is captured 12 times into a CUDA graph over 4 copies of the weight and timed.  One line per shape with the
+    pick, the best alternative and how far the pick is off."""
+    import torch
+
+    from janus_b200.kernels import ops
+    dev = "cuda:0"
+
+    def timed(fn, reps=12):
+        for _ in range(2):
+            fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            for _ in range(reps):
+                fn()
+        g.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(3):
+            g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        return a.elapsed_time(b) / (3 * reps) * 1e3
+
+    shapes = [("1B o", 2048, 2048), ("1B down", 2048, 8192), ("8B o", 4096, 4096), ("8B down", 4096, 14336),
+              ("13B o", 5120, 5120), ("13B down", 5120, 13824)]
+    for name, N, K in shapes:
+        ws = [ops.pack_weight((torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)) for _ in range(4)]
+        for T in (8, 64, 256, 1024):
+            x = torch.randn(T, K, device=dev).to(torch.bfloat16)
+            y = torch.zeros(T, N, device=dev, dtype=torch.float32)
+            pick = ops.gemm_plan(T, N, K, "add")
+            times = {}
+            k_tiles = (K + 63) // 64
+            for pair in ((False, True) if T >= ops.GEMM_PAIR_MIN_TOKENS else (False,)):
+                for split in sorted({1, 2, 3, 4, 6, 8, pick[1]}):
+                    if split > 1 and split > max(1, k_tiles // 4):
+                        continue
+                    if pair and split > 6:
+                        continue
+                    turn = [0]
+
+                    def fn():
+                        turn[0] += 1
+                        ops.gemm_bf16(x, ws[turn[0] % 4], y, mode="add", split_k=split, pair=pair)
+
+                    times[(pair, split)] = timed(fn)
+            best = min(times, key=times.get)
+            print(json.dumps({"product": name, "tokens": T, "pick": {"pairs": pick[0], "splits": pick[1]},
+                              "pick_us": round(times[pick], 1), "best": {"pairs": best[0], "splits": best[1]},
+                              "best_us": round(times[best], 1),
+                              "pick_off_by": round(times[pick] / times[best] - 1.0, 4)}), flush=True)
+    ops.check_kernel_status(torch.device(dev))
+
+
+def run_cpu_baseline():
+    """The plain implementation (tests/plain_llama.py: whole sequences, no cache, float32 on the host cores)
+    timed on the workloads of the two tiny configurations and on one 8B-sized layer.  The reference cannot be
+    built or run here; this is the one stand-in that runs, and what it shows is the cost of having no cache
+    and no GPU, not the reference's speed."""
+    import torch
+
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import plain_llama as P
+    from helpers import TINY_A, TINY_B, random_tokens
+
+    from janus_b200.config import resolve_architecture
+    from janus_b200.weights import RandomCheckpoint
+
+    def weights(cfg, seed):
+        arch = resolve_architecture(cfg)
+        ck = RandomCheckpoint(arch.weight_specs(arch.config_class.from_dict(cfg)), seed, dtype="float32")
+        return {n: ck.tensor(n) for n in ck.names()}
+
+    threads = torch.get_num_threads()
+    for name, cfg, seed, lens, new in (("Tiny A", TINY_A, 0, (5, 11, 17), 8), ("Tiny B", TINY_B, 1, (1, 7, 33, 64), 16)):
+        w = weights(cfg, seed)
+        prompts = [random_tokens(n, cfg["vocab_size"], n) for n in lens]
+        P.generate(cfg, w, prompts[0], 2, temperature=0.0)          # warm-up
+        t0 = time.perf_counter()
+        made = sum(len(P.generate(cfg, w, p, new, temperature=0.0)) for p in prompts)
+        dt = time.perf_counter() - t0
+        print(json.dumps({"impl": "plain implementation on the host", "workload": name, "prompts": list(lens),
+                          "new_tokens_each": new, "value": round(made / dt, 1), "unit": "tokens/s",
+                          "wall_s": round(dt, 3), "threads": threads, "dtype": "float32"}), flush=True)
+    layer = dict(CONFIG_8B, num_hidden_layers=1, vocab_size=2048, max_position_embeddings=1024)
+    w = weights(layer, 2)
+    ids = random_tokens(64, 2048, 1)
+    P.forward(layer, w, ids)
+    t0 = time.perf_counter()
+    for _ in range(3):
+        P.forward(layer, w, ids)
+    dt = (time.perf_counter() - t0) / 3
+    flops = 2 * 64 * layer_weight_elems(layer)
+    print(json.dumps({"impl": "plain implementation on the host", "workload": "one 8B-sized layer, 64 tokens, whole",
+                      "value": round(64 / dt, 1), "unit": "tokens/s", "ms": round(dt * 1e3, 2),
+                      "GFLOPs": round(flops / dt / 1e9, 1), "threads": threads, "dtype": "float32"}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -469,6 +660,11 @@ def main():
     ap.add_argument("--batch", type=int, default=8, help="batch size of the headline number")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration (named in `config`)")
     ap.add_argument("--quick", action="store_true", help="headline batch only")
+    ap.add_argument("--no-check", action="store_true",
+                    help="skip the comparison with the 32-bit engine before timing (`checked` is then null)")
+    ap.add_argument("--deterministic", action="store_true",
+                    help="time the headline with the slices of a cut K summed in their fixed order (same bits "
+                         "run to run; as JANUS_DETERMINISTIC=1)")
     ap.add_argument("--workload", default="8b", choices=["8b", "1b", "13b"],
                     help="8b: the headline benchmark; 1b / 13b: the other workloads of BASELINE.json, end to end")
     ap.add_argument("--prompt-lengths", nargs="?", const=PROMPT_STEPS, default=None, metavar="SEQSxTOKENS,...",
@@ -476,7 +672,18 @@ def main():
                          "each; --layers, default 8)")
     ap.add_argument("--kernels", action="store_true",
                     help="time the step's hot kernels alone at the 8B layer shapes (one JSON line each)")
+    ap.add_argument("--contexts", default=None, metavar="KEYS,...",
+                    help="with --kernels: decode attention alone at these context lengths (1 and 8 sequences)")
+    ap.add_argument("--plan-check", action="store_true",
+                    help="time the kernel and K-split that `ops.gemm_plan` picks against its alternatives for the "
+                         "products of 1B-, 8B- and 13B-sized layers (one JSON line each)")
+    ap.add_argument("--cpu-baseline", action="store_true",
+                    help="time the plain implementation of tests/ on the host (the only runnable stand-in for the "
+                         "reference on this box): Tiny A, Tiny B and one 8B-sized layer (one JSON line each)")
     args = ap.parse_args()
+    if args.cpu_baseline:
+        run_cpu_baseline()
+        return 0
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "DaCodeChick/Janus is a Rust workspace that runs WGSL shaders through wgpu (a graphics "
@@ -488,7 +695,10 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.kernels:
-        run_kernels()
+        run_kernels([int(c) for c in args.contexts.split(",")] if args.contexts else None)
+        return 0
+    if args.plan_check:
+        run_plan_check()
         return 0
     if args.prompt_lengths:
         run_prompt_lengths(args.layers or 8, args.prompt_lengths)
@@ -496,8 +706,7 @@ def main():
     if args.workload != "8b":
         run_workload(args.workload)
         return 0
-    run_ours(args)
-    return 0
+    return run_ours(args)
 
 
 if __name__ == "__main__":

@@ -111,8 +111,8 @@ class Model:
                  callback: Optional[Callable[[int, int], bool]] = None,
                  return_reasons: bool = False):
         """Generate up to `max_tokens` new tokens for each prompt (lists of token
-        ids).  Stop tokens are config.json's `eos_token_id` plus
-        `stop_token_ids`, unless `ignore_eos`.  Returns (tokens, stats), or
+        ids).  Stop tokens are the configuration's (config.json's
+        `eos_token_id`) plus `stop_token_ids`, unless `ignore_eos`.  Returns (tokens, stats), or
         (tokens, reasons, stats) with `return_reasons`."""
         sc = SamplerConfig(temperature=temperature, top_k=top_k, top_p=top_p,
                            repetition_penalty=repetition_penalty, max_tokens=max_tokens)
@@ -126,12 +126,21 @@ class Model:
                 self._samplers.clear()
             sampler = DeviceSampler(sc, self.engine.model.vocab_size, cache.n_slots, seed, self.device)
             self._samplers[skey] = sampler
-        stop = [] if ignore_eos else list(getattr(self.config, "eos_token_id", ()) or ())
+        if ignore_eos:
+            stop = []
+        elif hasattr(self.config, "stop_token_ids"):
+            stop = list(self.config.stop_token_ids())
+        else:
+            stop = list(getattr(self.config, "eos_token_id", ()) or ())
         stop += list(stop_token_ids or ())
+        # room that is free now: a caller of alloc_slot/step may hold pages of its own
+        free_tokens = min((g.pool.n_free for g in cache.groups), default=cache.n_pages) * PAGE_SIZE
+        captures_before = self.engine.graph_captures
         outputs, reasons, stats = run_generation(
             _EngineBackend(self.engine, sampler), [list(map(int, p)) for p in prompts], max_tokens, stop,
-            batch_size or cache.n_slots, cache.n_pages * PAGE_SIZE, self.engine.max_seq_len,
+            batch_size or cache.n_slots, free_tokens, self.engine.max_seq_len,
             cache.n_free_slots, PAGE_SIZE, callback)
+        stats.graph_captures = self.engine.graph_captures - captures_before
         self.check()
         if return_reasons:
             return outputs, reasons, stats
@@ -166,9 +175,13 @@ def load(model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_seq_len: 
 
 def load_random(config_dict: dict, seed: int, dtype="bfloat16", max_tokens: int = 8192,
                 max_seq_len: Optional[int] = None, max_slots: Optional[int] = None, device="cuda:0",
-                std: float = 0.02, norm_std: float = 0.0, use_graphs: bool = True) -> Model:
-    """A model with seeded random weights made on the device, without a folder."""
+                std: float = 0.02, norm_std: float = 0.0, use_graphs: bool = True,
+                stored_dtype=None) -> Model:
+    """A model with seeded random weights made on the device, without a folder.  `stored_dtype` is the
+    dtype the weights are "stored" in (default: the engine dtype): "bfloat16" under a float32 engine gives
+    the 32-bit engine exactly the weights that the bfloat16 engine has.  The values are a function of the
+    seed and the tensor's name alone, the same on every device (`weights.RandomCheckpoint`)."""
     def factory(arch, config):
-        return RandomCheckpoint(arch.weight_specs(config), seed, dtype=dtype, std=std, norm_std=norm_std,
-                                device=device)
+        return RandomCheckpoint(arch.weight_specs(config), seed, dtype=stored_dtype or dtype, std=std,
+                                norm_std=norm_std, device=device)
     return _build(config_dict, factory, dtype, max_tokens, max_seq_len, max_slots, device, use_graphs)

@@ -65,6 +65,11 @@ def _parse_rope_scaling(raw: Any) -> Optional[RopeScaling]:
     return s
 
 
+MAX_HEAD_DIM = 256                 # the attention kernels' largest head size, float32 and bfloat16
+LLAMA3_VOCAB_SIZE = 128_256
+LLAMA3_STOP_TOKEN_IDS = (128_001, 128_009)
+
+
 @dataclass(frozen=True)
 class LlamaConfig:
     hidden_size: int
@@ -79,6 +84,9 @@ class LlamaConfig:
     rope_theta: float = 10000.0
     rope_scaling: Optional[RopeScaling] = None
     tie_word_embeddings: bool = False
+    hidden_act: str = "silu"
+    attention_bias: bool = False
+    mlp_bias: bool = False
     bos_token_id: Optional[int] = None
     eos_token_id: Tuple[int, ...] = ()
     torch_dtype: Optional[str] = None
@@ -121,6 +129,9 @@ class LlamaConfig:
             rope_theta=r.number("rope_theta", default=10000.0),         # config.rs:299
             rope_scaling=_parse_rope_scaling(data.get("rope_scaling")),
             tie_word_embeddings=r.boolean("tie_word_embeddings", default=False),
+            hidden_act=r.string("hidden_act", default="silu"),
+            attention_bias=r.boolean("attention_bias", default=False),
+            mlp_bias=r.boolean("mlp_bias", default=False),
             bos_token_id=bos,
             eos_token_id=r.id_list("eos_token_id"),
             torch_dtype=r.string("torch_dtype", default=r.string("dtype", default=None)),
@@ -142,6 +153,19 @@ class LlamaConfig:
                 f"'num_key_value_heads' ({self.num_key_value_heads})")
         if self.head_dim % 2 != 0:
             raise ConfigError(f"key 'head_dim' ({self.head_dim}) must be even for rotary positions")
+        if self.head_dim > MAX_HEAD_DIM:
+            raise ConfigError(f"key 'head_dim' ({self.head_dim}) is not supported: the attention kernels take "
+                              f"head sizes up to {MAX_HEAD_DIM}")
+        # The reference's block has one activation and no bias anywhere (SiLU:
+        # compute/shaders/activations.wgsl:20-35; no bias is looked up: model/block.rs:239-276).
+        # A config.json that asks for something else is refused, not run as if it had not asked.
+        if self.hidden_act != "silu":
+            raise ConfigError(f"key 'hidden_act' ({self.hidden_act!r}) is not supported: the feed-forward's "
+                              f"gate is SiLU ('silu')")
+        if self.attention_bias:
+            raise ConfigError("key 'attention_bias' is true: attention projections with a bias are not supported")
+        if self.mlp_bias:
+            raise ConfigError("key 'mlp_bias' is true: feed-forward projections with a bias are not supported")
         if self.hidden_size > 32768:                                     # config.rs:207-212
             raise ConfigError(f"key 'hidden_size' ({self.hidden_size}) is unreasonably large (>32768)")
         if self.num_hidden_layers > 256:                                 # config.rs:214-219
@@ -151,6 +175,17 @@ class LlamaConfig:
         for t in self.eos_token_id:
             if not 0 <= t < self.vocab_size:
                 raise ConfigError(f"key 'eos_token_id': {t} is outside the vocabulary ({self.vocab_size})")
+
+    def stop_token_ids(self) -> Tuple[int, ...]:
+        """The tokens that end a sequence: config.json's `eos_token_id`; where it names none and the
+        vocabulary is Llama 3's (128,256 entries), the two ids the reference always stops at,
+        <|end_of_text|> 128001 and <|eot_id|> 128009
+        (crates/janus-engine/src/model/transformer/generation.rs:6-7,241)."""
+        if self.eos_token_id:
+            return self.eos_token_id
+        if self.vocab_size == LLAMA3_VOCAB_SIZE:
+            return LLAMA3_STOP_TOKEN_IDS
+        return ()
 
     # -- writing -----------------------------------------------------------
     def to_dict(self) -> Dict[str, Any]:
@@ -168,6 +203,9 @@ class LlamaConfig:
             "rope_theta": self.rope_theta,
             "rope_scaling": None if self.rope_scaling is None else self.rope_scaling.to_dict(),
             "tie_word_embeddings": self.tie_word_embeddings,
+            "hidden_act": self.hidden_act,
+            "attention_bias": self.attention_bias,
+            "mlp_bias": self.mlp_bias,
         }
         if self.bos_token_id is not None:
             d["bos_token_id"] = self.bos_token_id

@@ -634,6 +634,8 @@ JB_EXPORT int jb_attention_bf16_decode_fused(const float* qkv, int qkv_stride, c
 // ---------------------------------------------------------------------------
 // Entry point that allocates nothing (see attention_bf16_noalloc.h).
 // ---------------------------------------------------------------------------
+#include <atomic>
+
 #include "attention_bf16_noalloc.h"
 
 namespace {
@@ -643,7 +645,9 @@ namespace {
 static __device__ __align__(256) float noalloc_scratch[JB_NOALLOC_SCRATCH_FLOATS];
 
 constexpr int NOALLOC_MAX_DEVICES = 64;
-float* noalloc_device_ptr[NOALLOC_MAX_DEVICES];   // per device: address of noalloc_scratch there
+// per device: address of noalloc_scratch there.  Threads that make a device's first call at the same
+// time each look the address up and store the same value.
+std::atomic<float*> noalloc_device_ptr[NOALLOC_MAX_DEVICES];
 
 }  // namespace
 
@@ -656,8 +660,9 @@ JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cach
   JB_REFUSE(page_size != PAGE, "attention_bf16: page size %d (need %d)", page_size, PAGE);
   JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_bf16: %d heads are not a multiple of %d kv heads", nh, nkv);
   JB_REFUSE(n_splits < 1, "attention_bf16 decode: n_splits must be at least 1, got %d", n_splits);
-  const size_t o_floats = (size_t)n_seqs * nh * n_splits * HD;
-  const size_t ml_floats = (size_t)n_seqs * nh * n_splits * 2;
+  // one split writes straight to `out`: no scratch is touched, whatever the batch
+  const size_t o_floats = n_splits > 1 ? (size_t)n_seqs * nh * n_splits * HD : 0;
+  const size_t ml_floats = n_splits > 1 ? (size_t)n_seqs * nh * n_splits * 2 : 0;
   JB_REFUSE(o_floats + ml_floats > JB_NOALLOC_SCRATCH_FLOATS,
             "attention_bf16 decode without allocation: %zu scratch floats are needed (n_seqs %d x heads %d x "
             "splits %d x (head_dim %d + 2)), the built-in array holds %u",
@@ -666,17 +671,19 @@ JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cach
   cudaError_t e = cudaGetDevice(&device);
   if (e != cudaSuccess) return (int)e;
   JB_REFUSE(device < 0 || device >= NOALLOC_MAX_DEVICES, "attention_bf16 decode without allocation: device %d", device);
-  if (noalloc_device_ptr[device] == nullptr) {
+  float* scratch = noalloc_device_ptr[device].load();
+  if (scratch == nullptr) {
     // set-up, once per device, with that device current
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, noalloc_scratch);
     if (e != cudaSuccess) return (int)e;
     e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
     if (e != cudaSuccess) return (int)e;
-    noalloc_device_ptr[device] = static_cast<float*>(p);
+    scratch = static_cast<float*>(p);
+    noalloc_device_ptr[device].store(scratch);
   }
-  float* part_o = noalloc_device_ptr[device];
-  float* part_ml = part_o + o_floats;
+  float* part_o = n_splits > 1 ? scratch : nullptr;
+  float* part_ml = n_splits > 1 ? scratch + o_floats : nullptr;
   const int G = nh / nkv;
   const int n_rb = (G + 15) / 16;
   dim3 grid(n_seqs, nkv * n_rb, n_splits);

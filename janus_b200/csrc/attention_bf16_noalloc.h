@@ -12,12 +12,18 @@
 // scratch buffer.  Inputs and outputs are still the caller's.
 //
 //  * The array holds JB_NOALLOC_SCRATCH_FLOATS floats (4 MiB).  Every GPU that
-//    loads this library keeps it until the process exits.  A call needs
-//    n_seqs * n_heads * n_splits * (head_dim + 2) floats; a call that needs
-//    more is refused with JB_ERR_BAD_SIZE and a message on stderr.
+//    loads this library keeps it until the process exits.  The attention
+//    library is built once per head size (-DJB_HEAD_DIM), and each build is a
+//    shared library of its own with an array of its own: a process that loads
+//    the builds for four head sizes holds four arrays, 16 MiB per GPU.
+//  * A call with n_splits > 1 needs n_seqs * n_heads * n_splits * (head_dim + 2)
+//    floats; a call that needs more is refused with JB_ERR_BAD_SIZE and a
+//    message on stderr.  With n_splits == 1 the kernel writes straight to
+//    `out`, the array is not touched and any batch size is taken.
 //  * The first call on a device looks up the array's device address
 //    (cudaGetSymbolAddress, with that device current) and remembers it; make
-//    that first call before any stream capture begins.
+//    that first call before any stream capture begins.  Several host threads
+//    may make it at the same time.
 //  * No cudaMalloc, cudaFree or allocating library routine is called, on the
 //    first call or later.
 //  * All calls share the one array, and it keeps the last call's contents.

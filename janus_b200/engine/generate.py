@@ -39,6 +39,7 @@ class GenerationStats:
     decode_steps: int = 0
     decode_tokens: int = 0
     decode_ms: float = 0.0
+    graph_captures: int = 0       # decode steps that had to record a new CUDA graph (filled in by the caller)
 
     @property
     def prefill_tokens_per_s(self) -> float:
@@ -125,38 +126,59 @@ def run_generation(backend: GenerationBackend, prompts: Sequence[Sequence[int]],
                            page_size)
         pending = pending[len(batch):]
         stats.batches += 1
-        slots = {r: backend.alloc_slot() for r in batch}
-        backend.synchronize()
-        t0 = time.perf_counter()
-        first = backend.prefill([slots[r] for r in batch], [prompts[r] for r in batch], batch)
-        backend.synchronize()
-        stats.prefill_ms += (time.perf_counter() - t0) * 1e3
-        stats.prefill_tokens += sum(prompt_lens[r] for r in batch)
-        live: List[int] = []
-        for r, tok in zip(batch, first):
-            if accept(r, int(tok)):
-                live.append(r)
-            else:
-                backend.free_slot(slots.pop(r))
-        t0 = time.perf_counter()
-        if getattr(backend, "decode_launch", None) is not None:
-            _decode_run_ahead(backend, live, slots, outputs, prompt_lens, max_new_tokens, max_seq_len, accept, stats)
-        else:
-            while live:
-                toks = backend.decode([slots[r] for r in live], [outputs[r][-1] for r in live], live,
-                                      [len(outputs[r]) for r in live])
-                stats.decode_steps += 1
-                stats.decode_tokens += len(live)
-                still: List[int] = []
-                for r, tok in zip(live, toks):
-                    if accept(r, int(tok)):
-                        still.append(r)
-                    else:
+        slots: dict = {}
+        try:
+            for r in batch:
+                slots[r] = backend.alloc_slot()
+            _run_batch(backend, batch, slots, prompts, prompt_lens, outputs, max_new_tokens, max_seq_len, accept,
+                       stats)
+        finally:
+            # whatever ended the batch (a full cache, a kernel error, a callback that raised, an
+            # interrupt): wait for what is still in flight, then every slot it still holds comes back
+            if slots:
+                try:
+                    backend.synchronize()
+                finally:
+                    for r in list(slots):
                         backend.free_slot(slots.pop(r))
-                live = still
-        backend.synchronize()
-        stats.decode_ms += (time.perf_counter() - t0) * 1e3
     return outputs, reasons, stats
+
+
+def _run_batch(backend, batch: Sequence[int], slots: dict, prompts, prompt_lens: Sequence[int],
+               outputs: List[List[int]], max_new_tokens: int, max_seq_len: int,
+               accept: Callable[[int, int], bool], stats: GenerationStats) -> None:
+    """One batch from its prompts to its last token.  `slots` maps request to slot; a request
+    that ends gives its slot back at once and leaves the map."""
+    backend.synchronize()
+    t0 = time.perf_counter()
+    first = backend.prefill([slots[r] for r in batch], [prompts[r] for r in batch], batch)
+    backend.synchronize()
+    stats.prefill_ms += (time.perf_counter() - t0) * 1e3
+    stats.prefill_tokens += sum(prompt_lens[r] for r in batch)
+    live: List[int] = []
+    for r, tok in zip(batch, first):
+        if accept(r, int(tok)):
+            live.append(r)
+        else:
+            backend.free_slot(slots.pop(r))
+    t0 = time.perf_counter()
+    if getattr(backend, "decode_launch", None) is not None:
+        _decode_run_ahead(backend, live, slots, outputs, prompt_lens, max_new_tokens, max_seq_len, accept, stats)
+    else:
+        while live:
+            toks = backend.decode([slots[r] for r in live], [outputs[r][-1] for r in live], live,
+                                  [len(outputs[r]) for r in live])
+            stats.decode_steps += 1
+            stats.decode_tokens += len(live)
+            still: List[int] = []
+            for r, tok in zip(live, toks):
+                if accept(r, int(tok)):
+                    still.append(r)
+                else:
+                    backend.free_slot(slots.pop(r))
+            live = still
+    backend.synchronize()
+    stats.decode_ms += (time.perf_counter() - t0) * 1e3
 
 
 FROM_DEVICE = -1   # as a token handed to `decode_launch`: the token the step before produced for that slot

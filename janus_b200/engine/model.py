@@ -18,9 +18,7 @@ from ..weights.loader import TensorSpec, load_named
 
 
 def _layer_parts(spec: LayerSpec):
-    return (("mixer_norm", "norm", spec.mixer_norm), ("mixer", "mixer", spec.mixer),
-            ("feed_forward_norm", "norm", spec.feed_forward_norm),
-            ("feed_forward", "feed_forward", spec.feed_forward))
+    return spec.parts()
 
 
 class DecoderModel:
@@ -34,6 +32,8 @@ class DecoderModel:
             self._layer_part_objs.append(objs)
             self.layers.append(_arrange(ls.arrangement, objs, spec.hidden_size, dtype))
         self.final_norm = make_part("norm", spec.final_norm, dtype, device)
+        self.embedding_transforms = [make_part("transform", ps, dtype, device) for ps in spec.embedding_transforms]
+        self.logit_transforms = [make_part("transform", ps, dtype, device) for ps in spec.logit_transforms]
         self.embedding: Optional[torch.Tensor] = None
         self.head = Linear(spec.hidden_size, spec.vocab_size, dtype, device)
         self.schedule = list(spec.schedule)
@@ -52,13 +52,24 @@ class DecoderModel:
                        else self._layer_part_objs[e.layer]["mixer"].cache_spec())
         return out
 
+    def limit_positions(self, n: int) -> None:
+        """The engine's longest sequence: parts that tabulate something per position
+        (rotary tables) need no more rows than that."""
+        for objs in self._layer_part_objs:
+            for part in objs.values():
+                limit = getattr(part, "limit_positions", None)
+                if limit is not None:
+                    limit(n)
+
     # -- weights --------------------------------------------------------------------
     def weight_specs(self) -> List[TensorSpec]:
-        return model_weight_specs(self.spec, self._layer_part_objs, self.final_norm)
+        return model_weight_specs(self.spec, self._layer_part_objs, self.final_norm,
+                                  self.embedding_transforms + self.logit_transforms)
 
     def load(self, checkpoint) -> None:
         spec = self.spec
-        named = load_named(checkpoint, self.weight_specs(), ignorable=spec.ignorable_weights)
+        named = load_named(checkpoint, self.weight_specs(), ignorable=spec.ignorable_weights,
+                           engine_dtype=self.dtype)
         emb = named[spec.embedding_weight]
         self.embedding = emb.to(device=self.device, dtype=self.dtype).contiguous()
         if spec.head_weight is None:
@@ -69,6 +80,9 @@ class DecoderModel:
         for ls, objs in zip(spec.layers, self._layer_part_objs):
             for attr, _family, ps in _layer_parts(ls):
                 objs[attr].load(**{k: named[v] for k, v in ps.weights.items()})
+        for ps, part in zip(spec.embedding_transforms + spec.logit_transforms,
+                            self.embedding_transforms + self.logit_transforms):
+            part.load(**{k: named[v] for k, v in ps.weights.items()})
 
     # -- forward ----------------------------------------------------------------------
     def forward(self, ctx, want_rows: torch.Tensor, logits: torch.Tensor) -> None:
@@ -82,6 +96,8 @@ class DecoderModel:
         residual = ctx.workspace.get("residual", (T, self.hidden_size), torch.float32)
         ops.embed_gather(self.embedding, ctx.token_ids, residual, ctx.feedback,
                          ctx.seq_slot if ctx.feedback is not None else None)
+        for transform in self.embedding_transforms:
+            transform.forward(residual, ctx)
         for place, entry in enumerate(self.schedule):
             view = ctx.cache_view(place if entry.reads_cache_of is None else entry.reads_cache_of)
             self.layers[entry.layer].forward(residual, ctx, view, writes_cache=entry.reads_cache_of is None)
@@ -91,6 +107,8 @@ class DecoderModel:
         z = ctx.workspace.get("final_normed", (n_want, self.hidden_size), self.dtype)
         self.final_norm.forward(residual, z, row_index=want_rows)
         self.head.forward(z, logits)
+        for transform in self.logit_transforms:
+            transform.forward(logits, ctx)
 
 
 def _arrange(kind: str, objs: Dict[str, object], hidden_size: int, dtype: torch.dtype):
@@ -99,11 +117,10 @@ def _arrange(kind: str, objs: Dict[str, object], hidden_size: int, dtype: torch.
         factory = _REGISTRIES["arrangement"][kind]
     except KeyError:
         raise KeyError(f"no arrangement '{kind}' is registered") from None
-    return factory(objs["mixer_norm"], objs["mixer"], objs["feed_forward_norm"], objs["feed_forward"],
-                   hidden_size, dtype)
+    return factory(objs, hidden_size, dtype)
 
 
-def model_weight_specs(spec: ModelSpec, layer_part_objs=None, final_norm=None) -> List[TensorSpec]:
+def model_weight_specs(spec: ModelSpec, layer_part_objs=None, final_norm=None, transforms=None) -> List[TensorSpec]:
     """Every tensor the model reads, with its shape, from the parts' own
     `weight_shapes()` and the spec's names.  Built on the CPU when no parts are
     given (the random-weights writer needs no device)."""
@@ -112,6 +129,8 @@ def model_weight_specs(spec: ModelSpec, layer_part_objs=None, final_norm=None) -
         layer_part_objs = [{attr: make_part(family, ps, torch.float32, cpu) for attr, family, ps in _layer_parts(ls)}
                            for ls in spec.layers]
         final_norm = make_part("norm", spec.final_norm, torch.float32, cpu)
+        transforms = [make_part("transform", ps, torch.float32, cpu)
+                      for ps in spec.embedding_transforms + spec.logit_transforms]
     out: Dict[str, TensorSpec] = {}
 
     def add(name: str, shape, init: str):
@@ -130,6 +149,12 @@ def model_weight_specs(spec: ModelSpec, layer_part_objs=None, final_norm=None) -
                 add(ps.weights[param], shape, init)
     for param, (shape, init) in final_norm.weight_shapes().items():
         add(spec.final_norm.weights[param], shape, init)
+    for ps, part in zip(spec.embedding_transforms + spec.logit_transforms, transforms or ()):
+        shapes = part.weight_shapes()
+        if set(shapes) != set(ps.weights):
+            raise ValueError(f"{ps.kind}: weights {sorted(shapes)} are needed, names are given for {sorted(ps.weights)}")
+        for param, (shape, init) in shapes.items():
+            add(ps.weights[param], shape, init)
     if spec.head_weight is not None:
         add(spec.head_weight, (spec.vocab_size, spec.hidden_size), "normal")
     return list(out.values())

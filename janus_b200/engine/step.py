@@ -94,11 +94,16 @@ class Engine:
         self.max_seq_len = min(o.max_seq_len or model.spec.max_positions, model.spec.max_positions)
         n_pages = max(1, (o.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE)
         n_slots = o.max_slots or min(n_pages, 1024)
+        model.limit_positions(self.max_seq_len)
         self.cache = SequenceCache(model.place_cache_specs(), o.max_tokens, n_slots, self.dtype, self.device)
         self.workspace = Workspace(self.device)
         self._pinned: Optional[torch.Tensor] = None
         self._graphs: Dict[Tuple, object] = {}
         self._capture_stream: Optional[torch.cuda.Stream] = None
+        self.graph_captures = 0            # decode steps that found no captured graph and recorded one
+        # logits and sampled tokens of graph steps: one buffer for all graphs (a graph records a view)
+        self._graph_logits: Optional[torch.Tensor] = None
+        self._graph_tokens = torch.zeros(n_slots, dtype=torch.int32, device=self.device)
         self.last_graph_launches = 0       # kernels of this library in the last step
         self.last_step_h2d_bytes = 0       # bytes of the last step's index buffer
         # per slot: the token sampled last by a graph step, so that the next step can
@@ -302,7 +307,7 @@ class Engine:
                 del self._graphs[k]          # buffers moved: those graphs hold stale addresses
             rec = _DecodeGraph(self, B, cap, sampler)
             rec.fill(entries, sampling)
-            rec.run_forward(sample=False)    # eager: sizes the workspace, configures the kernels
+            rec.run_forward()                # direct: this run is the step
             torch.cuda.synchronize(self.device)
             key = (B, cap, self.workspace.generation, key[3])
             graph = torch.cuda.CUDAGraph()
@@ -329,17 +334,29 @@ class Engine:
                 if gc_was_on:
                     gc.enable()
             rec.graph, rec.launches = graph, ops.launch_count() - before
-            while len(self._graphs) >= MAX_DECODE_GRAPHS:      # each holds a logits buffer: keep the newest
+            self.graph_captures += 1
+            while len(self._graphs) >= MAX_DECODE_GRAPHS:      # keep the ones used last
                 del self._graphs[next(iter(self._graphs))]
             self._graphs[key] = rec
-            # the eager run and the capture wrote this step's keys already; the
-            # replay below writes the same values again
         else:
+            self._graphs[key] = self._graphs.pop(key)          # used last: to the end of the line
             rec.fill(entries, sampling)
+            rec.graph.replay()
         self.last_graph_launches = rec.launches
         self.last_step_h2d_bytes = 4 * rec.total
-        rec.graph.replay()
         return rec.logits, rec.tokens_out
+
+    def _graph_output_buffers(self, B: int):
+        """Views for B rows of the logits and token buffers that all captured steps share.  A batch
+        larger than any before gets a larger buffer; graphs recorded on the old one keep it alive."""
+        V = self.model.vocab_size
+        if self._graph_logits is None or self._graph_logits.shape[0] < B:
+            rows = 8
+            while rows < B:
+                rows *= 2
+            rows = min(rows, max(self.cache.n_slots, B))
+            self._graph_logits = torch.empty((rows, V), dtype=torch.float32, device=self.device)
+        return self._graph_logits[:B], self._graph_tokens[:B]
 
 
 class _DecodeGraph:
@@ -359,8 +376,8 @@ class _DecodeGraph:
         self.extra = 7 + 2 * G                      # first of the three sampling segments
         dev = engine.device
         self.meta = torch.zeros(self.total, dtype=torch.int32, device=dev)
-        self.logits = torch.empty((B, engine.model.vocab_size), dtype=torch.float32, device=dev)
-        self.tokens_out = torch.zeros(B, dtype=torch.int32, device=dev) if sampler is not None else None
+        self.logits, tokens_out = engine._graph_output_buffers(B)
+        self.tokens_out = tokens_out if sampler is not None else None
         self.host = [torch.zeros(self.total, dtype=torch.int32, pin_memory=True) for _ in range(2)]
         self.host_np = [h.numpy() for h in self.host]
         o = self.offsets
@@ -390,9 +407,9 @@ class _DecodeGraph:
         self.ctx, self.want_rows = ctx, seg(6, B)
         self.sample_meta = (seg(self.extra, B), seg(self.extra + 1, B), seg(self.extra + 2, B))
 
-    def run_forward(self, sample: bool = True) -> None:
+    def run_forward(self) -> None:
         self.engine.model.forward(self.ctx, self.want_rows, self.logits)
-        if sample and self.sampler is not None:   # sampling may count tokens: it runs in the replay only
+        if self.sampler is not None:
             requests, steps, count_rows = self.sample_meta
             self.sampler.sample_into(self.logits, self.tokens_out, requests, steps, count_rows,
                                      self.engine.feedback)

@@ -580,6 +580,10 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_
 
 
 # -- bfloat16 attention (one library per head size) -----------------------------------
+ATTENTION_MAX_HEAD_DIM = 256      # every attention kernel, float32 and bfloat16
+ATTENTION_BF16_MAX_GROUP = 64     # query heads per kv head of the mma.sync prompt kernel (a row tile holds 64 rows)
+
+
 def _attention_lib(hd: int):
     if hd % 8 or not 8 <= hd <= 256:
         raise KernelError(f"attention_bf16: head_dim {hd} is not a multiple of 8 in [8, 256]")

@@ -17,12 +17,28 @@ from typing import Optional
 import torch
 
 from ..kernels import ops
-from .base import KVSpec, Mixer, PartSpec, make_part, register_part
+from .base import KVSpec, Mixer, PartSpec, register_part, shared_part
 from .linear import Linear
 
 
 # JANUS_FUSED_DECODE=0 keeps rotation and cache append in a kernel of their own for decode steps too
 _FUSED_DECODE = os.environ.get("JANUS_FUSED_DECODE", "1") != "0"
+
+
+def _check_kernel_limits(num_heads: int, num_kv_heads: int, head_dim: int, dtype: torch.dtype) -> None:
+    """Refuse, when the part is built, the sizes that the attention kernels refuse at a step."""
+    if head_dim < 1 or head_dim > ops.ATTENTION_MAX_HEAD_DIM:
+        raise ValueError(f"head_dim {head_dim} is not supported: the attention kernels take head sizes up to "
+                         f"{ops.ATTENTION_MAX_HEAD_DIM}")
+    if dtype == torch.bfloat16:
+        if head_dim % 8:
+            raise ValueError(f"head_dim {head_dim} is not supported in bfloat16 (it must be a multiple of 8: "
+                             f"cache rows are read in 16-byte pieces); such a model runs with dtype float32")
+        group = num_heads // num_kv_heads
+        if (group > ops.ATTENTION_BF16_MAX_GROUP
+                and not ops.attention_tc_supported(num_heads, num_kv_heads, head_dim)):
+            raise ValueError(f"{group} query heads per key/value head are not supported in bfloat16 with head_dim "
+                             f"{head_dim} (at most {ops.ATTENTION_BF16_MAX_GROUP}); such a model runs with dtype float32")
 
 
 class GQAttention(Mixer):
@@ -35,7 +51,9 @@ class GQAttention(Mixer):
         self.window = int(window)
         self.dtype, self.device = dtype, device
         self.scale = 1.0 / math.sqrt(head_dim)          # crates/janus-engine/src/compute/ops/attention.rs:98
-        self.position = make_part("position", position, dtype, device) if position is not None else None
+        _check_kernel_limits(num_heads, num_kv_heads, head_dim, dtype)
+        # layers that name the same position encoding share one object (one table on the device)
+        self.position = shared_part("position", position, dtype, device) if position is not None else None
         self.q_width, self.kv_width = num_heads * head_dim, num_kv_heads * head_dim
         self.qkv = Linear(hidden_size, self.q_width + 2 * self.kv_width, dtype, device)
         self.q_only: Optional[Linear] = None             # view of the q rows, for layers that read another cache
@@ -43,6 +61,11 @@ class GQAttention(Mixer):
 
     def cache_spec(self) -> KVSpec:
         return KVSpec(self.nkv, self.hd, self.window)
+
+    def limit_positions(self, n: int) -> None:
+        limit = getattr(self.position, "limit_positions", None)
+        if limit is not None:
+            limit(n)
 
     def weight_shapes(self):
         return {"q": ((self.q_width, self.hidden_size), "normal"),

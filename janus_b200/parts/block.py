@@ -10,9 +10,19 @@ from .base import register_part
 
 
 class PreNormBlock:
-    def __init__(self, mixer_norm, mixer, feed_forward_norm, feed_forward, hidden_size: int, dtype: torch.dtype):
-        self.mixer_norm, self.mixer = mixer_norm, mixer
-        self.feed_forward_norm, self.feed_forward = feed_forward_norm, feed_forward
+    """`parts`: mixer_norm and mixer, and, unless the layer has no feed-forward,
+    feed_forward_norm and feed_forward."""
+
+    def __init__(self, parts: dict, hidden_size: int, dtype: torch.dtype):
+        unknown = set(parts) - {"mixer_norm", "mixer", "feed_forward_norm", "feed_forward"}
+        if unknown:
+            raise ValueError(f"the pre_norm arrangement has no use for the parts {sorted(unknown)}")
+        try:
+            self.mixer_norm, self.mixer = parts["mixer_norm"], parts["mixer"]
+            self.feed_forward = parts.get("feed_forward")
+            self.feed_forward_norm = parts["feed_forward_norm"] if self.feed_forward is not None else None
+        except KeyError as e:
+            raise ValueError(f"the pre_norm arrangement needs the part {e.args[0]!r}") from None
         self.hidden_size, self.dtype = hidden_size, dtype
 
     def forward(self, residual: torch.Tensor, ctx, cache_view, writes_cache: bool = True) -> None:
@@ -26,6 +36,8 @@ class PreNormBlock:
         else:
             self.mixer_norm.forward(residual, x)
             self.mixer.forward(x, residual, ctx, cache_view, writes_cache)
+        if self.feed_forward is None:
+            return
         self.feed_forward_norm.forward(residual, x)
         self.feed_forward.forward(x, residual, ctx)
 

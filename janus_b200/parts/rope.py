@@ -45,8 +45,28 @@ class RotaryEncoding(PositionEncoding):
         if scaling is not None:
             inv_freq = llama3_scaled(inv_freq, **{k: v for k, v in scaling.items() if k != "rope_type"})
         self.inv_freq = inv_freq
-        angle = torch.arange(self.max_positions, dtype=torch.float32)[:, None] * inv_freq[None, :]
-        self.table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).contiguous().to(device)
+        self._limit = self.max_positions
+        self._table: Optional[torch.Tensor] = None
+
+    def limit_positions(self, n: int) -> None:
+        """Positions beyond `n` are never asked for (the engine's longest sequence):
+        the table gets no more rows than that.  Several engines may share this
+        object; the largest limit counts, and a table that is too short is made
+        anew (the engine that asked for less has captured no step yet)."""
+        n = min(int(n), self.max_positions)
+        if self._table is None:
+            self._limit = n
+        elif n > self._table.shape[0]:
+            self._limit, self._table = n, None
+
+    @property
+    def table(self) -> torch.Tensor:
+        """cos and sin of position * inv_freq, float32 [positions, head_dim/2, 2],
+        tabulated on the host at first use and shared by every layer."""
+        if self._table is None:
+            angle = torch.arange(self._limit, dtype=torch.float32)[:, None] * self.inv_freq[None, :]
+            self._table = torch.stack([torch.cos(angle), torch.sin(angle)], dim=-1).contiguous().to(self.device)
+        return self._table
 
     def fused_rotary_table(self) -> torch.Tensor:
         return self.table

@@ -16,6 +16,9 @@ def main(argv=None) -> int:
     ap.add_argument("--out", required=True, help="folder for <step>.f32 files")
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time, each rounded up to a multiple of 64")
+    ap.add_argument("--no-graphs", action="store_true",
+                    help="launch the kernels of single-token steps one by one instead of replaying them from "
+                         "CUDA graphs, as generation does")
     args = ap.parse_args(argv)
 
     print("[trace_run] loading (kernels are compiled at the first call; this can take a minute)",
@@ -26,7 +29,8 @@ def main(argv=None) -> int:
     from janus_b200.engine.step import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
-    model = janus_b200.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens, use_graphs=False)
+    model = janus_b200.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
+                            use_graphs=not args.no_graphs)
     slots: Dict[str, int] = {}
     for line in sys.stdin:
         line = line.strip()

@@ -8,8 +8,12 @@ before anything is copied to a device.  (The reference reports one missing name
 at a time, crates/janus-engine/src/model/block.rs:19-51, and only warns on a
 size mismatch, crates/janus-engine/src/formats/safetensors.rs:137-146.)
 
-Stored dtypes are kept: 16-bit floats become bfloat16, a tensor stored in
-32-bit floats stays float32, integer tables become int32.
+Stored dtypes are kept for the bfloat16 engine: 16-bit floats become bfloat16
+(float16 is rounded once, to nearest even), a tensor stored in 32-bit floats
+stays float32, integer tables become int32.  The float32 engine widens every
+stored float exactly (the reference widens each stored dtype before its one
+rounding, crates/janus-engine/src/compute/engine.rs:446-633); float16 is never
+rounded to bfloat16 on the way.
 """
 from __future__ import annotations
 
@@ -49,9 +53,13 @@ class FolderCheckpoint:
         if os.path.exists(single):
             files = [single]
         elif os.path.exists(index):
-            with open(index) as f:
-                weight_map = json.load(f).get("weight_map", {})
-            files = sorted({os.path.join(model_dir, v) for v in weight_map.values()})
+            try:
+                with open(index) as f:
+                    weight_map = json.load(f)["weight_map"]
+                files = sorted({os.path.join(model_dir, v) for v in weight_map.values()})
+            except (OSError, ValueError, KeyError, TypeError, AttributeError) as e:
+                raise WeightError(f"'{index}' is no shard index (a JSON object with a 'weight_map' of tensor "
+                                  f"name -> file name): {e!r}") from e
         else:
             raise WeightError(
                 f"no weights in '{model_dir}': expected model.safetensors or model.safetensors.index.json")
@@ -61,6 +69,8 @@ class FolderCheckpoint:
             except SafetensorsError as e:
                 raise WeightError(str(e)) from e
             for n in sf.names():
+                if n in self._where:
+                    raise WeightError(f"tensor '{n}' is stored twice: in '{self._where[n].path}' and in '{path}'")
                 self._where[n] = sf
 
     def names(self) -> List[str]:
@@ -76,9 +86,10 @@ class FolderCheckpoint:
         return self._where[name].tensor(name)
 
 
-def kept_dtype(stored: torch.dtype) -> torch.dtype:
+def kept_dtype(stored: torch.dtype, engine_dtype: torch.dtype = torch.bfloat16) -> torch.dtype:
+    """The dtype a stored tensor is handed out in, for an engine of `engine_dtype`."""
     if stored in (torch.bfloat16, torch.float16):
-        return torch.bfloat16
+        return torch.float32 if engine_dtype == torch.float32 else torch.bfloat16
     if stored in (torch.float32, torch.float64):
         return torch.float32
     if stored in (torch.int64, torch.int32, torch.int16, torch.int8, torch.uint8, torch.bool):
@@ -113,9 +124,10 @@ class NamedTensors:
     the checkpoint when a part asks for it, so a model larger than host memory
     can still be placed tensor by tensor."""
 
-    def __init__(self, checkpoint, names: Iterable[str]):
+    def __init__(self, checkpoint, names: Iterable[str], engine_dtype: torch.dtype = torch.bfloat16):
         self._checkpoint = checkpoint
         self._names = set(names)
+        self._engine_dtype = engine_dtype
 
     def __contains__(self, name: str) -> bool:
         return name in self._names
@@ -124,15 +136,17 @@ class NamedTensors:
         if name not in self._names:
             raise KeyError(name)
         t = self._checkpoint.tensor(name)
-        return t.to(kept_dtype(t.dtype))
+        return t.to(kept_dtype(t.dtype, self._engine_dtype))
 
     def keys(self):
         return sorted(self._names)
 
 
-def load_named(checkpoint, specs: Sequence[TensorSpec], ignorable: Iterable[str] = ()) -> NamedTensors:
+def load_named(checkpoint, specs: Sequence[TensorSpec], ignorable: Iterable[str] = (),
+               engine_dtype: torch.dtype = torch.bfloat16) -> NamedTensors:
     """Check the whole checkpoint against the specs (one error for all
-    misfits), then give access to the tensors the specs name."""
+    misfits), then give access to the tensors the specs name, in the dtype
+    an engine of `engine_dtype` keeps them in."""
     check_names(checkpoint, specs, ignorable)
     have = set(checkpoint.names())
-    return NamedTensors(checkpoint, [s.name for s in specs if s.name in have])
+    return NamedTensors(checkpoint, [s.name for s in specs if s.name in have], engine_dtype)

@@ -37,25 +37,44 @@ TINY_B = dict(
 TINY = {"A": TINY_A, "B": TINY_B}
 
 
-def make_model_dir(cfg: dict, out_dir: str, seed: int, dtype: str, sharpen: float = 6.0) -> str:
+def make_model_dir(cfg: dict, out_dir: str, seed: int, dtype: str, sharpen: float = 6.0,
+                   stored: str = None, shards: int = 1) -> str:
     """A model folder with random weights; q and k projections are scaled by
-    `sharpen` so that attention is peaked and a wrong key shows in the logits."""
+    `sharpen` so that attention is peaked and a wrong key shows in the logits.
+    `stored`: "float16" writes the file in float16 (values made in float32);
+    `shards` > 1 writes that many files and `model.safetensors.index.json`."""
     from janus_b200.config import resolve_architecture
     from janus_b200.weights import RandomCheckpoint, save_file
 
     arch = resolve_architecture(cfg)
     config = arch.config_class.from_dict(cfg)
-    ck = RandomCheckpoint(arch.weight_specs(config), seed, dtype=dtype, std=0.02, norm_std=0.02)
+    # the random source gives the same bits on every device: a GPU, where there is one, is only faster
+    device = "cuda" if torch.cuda.is_available() else "cpu"
+    ck = RandomCheckpoint(arch.weight_specs(config), seed, dtype="float32" if stored else dtype, std=0.02,
+                          norm_std=0.02, device=device)
     tensors = {}
     for name in ck.names():
-        t = ck.tensor(name)
+        t = ck.tensor(name).cpu()
         if name.endswith("q_proj.weight") or name.endswith("k_proj.weight"):
             t = (t.float() * sharpen).to(t.dtype)
+        if stored:
+            t = t.to(getattr(torch, stored))
         tensors[name] = t
     os.makedirs(out_dir, exist_ok=True)
     with open(os.path.join(out_dir, "config.json"), "w") as f:
         json.dump(cfg, f)
-    save_file(tensors, os.path.join(out_dir, "model.safetensors"))
+    if shards <= 1:
+        save_file(tensors, os.path.join(out_dir, "model.safetensors"))
+        return out_dir
+    names = sorted(tensors)
+    weight_map = {}
+    for i in range(shards):
+        fname = f"model-{i + 1:05d}-of-{shards:05d}.safetensors"
+        mine = names[i::shards]
+        save_file({n: tensors[n] for n in mine}, os.path.join(out_dir, fname))
+        weight_map.update({n: fname for n in mine})
+    with open(os.path.join(out_dir, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {}, "weight_map": weight_map}, f)
     return out_dir
 
 
@@ -80,12 +99,12 @@ class TraceRun:
     """Drives `bin/trace_run` as a user does: steps in on stdin, one at a time
     after the `done` line of the one before; logits back from files."""
 
-    def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int):
+    def __init__(self, model_dir: str, dtype: str, out_dir: str, max_tokens: int, graphs: bool = True):
         self.out_dir = out_dir
         env = dict(os.environ)
         self.proc = subprocess.Popen(
             [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
-             "--out", out_dir, "--max-tokens", str(max_tokens)],
+             "--out", out_dir, "--max-tokens", str(max_tokens)] + ([] if graphs else ["--no-graphs"]),
             stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
         self.step_no = 0
 

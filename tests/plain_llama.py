@@ -38,9 +38,16 @@ def read_model_dir(model_dir: str, dtype=torch.float32):
     with open(os.path.join(model_dir, "config.json")) as f:
         cfg = json.load(f)
     tensors = {}
-    with safe_open(os.path.join(model_dir, "model.safetensors"), framework="pt") as f:
-        for name in f.keys():
-            tensors[name] = f.get_tensor(name).to(dtype)
+    single = os.path.join(model_dir, "model.safetensors")
+    if os.path.exists(single):
+        files = [single]
+    else:      # a sharded folder: every file that model.safetensors.index.json names
+        with open(os.path.join(model_dir, "model.safetensors.index.json")) as f:
+            files = sorted({os.path.join(model_dir, v) for v in json.load(f)["weight_map"].values()})
+    for path in files:
+        with safe_open(path, framework="pt") as f:
+            for name in f.keys():
+                tensors[name] = f.get_tensor(name).to(dtype)
     return cfg, tensors
 
 

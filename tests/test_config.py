@@ -141,3 +141,76 @@ def test_key_splits_of_decode_attention_stay_within_the_pages():
     assert ops.decode_splits_for(8, 8, 4096, 64) == 4
     assert ops.decode_splits_for(64, 8, 4096, 64) == 1
     assert ops.decode_splits_for(1, 8, 4096, 64) == 16
+
+
+def test_keys_the_kernels_cannot_honour_are_refused_by_name():
+    """A config.json that asks for another activation or for biases is refused when it is read; it would
+    otherwise run as if it had not asked."""
+    from janus_b200.config import ConfigError, LlamaConfig
+    from helpers import TINY_A
+    assert LlamaConfig.from_dict(dict(TINY_A, hidden_act="silu", attention_bias=False, mlp_bias=False)).hidden_act == "silu"
+    for key, value in (("hidden_act", "gelu"), ("attention_bias", True), ("mlp_bias", True)):
+        with pytest.raises(ConfigError, match=key):
+            LlamaConfig.from_dict(dict(TINY_A, **{key: value}))
+    with pytest.raises(ConfigError, match="head_dim"):
+        LlamaConfig.from_dict(dict(TINY_A, head_dim=272))
+    # the keys survive a round trip through to_dict
+    cfg = LlamaConfig.from_dict(TINY_A)
+    assert LlamaConfig.from_dict(cfg.to_dict()) == cfg
+
+
+def test_sizes_the_attention_kernels_cannot_take_are_refused_when_the_model_is_built():
+    """head sizes and group sizes that a kernel would refuse at the first step are refused by the part's
+    constructor: bfloat16 needs head_dim % 8 == 0 and at most 64 query heads per kv head unless the tensor-core
+    prompt kernel takes the shape; float32 takes them all up to head_dim 256."""
+    import torch
+    from janus_b200.config import resolve_architecture
+    from helpers import TINY_A
+    cpu = torch.device("cpu")
+
+    def build(dtype, **over):
+        cfg = dict(TINY_A, **over)
+        arch = resolve_architecture(cfg)
+        return arch.build(arch.config_class.from_dict(cfg), dtype, cpu)
+
+    build(torch.float32, head_dim=12)
+    with pytest.raises(ValueError, match="multiple of 8"):
+        build(torch.bfloat16, head_dim=12)
+    # 96 query heads on one kv head of 16: no kernel of the bfloat16 prompt path takes that group
+    build(torch.float32, hidden_size=96, num_attention_heads=96, num_key_value_heads=1, head_dim=16)
+    with pytest.raises(ValueError, match="query heads per key/value head"):
+        build(torch.bfloat16, hidden_size=96, num_attention_heads=96, num_key_value_heads=1, head_dim=16)
+    build(torch.bfloat16, hidden_size=64, num_attention_heads=64, num_key_value_heads=1, head_dim=16)
+
+
+def test_layers_share_one_rotary_table_no_longer_than_the_engine_needs():
+    """Every layer names the same position encoding and gets the same object: one table on the device, not one
+    per layer; its rows stop at the engine's longest sequence."""
+    import torch
+    from janus_b200.config import resolve_architecture
+    from helpers import TINY_B
+    cfg = dict(TINY_B, max_position_embeddings=131072)
+    arch = resolve_architecture(cfg)
+    model = arch.build(arch.config_class.from_dict(cfg), torch.float32, torch.device("cpu"))
+    positions = [layer.mixer.position for layer in model.layers]
+    assert len(positions) == 3 and all(p is positions[0] for p in positions)
+    model.limit_positions(200)
+    table = positions[0].fused_rotary_table()
+    assert tuple(table.shape) == (200, 20, 2)
+    assert all(layer.mixer.position.fused_rotary_table() is table for layer in model.layers)
+    # another model with other constants gets a table of its own
+    other_cfg = dict(cfg, rope_theta=10000.0)
+    other = arch.build(arch.config_class.from_dict(other_cfg), torch.float32, torch.device("cpu"))
+    assert other.layers[0].mixer.position is not positions[0]
+
+
+def test_default_stop_tokens():
+    """config.json's eos ids; for a Llama 3 vocabulary without any, the two ids the reference always stops at."""
+    from janus_b200.config import LlamaConfig
+    from helpers import TINY_A, TINY_B
+    assert LlamaConfig.from_dict(TINY_A).stop_token_ids() == (250, 251)
+    assert LlamaConfig.from_dict(TINY_B).stop_token_ids() == (383,)
+    no_eos = {k: v for k, v in TINY_A.items() if k != "eos_token_id"}
+    assert LlamaConfig.from_dict(no_eos).stop_token_ids() == ()
+    assert LlamaConfig.from_dict(dict(no_eos, vocab_size=128256)).stop_token_ids() == (128001, 128009)
+    assert LlamaConfig.from_dict(dict(TINY_A, vocab_size=128256)).stop_token_ids() == (250, 251)

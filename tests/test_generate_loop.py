@@ -207,3 +207,36 @@ def test_any_mix_of_requests_is_served_whole_and_every_slot_comes_back():
                     assert sum(tokens_held(len(prompts[r]), max_new, page) for r in reqs) <= cap
             assert stats.requests == n and stats.prefill_tokens == sum(len(p) for p in prompts)
     check()
+
+
+@pytest.mark.parametrize("fail_in", ["callback", "decode", "prefill"])
+def test_every_slot_comes_back_when_a_batch_ends_in_an_error(fail_in):
+    """A callback that raises, or a step that raises in the middle of a batch, ends the call; no slot
+    stays held, so the next call finds the whole cache again."""
+    script = {r: [r + 1] * 10 for r in range(4)}
+
+    class Failing(ScriptedBackend):
+        def decode(self, slots, last, requests, steps):
+            if fail_in == "decode" and max(steps) >= 2:
+                raise RuntimeError("the step failed")
+            return super().decode(slots, last, requests, steps)
+
+        def prefill(self, slots, prompts, requests):
+            if fail_in == "prefill":
+                raise RuntimeError("the step failed")
+            return super().prefill(slots, prompts, requests)
+
+    def cb(request, token):
+        if fail_in == "callback" and request == 1:
+            raise KeyError("the caller's own fault")
+        return True
+
+    b = Failing(script, 4)
+    with pytest.raises((RuntimeError, KeyError)):
+        run_generation(b, [[1, 2]] * 4, 5, [], 4, 10_000, 1000, 4, 64, cb)
+    assert not b.held and sorted(b.free) == [0, 1, 2, 3]
+    # and the same backend serves the next call
+    ok = ScriptedBackend(script, 4)
+    ok.free, ok.held = b.free, b.held
+    toks, reasons, stats = run_generation(ok, [[1, 2]] * 4, 3, [], 4, 10_000, 1000, 4, 64, None)
+    assert toks == [[r + 1] * 3 for r in range(4)] and not ok.held

@@ -79,6 +79,39 @@ def test_long_prompt_runs_the_pair_products(big_model):
     ops.check_kernel_status(model.device)
 
 
+@pytest.mark.parametrize("switch", ["fused_decode", "qkv_fused", "gemm_pair", "attn_tc"])
+def test_the_documented_switches_select_kernels_that_give_the_same_logits(big_model, monkeypatch, switch):
+    """JANUS_FUSED_DECODE=0, JANUS_QKV_FUSED=0, JANUS_GEMM_PAIR=0 and JANUS_ATTN_TC=0 each take a step through
+    other kernels (rotation and append in a kernel of their own, a plain q/k/v projection, single-CTA
+    products, mma.sync prompt attention); the environment is read at import, so the test turns the same
+    module switches.  A prompt of 600 tokens, then tokens one by one."""
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    from janus_b200.kernels import ops
+    from janus_b200.parts import attention
+    d, ids, ref = big_model
+    if switch == "fused_decode":
+        monkeypatch.setattr(attention, "_FUSED_DECODE", False)
+    elif switch == "qkv_fused":
+        monkeypatch.setattr(ops, "_QKV_FUSED", False)
+    elif switch == "gemm_pair":
+        monkeypatch.setattr(ops, "_GEMM_PAIR", False)
+    else:
+        monkeypatch.setattr(ops, "_ATTN_TC", False)
+    ops.gemm_plan.cache_clear()
+    try:
+        model = janus_b200.load(d, dtype="bfloat16", max_tokens=1024)
+        a = model.alloc_slot()
+        rows = [model.step([StepEntry(a, ids[2][:590], range(590))]).cpu().numpy()]
+        for j in range(590, 600):
+            rows.append(model.step([StepEntry(a, [ids[2][j]], [0])]).cpu().numpy())
+        model.check()
+        assert rel_err(np.concatenate(rows), ref[2]) < tol_for("bfloat16")
+    finally:
+        monkeypatch.undo()
+        ops.gemm_plan.cache_clear()
+
+
 def test_deterministic_mode_gives_the_same_bits_twice(big_model):
     """With the slices of a cut K summed in their fixed order nothing depends on the order of the day: two
     engines built one after the other give bitwise equal logits for a prompt and for decoded tokens."""

@@ -151,7 +151,9 @@ def test_layers_with_and_without_a_window_have_storage_of_their_own(tmp_path, dt
 
 class RunningMeanMixer:
     """Toy mixer with fixed-size state: out_t = scale * mean(x_0 .. x_t) over the
-    sequence so far.  State per sequence: the running sum (H floats) and the count."""
+    sequence so far.  State per sequence: the running sum (H floats) and the count.
+    Device work only, on the current stream, so that a decode step can be recorded
+    into a CUDA graph and replayed."""
 
     def __init__(self, hidden_size, scale, dtype, device):
         self.H, self.scale, self.dtype, self.device = hidden_size, scale, dtype, device
@@ -168,17 +170,19 @@ class RunningMeanMixer:
 
     def forward(self, x, residual, ctx, cache_view, writes_cache=True):
         from janus_b200.kernels import ops
-        state = cache_view.state
-        starts, slots = ctx.q_start.cpu().tolist(), ctx.seq_slot.cpu().tolist()
-        out = torch.empty(x.shape, dtype=torch.float32, device=x.device)
-        for i, slot in enumerate(slots):
-            seg = x[starts[i]:starts[i + 1]].float()
-            csum = torch.cumsum(seg, 0) + state[slot, :self.H]
-            count = state[slot, self.H] + torch.arange(1, seg.shape[0] + 1, device=x.device)
-            out[starts[i]:starts[i + 1]] = self.scale * csum / count[:, None]
-            state[slot, :self.H] = csum[-1]
-            state[slot, self.H] = count[-1]
-        ops.residual_add(residual, out)
+        H, state = self.H, cache_view.state                      # [slots, H + 1]
+        seq = ctx.token_seq.long()                               # sequence of each token
+        slots = ctx.seq_slot.long()
+        starts = ctx.q_start.long()
+        xf = x.float()
+        total = torch.cumsum(xf, 0)
+        before = torch.cat([torch.zeros(1, H, device=x.device), total])[starts[:-1]]    # sum ahead of each sequence
+        prev = state[slots]
+        csum = total - before[seq] + prev[seq, :H]
+        count = prev[seq, H] + (torch.arange(x.shape[0], device=x.device) - starts[:-1][seq] + 1)
+        last = starts[1:] - 1
+        state.index_copy_(0, slots, torch.cat([csum[last], count[last, None]], dim=1))
+        ops.residual_add(residual, (self.scale * csum / count[:, None]).contiguous())
 
 
 def plain_toy_forward(cfg, w, ids, scale):
@@ -195,10 +199,10 @@ def plain_toy_forward(cfg, w, ids, scale):
     return P.linear(P.rms_norm(x, w["model.norm.weight"], eps), P.lm_head_weight(cfg, w))
 
 
-def test_toy_mixer_with_state_registers_builds_and_steps():
+def toy_state_engine(use_graphs):
     from dataclasses import replace
     from janus_b200.config import LlamaConfig
-    from janus_b200.engine import DecoderModel, Engine, EngineOptions, StepEntry
+    from janus_b200.engine import DecoderModel, Engine, EngineOptions
     from janus_b200.models.llama import llama_spec
     from janus_b200.parts import PartSpec, register_part
     from janus_b200.weights import RandomCheckpoint
@@ -214,7 +218,13 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     ck = RandomCheckpoint(model.weight_specs(), seed=8, dtype="float32")
     model.load(ck)
     w = {n: ck.tensor(n) for n in ck.names()}
-    eng = Engine(model, EngineOptions(max_tokens=512, max_slots=2, use_graphs=False))
+    return Engine(model, EngineOptions(max_tokens=512, max_slots=2, use_graphs=use_graphs)), cfg, w
+
+
+@pytest.mark.parametrize("use_graphs", [False, True], ids=["no-graphs", "graphs"])
+def test_toy_mixer_with_state_registers_builds_and_steps(use_graphs):
+    from janus_b200.engine import StepEntry
+    eng, cfg, w = toy_state_engine(use_graphs)
     seqs = [random_tokens(n, 256, 40 + n) for n in (37, 9, 70)]
     ref = [plain_toy_forward(cfg, w, ids, 0.5) for ids in seqs]
     # two sequences together: prompts of unequal length, then one token each
@@ -232,3 +242,27 @@ def test_toy_mixer_with_state_registers_builds_and_steps():
     assert s2 == s1
     d = eng.step([StepEntry(s2, seqs[2], range(70))]).cpu()
     assert rel_err(d, ref[2]) < 1e-4
+
+
+def test_state_is_stepped_once_by_every_decode_step_under_cuda_graphs():
+    """Decode steps replay CUDA graphs; a step that finds no graph (a new batch size, a page capacity that a
+    sequence outgrew) must still advance a mixer's state exactly once.  Two sequences decode token by token
+    from short prompts past position 64 (the page capacity doubles), the shorter one ends on the way (the
+    batch size changes); every row is compared with the plain restatement."""
+    from janus_b200.engine import StepEntry
+    eng, cfg, w = toy_state_engine(True)
+    seqs = [random_tokens(n, 256, 90 + n) for n in (120, 50)]
+    ref = [plain_toy_forward(cfg, w, ids, 0.5) for ids in seqs]
+    s0, s1 = eng.alloc_slot(), eng.alloc_slot()
+    eng.step([StepEntry(s0, seqs[0][:20], ()), StepEntry(s1, seqs[1][:7], ())])
+    pos = [20, 7]
+    captures = eng.graph_captures
+    while pos[0] < len(seqs[0]):
+        live = [i for i in (0, 1) if pos[i] < len(seqs[i])]
+        out = eng.step([StepEntry((s0, s1)[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu()
+        for row, i in enumerate(live):
+            err = rel_err(out[row:row + 1], ref[i][pos[i]:pos[i] + 1])
+            assert err < 1e-4, f"sequence {i} at position {pos[i]}: {err}"
+            pos[i] += 1
+    # batch of two at capacity 1, then one sequence at capacities 1 and 2
+    assert eng.graph_captures - captures >= 3

@@ -20,9 +20,10 @@ def plain_logits():
     return {}
 
 
+@pytest.mark.parametrize("graphs", [True, False], ids=["graphs", "no-graphs"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["A", "B"])
-def test_replay_matches_plain_however_the_tokens_are_cut(tmp_path, name, dtype):
+def test_replay_matches_plain_however_the_tokens_are_cut(tmp_path, name, dtype, graphs):
     cfg = TINY[name]
     model_dir = make_model_dir(cfg, str(tmp_path / "model"), seed={"A": 0, "B": 1}[name], dtype=dtype)
     pcfg, pw = P.read_model_dir(model_dir)
@@ -30,7 +31,7 @@ def test_replay_matches_plain_however_the_tokens_are_cut(tmp_path, name, dtype):
     ref = {rid: P.forward(pcfg, pw, ids).numpy() for rid, ids in reqs.items()}
     tol = tol_for(dtype)
     # room for 5 pages: two batches cannot be live at once, so pages and slots are used again
-    run = TraceRun(model_dir, dtype, str(tmp_path / "out"), max_tokens=320)
+    run = TraceRun(model_dir, dtype, str(tmp_path / "out"), max_tokens=320, graphs=graphs)
     try:
         # 1. each request alone and whole
         for rid, ids in reqs.items():

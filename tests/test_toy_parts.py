@@ -164,3 +164,125 @@ def test_toy_routing_and_toy_positions_register_build_and_step(dtype, routed):
     s2 = eng.alloc_slot()
     d = eng.step([StepEntry(s2, seqs[2], range(75))]).cpu()
     assert rel_err(d, ref[2]) < tol
+
+
+# ---------------------------------------------------------------- layers of another make
+class ToySandwichBlock:
+    """A toy arrangement with a part of its own: the mixer's output is normed once more before it joins the
+    residual stream (h1 = x + post(mixer(pre(x)))), and the layer has no feed-forward at all.  The mixer adds
+    into whatever float32 buffer it is handed, so it is handed a cleared one."""
+
+    def __init__(self, parts, hidden_size, dtype):
+        self.pre, self.mixer, self.post = parts["mixer_norm"], parts["mixer"], parts["post_mixer_norm"]
+        assert "feed_forward" not in parts
+        self.H, self.dtype = hidden_size, dtype
+
+    def forward(self, residual, ctx, cache_view, writes_cache=True):
+        from janus_b200.kernels import ops
+        T = residual.shape[0]
+        x = ctx.workspace.get("normed", (T, self.H), self.dtype)
+        branch = ctx.workspace.get("toy_branch", (T, self.H), torch.float32)
+        y = ctx.workspace.get("toy_branch_normed", (T, self.H), self.dtype)
+        self.pre.forward(residual, x)
+        branch.zero_()
+        self.mixer.forward(x, branch, ctx, cache_view, writes_cache)
+        self.post.forward(branch, y)
+        ops.residual_add(residual, y)
+
+
+class ToyScale:
+    """A transform of a whole tensor in place: t *= factor (an embedding multiplier)."""
+
+    def __init__(self, factor, dtype, device):
+        self.factor = factor
+
+    def weight_shapes(self):
+        return {}
+
+    def load(self):
+        pass
+
+    def forward(self, t, ctx):
+        t.mul_(self.factor)
+
+
+class ToySoftCap(ToyScale):
+    """logits = cap * tanh(logits / cap)"""
+
+    def forward(self, t, ctx):
+        t.copy_(self.factor * torch.tanh(t / self.factor))
+
+
+def plain_other_layers(cfg, w, ids, scale, cap):
+    """Embedding times `scale`; layer 0: x + post_norm(attention(pre_norm(x))), no feed-forward; layer 1 as the
+    architecture has it; logits soft-capped at `cap`."""
+    eps = P.cfg_get(cfg, "rms_norm_eps")
+    pos = torch.arange(len(ids))
+    x = P.embed(w["model.embed_tokens.weight"], torch.tensor(ids)) * scale
+    a, _ = P.attention_block(P.rms_norm(x, w["model.layers.0.input_layernorm.weight"], eps), pos, cfg, w, 0)
+    x = x + P.rms_norm(a, w["toy.post_mixer_norm.weight"], eps)
+    x, _ = P.decoder_block(x, pos, cfg, w, 1)
+    logits = P.linear(P.rms_norm(x, w["model.norm.weight"], eps), P.lm_head_weight(cfg, w))
+    return cap * torch.tanh(logits / cap)
+
+
+@pytest.mark.parametrize("use_graphs", [False, True], ids=["no-graphs", "graphs"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_layer_without_feed_forward_an_arrangement_with_a_part_of_its_own_and_transforms(dtype, use_graphs):
+    """What a layer consists of is data too: a layer may leave the feed-forward out, an arrangement registered
+    from here takes a further norm by a role of its own, and transforms registered from here scale the
+    embedding and cap the logits; the library's files stay as they are."""
+    from janus_b200.config import LlamaConfig
+    from janus_b200.engine import DecoderModel, Engine, EngineOptions, StepEntry
+    from janus_b200.models.llama import llama_spec
+    from janus_b200.parts import LayerSpec, PartSpec, register_part
+    from janus_b200.weights import RandomCheckpoint
+
+    register_part("arrangement", "toy_sandwich", ToySandwichBlock)
+    register_part("transform", "toy_scale", ToyScale)
+    register_part("transform", "toy_soft_cap", ToySoftCap)
+    cfg = TINY["A"]
+    scale, cap = 3.0, 0.4          # logits reach about 0.55: the cap bends them without flattening them
+    base = llama_spec(LlamaConfig.from_dict(cfg))
+    l0 = base.layers[0]
+    post = PartSpec("rms_norm", dict(l0.mixer_norm.params), weights=dict(gamma="toy.post_mixer_norm.weight"))
+    layer0 = LayerSpec(mixer=l0.mixer, mixer_norm=l0.mixer_norm, arrangement="toy_sandwich",
+                       extra=(("post_mixer_norm", "norm", post),))
+    spec = replace(base, layers=(layer0, base.layers[1]),
+                   embedding_transforms=(PartSpec("toy_scale", dict(factor=scale)),),
+                   logit_transforms=(PartSpec("toy_soft_cap", dict(factor=cap)),))
+    model = DecoderModel(spec, getattr(torch, dtype), torch.device(DEV))
+    names = [s.name for s in model.weight_specs()]
+    assert "toy.post_mixer_norm.weight" in names and not any("layers.0.mlp" in n for n in names)
+    assert not any("layers.0.post_attention_layernorm" in n for n in names)
+    ck = RandomCheckpoint(model.weight_specs(), seed=12, dtype=dtype, norm_std=0.02)
+    model.load(ck)
+    w = {n: ck.tensor(n).float() for n in ck.names()}
+    eng = Engine(model, EngineOptions(max_tokens=512, max_slots=2, use_graphs=use_graphs))
+    seqs = [random_tokens(n, cfg["vocab_size"], 30 + n) for n in (80, 21)]
+    ref = [plain_other_layers(cfg, w, ids, scale, cap) for ids in seqs]
+    tol = tol_for(dtype)
+    s0, s1 = eng.alloc_slot(), eng.alloc_slot()
+    a = eng.step([StepEntry(s0, seqs[0][:50], range(50)), StepEntry(s1, seqs[1][:9], range(9))]).cpu()
+    assert rel_err(a[:50], ref[0][:50]) < tol and rel_err(a[50:], ref[1][:9]) < tol
+    for j in range(30):                                  # past position 64; the shorter sequence ends on the way
+        entries = [StepEntry(s0, [seqs[0][50 + j]], [0])]
+        if 9 + j < len(seqs[1]):
+            entries.append(StepEntry(s1, [seqs[1][9 + j]], [0]))
+        b = eng.step(entries).cpu()
+        assert rel_err(b[0:1], ref[0][50 + j:51 + j]) < tol, f"position {50 + j}"
+        if len(entries) == 2:
+            assert rel_err(b[1:2], ref[1][9 + j:10 + j]) < tol
+
+
+def test_an_arrangement_is_told_which_part_it_lacks():
+    from janus_b200.config import LlamaConfig
+    from janus_b200.engine import DecoderModel
+    from janus_b200.models.llama import llama_spec
+    from janus_b200.parts import LayerSpec
+    base = llama_spec(LlamaConfig.from_dict(TINY["A"]))
+    l0 = base.layers[0]
+    with pytest.raises(ValueError, match="feed_forward_norm"):
+        DecoderModel(replace(base, layers=(LayerSpec(mixer=l0.mixer, mixer_norm=l0.mixer_norm,
+                                                     feed_forward=l0.feed_forward), base.layers[1])),
+                     torch.float32, torch.device(DEV))

@@ -94,6 +94,13 @@ def test_kept_dtypes(tmp_path):
     assert named["m"].dtype == torch.bfloat16      # 16-bit floats are kept in bfloat16
     assert named["n"].dtype == torch.float32       # stored in 32-bit stays so
     assert named["t"].dtype == torch.int32         # integer tables as int32
+    # the float32 engine widens a float16 tensor exactly: no rounding to bfloat16 on the way
+    wide = load_named(FolderCheckpoint(str(tmp_path)), specs, engine_dtype=torch.float32)
+    stored = FolderCheckpoint(str(tmp_path)).tensor("m")
+    assert stored.dtype == torch.float16 and wide["m"].dtype == torch.float32
+    assert torch.equal(wide["m"], stored.float())
+    assert not torch.equal(named["m"].float(), stored.float())
+    assert wide["t"].dtype == torch.int32
 
 
 @pytest.mark.parametrize("cfg, dtype", [(TINY_A, "float32"), (TINY_B, "bfloat16")])
@@ -123,3 +130,72 @@ def test_random_tensor_does_not_depend_on_other_tensors():
     s2 = [TensorSpec("y", (4,), "ones"), TensorSpec("z", (2, 2)), TensorSpec("x", (8, 8))]
     a, b = RandomCheckpoint(s1, 7, "float32"), RandomCheckpoint(s2, 7, "float32")
     assert torch.equal(a.tensor("x"), b.tensor("x")) and torch.equal(a.tensor("y"), b.tensor("y"))
+
+
+def test_sharded_folder(tmp_path):
+    """Shards named by model.safetensors.index.json read as one checkpoint; a shard that is missing, an
+    index that is none and a tensor stored twice are weight errors."""
+    from helpers import make_model_dir
+    arch = resolve_architecture(TINY_B)
+    specs = arch.weight_specs(LlamaConfig.from_dict(TINY_B))
+    one = make_model_dir(TINY_B, str(tmp_path / "one"), seed=4, dtype="bfloat16")
+    three = make_model_dir(TINY_B, str(tmp_path / "three"), seed=4, dtype="bfloat16", shards=3)
+    files = sorted(os.listdir(three))
+    assert "model.safetensors" not in files and len([f for f in files if f.endswith(".safetensors")]) == 3
+    a, b = FolderCheckpoint(one), FolderCheckpoint(three)
+    check_names(b, specs)
+    assert sorted(a.names()) == sorted(b.names())
+    for n in a.names():
+        assert torch.equal(a.tensor(n), b.tensor(n)) and a.shape(n) == b.shape(n) and a.dtype(n) == b.dtype(n)
+    # a tensor that two shards store
+    twice = os.path.join(three, files[1])
+    dup = SafetensorsFile(os.path.join(three, files[2]))
+    name = dup.names()[0]
+    extra = SafetensorsFile(twice)
+    save_file(dict({n: extra.tensor(n).clone() for n in extra.names()}, **{name: dup.tensor(name).clone()}),
+              str(tmp_path / "dup.safetensors"))
+    del extra, dup
+    os.replace(str(tmp_path / "dup.safetensors"), twice)
+    with pytest.raises(WeightError, match="stored twice"):
+        FolderCheckpoint(three)
+    # a shard that is not there
+    os.remove(twice)
+    with pytest.raises(WeightError, match="cannot open"):
+        FolderCheckpoint(three)
+    # an index that is none
+    with open(os.path.join(three, "model.safetensors.index.json"), "w") as f:
+        f.write('{"metadata": {}}')
+    with pytest.raises(WeightError, match="no shard index"):
+        FolderCheckpoint(three)
+
+
+def test_random_values_are_a_function_of_seed_name_and_index():
+    """The generator against its definition in plain integers: element i is the sum of twelve 16-bit pieces of
+    three splitmix64 values of key + (3 i + d + 1) * golden, centred and scaled by 2^-16.  Chunks and the order
+    of creation change nothing."""
+    from janus_b200.weights.random_init import standard_normal, tensor_key
+    M = (1 << 64) - 1
+
+    def mix(x):
+        x = ((x ^ (x >> 30)) * 0xBF58476D1CE4E5B9) & M
+        x = ((x ^ (x >> 27)) * 0x94D049BB133111EB) & M
+        return x ^ (x >> 31)
+
+    def element(key, i):
+        total = 0
+        for d in range(3):
+            h = mix((key + (3 * i + d + 1) * 0x9E3779B97F4A7C15) & M)
+            total += sum((h >> s) & 0xFFFF for s in (0, 16, 32, 48))
+        return (total - 6 * 65535) / 65536.0
+
+    key = tensor_key(7, "model.layers.0.mlp.up_proj.weight")
+    assert key == tensor_key(7, "model.layers.0.mlp.up_proj.weight") != tensor_key(8, "model.layers.0.mlp.up_proj.weight")
+    z = standard_normal(key, 0, 1000, "cpu")
+    assert z.dtype == torch.float32
+    for i in (0, 1, 2, 499, 999):
+        assert float(z[i]) == element(key, i)
+    assert torch.equal(standard_normal(key, 990, 10, "cpu"), z[990:])
+    big = standard_normal(key, 0, 1 << 18, "cpu")
+    assert abs(float(big.mean())) < 0.01 and abs(float(big.std()) - 1.0) < 0.01
+    ck = RandomCheckpoint([TensorSpec("model.layers.0.mlp.up_proj.weight", (20, 50))], 7, "float32", std=0.5)
+    assert torch.equal(ck.tensor("model.layers.0.mlp.up_proj.weight").view(-1), z * 0.5)

@@ -8,9 +8,14 @@ scratch (the splits' partial outputs, maxima and sums) in a fixed 4 MiB array
 inside the library.  This test calls the exported C symbol directly, twice in a
 row with different inputs (the array keeps the first call's contents, which must
 not leak into the second), and compares each result with the ordinary entry
-point that takes caller-provided scratch.  It also checks that a call too large
-for the array is refused.  The file sorts last so that a run which stops at
-the first failure has already run every other test.
+point that takes caller-provided scratch: both launch the same kernels with the
+same splits, so the results must be equal bit for bit.  It also checks that a
+call too large for the array is refused, and that a call with one split, which
+uses no scratch, is taken at any size.  The ordinary entry point runs first, so
+the library (and with it the array, which is part of the loaded module and is
+no allocation of any call) is on the device before free memory is compared.
+The file sorts last so that a run which stops at the first failure has already
+run every other test.
 """
 import ctypes
 import math
@@ -43,11 +48,11 @@ def _ptr(t):
     return ctypes.c_void_p(t.data_ptr())
 
 
-def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
+@pytest.mark.parametrize("nh, nkv, hd, n_splits", [(8, 2, 64, 4), (32, 8, 128, 3)])
+def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row(nh, nkv, hd, n_splits):
     from janus_b200.kernels import ops
     from janus_b200.kernels.build import ensure_built
 
-    nh, nkv, hd, n_splits = 8, 2, 64, 4
     lib = ctypes.CDLL(str(ensure_built("attention_bf16", {"JB_HEAD_DIM": hd})))
     fn = lib.jb_attention_bf16_decode_noalloc
     fn.restype = ctypes.c_int
@@ -71,8 +76,7 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
         assert code == 0, f"call {call} returned {code}"
         assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the free device memory"
         assert torch.isfinite(got.float()).all()
-        err = float((got.float() - want.float()).abs().max() / want.float().abs().max())
-        assert err < 1.5e-2, f"call {call}: relative error {err}"
+        assert torch.equal(got, want), f"call {call}: the two entry points differ"
 
     # a call that needs more scratch than the array holds is refused, nothing is launched
     n_seqs = SCRATCH_FLOATS // (nh * n_splits * (hd + 2)) + 1
@@ -82,3 +86,10 @@ def test_noalloc_entry_point_matches_the_ordinary_one_twice_in_a_row():
               bt.shape[1], 0, ctypes.c_float(scale), n_splits, stream)
     torch.cuda.synchronize()
     assert code == 10001 and float(out.float().abs().sum()) == 0.0
+    # the same batch with one split needs no scratch: it is taken and matches the ordinary entry point
+    want = torch.empty_like(q)
+    ops.attention_bf16_decode(q, kc, vc, want, bt, kv_len, nh, nkv, hd, PAGE, 0, scale, Scratch(), 3, n_splits=1)
+    code = fn(_ptr(q), _ptr(kc), _ptr(vc), _ptr(out), _ptr(bt), _ptr(kv_len), n_seqs, nh, nkv, hd, PAGE,
+              bt.shape[1], 0, ctypes.c_float(scale), 1, stream)
+    torch.cuda.synchronize()
+    assert code == 0 and torch.equal(out, want)
