@@ -452,6 +452,10 @@ def _defines_from_env(name: str) -> dict:
     return {k.strip(): int(v) for k, v in (item.split("=") for item in text.split(",") if item.strip())}
 
 
+def _defines_key(defines: Optional[dict]):
+    return tuple(sorted(defines.items())) if defines else None
+
+
 _GEMM_DEFINES = _defines_from_env("JANUS_GEMM_DEFINES") or None
 _PAIR_DEFINES = _defines_from_env("JANUS_GEMM_PAIR_DEFINES") or None
 _ATTN_TC_DEFINES = _defines_from_env("JANUS_ATTN_TC_DEFINES")
@@ -498,7 +502,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     elif pair is None:
         pair = False
     if pair:
-        _check(_lib("gemm_bf16_tc2", None, _PAIR_DEFINES).jb_gemm_bf16_pair(
+        _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair(
             _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
             int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
@@ -514,7 +518,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
             split_k = 1          # too much scratch: K whole
         else:
             partials, tickets = scratch
-    _check(_lib("gemm_bf16_tc", None, _GEMM_DEFINES).jb_gemm_bf16(
+    _check(_lib("gemm_bf16_tc", _defines_key(_GEMM_DEFINES), _GEMM_DEFINES).jb_gemm_bf16(
         _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
         int(split_k), _ptr(partials), ctypes.c_longlong(0 if partials is None else partials.numel()), _ptr(tickets),
         0 if tickets is None else tickets.numel(), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
@@ -549,7 +553,7 @@ def gemm_qkv_rope_cache(x: torch.Tensor, w: PackedWeight, q_out: torch.Tensor, c
     _need(v_cache, "v cache", torch.bfloat16)
     if k_cache.shape[1:] != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
         raise KernelError(f"qkv: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
-    _check(_lib("gemm_bf16_tc2", None, _PAIR_DEFINES).jb_gemm_bf16_pair_qkv_rope(
+    _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair_qkv_rope(
         _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
         _ptr(cos_sin), _ptr(positions), _ptr(dest),
         nh, nkv, hd, page_size, _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair_qkv_rope")

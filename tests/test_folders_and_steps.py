@@ -92,3 +92,28 @@ def test_a_step_that_mixes_a_prompt_chunk_with_single_tokens(tmp_path, name, dty
     assert rel_err(out[0:1], ref[0][85:86]) < tol and rel_err(out[1:2], ref[1][13:14]) < tol
     assert rel_err(out[2:3], ref[2][67:68]) < tol
     model.check()
+
+
+def test_a_one_layer_model_decodes_many_steps_right():
+    """With one layer only about ten kernels lie between the step that writes a cached row and the step that
+    reads it, all launched with programmatic dependent launch; decode attention asks for cached pages before
+    its dependency wait.  What orders the two steps is the copy of each step's index buffer at the step's
+    start.  A hundred decode steps from a short prompt, across a page boundary, every row against plain."""
+    import os
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    assert os.environ.get("JANUS_PDL", "1") != "0"
+    cfg = dict(TINY["A"], num_hidden_layers=1)
+    import tempfile
+    with tempfile.TemporaryDirectory() as tmp:
+        d = make_model_dir(cfg, os.path.join(tmp, "m"), seed=24, dtype="bfloat16")
+        pcfg, pw = P.read_model_dir(d)
+        model = janus_b200.load(d, dtype="bfloat16", max_tokens=256)
+    ids = random_tokens(120, cfg["vocab_size"], 8)
+    ref = P.forward(pcfg, pw, ids).numpy()
+    s = model.alloc_slot()
+    model.step([StepEntry(s, ids[:20], ())])
+    rows = [model.step([StepEntry(s, [ids[j]], [0])]) for j in range(20, 120)]      # no host read in between
+    got = torch.cat(rows).cpu().numpy()
+    model.check()
+    assert rel_err(got, ref[20:]) < tol_for("bfloat16")

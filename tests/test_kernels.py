@@ -518,6 +518,28 @@ def test_kernels_write_nothing_outside_their_outputs(ops, T):
     ops.check_kernel_status(torch.device(DEV))
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable(ops, monkeypatch):
+    """Every wait of the tensor-core kernels on an mbarrier has a time limit.  A build for this test alone has
+    a limit of 3 ms and a producer warp that asks for no tile at all, so nothing is in flight: the MMA warp's
+    and the epilogue's waits run out, the kernel records who gave up, frees its TMEM and returns.  The host
+    reads the status word as a `KernelError`, the word is cleared, and an ordinary product afterwards is right."""
+    dev = torch.device(DEV)
+    ops.check_kernel_status(dev)
+    x, w = bf16_inputs(8, 128, 64, 3)
+    packed = ops.pack_weight(w)
+    y = torch.zeros(8, 128, device=DEV)
+    monkeypatch.setattr(ops, "_GEMM_DEFINES", {"JB_WAIT_LIMIT_NS": 3000000, "JB_TEST_NO_LOADS": 1})
+    ops.gemm_bf16(x, packed, y, mode="store", pair=False)          # one tile, one CTA; returns after about 6 ms
+    with pytest.raises(ops.KernelError, match="timed out waiting on an mbarrier"):
+        ops.check_kernel_status(dev)
+    monkeypatch.undo()
+    ops.check_kernel_status(dev)                                    # the word was cleared
+    assert int(ops.kernel_status(dev).item()) == 0
+    ops.gemm_bf16(x, packed, y, mode="store", pair=False)
+    close(y, x.double().cpu() @ w.double().cpu().T, 2e-5)
+    ops.check_kernel_status(dev)
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take(ops):
     w = torch.zeros(16, 100, device=DEV, dtype=torch.bfloat16)       # K = 100 is not a multiple of 8
     with pytest.raises(Exception, match="multiple of 8"):
