@@ -1,7 +1,8 @@
 // Causal grouped-query flash attention for prefill on the 5th-generation tensor
 // cores (tcgen05) of sm_100a, over the paged cache.  Built for one head size
-// (-DJB_HEAD_DIM = 64 or 128); other head sizes and group sizes that are no
-// power of two take the mma.sync kernel of attention_bf16.cu.
+// (-DJB_HEAD_DIM = 64 or 128) and any number of query heads per kv head up to 128: a tile holds
+// floor(128 / G) tokens x G heads, and the rows left over (2 of 128 with 3, 6 or 7 heads per kv head)
+// belong to no token.  Other head sizes take the mma.sync kernel of attention_bf16.cu.
 //
 // Two kernels.  prefill_tc_kernel: one CTA owns a tile of 128 rows = (token, query head of one kv group)
 // pairs of one sequence and walks its causal range of 64-key pages:
@@ -339,7 +340,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   if (active && warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(q_full, NT * Q_BYTES);
+      mbar_expect_tx(q_full, NT * NH64 * tpt * G * 128);   // the box holds tpt tokens x G heads: its bytes, not the tile's
       for (int w = 0; w < NT; ++w)   // a tile past the sequence's end reads rows that no one uses (or zeros past the tensor)
         for (int h = 0; h < NH64; ++h)
           tma_load_4d(q_s + w * Q_BYTES + h * BM * 128, &map_q, q_full, h * 64, 0, kvh, qs + tok_first + w * tpt);
@@ -405,7 +406,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const int quarter = warp & 3;              // the 32 TMEM lanes this warp may touch
     const int row = quarter * 32 + lane;
     const int tl = w * tpt + row / G;          // token within the pair
-    const bool valid = tl < n_tok_all;
+    const bool valid = row < tpt * G && tl < n_tok_all;   // rows past tpt * G belong to no token
     const int row_pos = valid ? pos_first + tl : -1;
     const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
@@ -577,7 +578,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
   if (active && warp == 0) {
     // ---------------- producer ----------------
     if (lane == 0) {
-      mbar_expect_tx(q_full, 2 * Q_BYTES);
+      mbar_expect_tx(q_full, 2 * NH64 * tpt * G * 128);   // the box holds tpt tokens x G heads: its bytes, not the tile's
       for (int w = 0; w < 2; ++w)
         for (int h = 0; h < NH64; ++h)
           tma_load_4d(q_s + w * Q_BYTES + h * BM * 128, &map_q, q_full, h * 64, 0, kvh, qs + tok_first + w * tpt);
@@ -647,7 +648,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     const int quarter = warp & 3;
     const int row = quarter * 32 + lane;
     const int tl = w * tpt + row / G;
-    const bool valid = tl < n_tok_all;
+    const bool valid = row < tpt * G && tl < n_tok_all;   // rows past tpt * G belong to no token
     const int row_pos = valid ? pos_first + tl : -1;
     const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
@@ -754,7 +755,7 @@ EncodeTiledFn encode_fn() {
 
 JB_EXPORT int jb_attention_tc_head_dim() { return HD; }
 
-// q, out: [T, nh * hd] bf16; caches: [n_pages, nkv, 64, hd] bf16.  Needs nh / nkv a power of two <= 128.
+// q, out: [T, nh * hd] bf16; caches: [n_pages, nkv, 64, hd] bf16.  Needs nh / nkv <= 128.
 JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* block_table, const int* q_start, const int* kv_len, int T,
                                       int n_pages, int n_seqs, int max_q_len, int nh, int nkv, int hd,
@@ -765,7 +766,7 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
   JB_REFUSE(page_size != PAGE, "attention_tc: page size %d (need %d)", page_size, PAGE);
   JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
   const int G = nh / nkv;
-  JB_REFUSE(G > BM || (G & (G - 1)) != 0, "attention_tc: %d query heads per kv head is no power of two <= %d", G, BM);
+  JB_REFUSE(G > BM, "attention_tc: %d query heads per kv head are more than %d", G, BM);
   JB_REFUSE(((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15, "attention_tc: operands must be 16-byte aligned");
   EncodeTiledFn enc = encode_fn();
   if (!enc) return JB_ERR_TENSORMAP;

@@ -681,11 +681,10 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
         ctypes.c_float(scale), int(n_splits), int(write_kv), _stream()), "attention_bf16_decode_fused", kernels=kernels)
 
 
-# -- tcgen05 prefill attention (head sizes 64 and 128, power-of-two groups) ------------------
+# -- tcgen05 prefill attention (head sizes 64 and 128, up to 128 query heads per kv head) ------------------
 def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
     g = nh // max(nkv, 1)
-    return (_ATTN_TC and hd in (64, 128) and nkv > 0 and nh % nkv == 0
-            and g <= 128 and (g & (g - 1)) == 0)
+    return _ATTN_TC and hd in (64, 128) and nkv > 0 and nh % nkv == 0 and g <= 128
 
 
 def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,

@@ -229,7 +229,10 @@ def test_attention_bf16_prefill(ops, nh, nkv, hd, window):
 
 @pytest.mark.parametrize("tiles", ["1", "2"])
 @pytest.mark.parametrize("nh, nkv, hd, window", [(32, 8, 128, 0), (8, 1, 64, 100), (4, 4, 128, 0), (16, 2, 128, 70),
-                                                 (2, 1, 64, 0), (64, 1, 128, 0)])
+                                                 (2, 1, 64, 0), (64, 1, 128, 0),
+                                                 # groups that do not divide the 128 rows of a tile: 3, 5, 6, 7, 100
+                                                 (24, 8, 128, 0), (10, 2, 128, 90), (6, 1, 64, 50), (12, 4, 64, 0),
+                                                 (7, 1, 128, 0), (100, 1, 64, 0)])
 def test_attention_tc_prefill(ops, nh, nkv, hd, window, tiles, monkeypatch):
     """The tcgen05 kernel against the plain attention: ragged batch, chunked prompts
     (queries are the last q_len positions), a far key that stands out; the one-tile kernel and the
