@@ -212,6 +212,7 @@ def run_ours(args):
                    frac_of_sustained=round(flops / (prefill_ms * 1e-3) / (pk["bf16_tflops_sustained"] * 1e12), 4))
 
     # ---- decode at each batch size ----------------------------------------------
+    torch.cuda.profiler.start()          # for `ncu --profile-from-start off`: the decode steps from here on
     results, launches = {}, {}
     clocks = None
     for B in batches:
@@ -349,10 +350,12 @@ def run_workload(name):
                                    max_slots=w["batch"], max_seq_len=w["context"], norm_std=0.0)
     model.generate([p[:32] for p in prompts[:w["batch"]]], max_tokens=4, ignore_eos=True)      # warm-up
     torch.cuda.synchronize()
+    torch.cuda.profiler.start()          # for `ncu --profile-from-start off`: nothing before this is captured
     t0 = time.perf_counter()
     out, stats = model.generate(prompts, max_tokens=w["max_new"], ignore_eos=True)
     torch.cuda.synchronize()
     wall = time.perf_counter() - t0
+    torch.cuda.profiler.stop()
     new_tokens = sum(len(o) for o in out)
     # what the decode steps had to read: every weight once per step, and the cached keys and values of the
     # sequences that were live at the step (request r's j-th decode step reads prompt + j tokens)
