@@ -100,6 +100,7 @@ class Engine:
         self._pinned: Optional[torch.Tensor] = None
         self._graphs: Dict[Tuple, object] = {}
         self._capture_stream: Optional[torch.cuda.Stream] = None
+        self._checked_shapes = set()       # shapes of steps that have run with the kernel faces' checks on
         self.graph_captures = 0            # decode steps that found no captured graph and recorded one
         # logits and sampled tokens of graph steps: one buffer for all graphs (a graph records a view)
         self._graph_logits: Optional[torch.Tensor] = None
@@ -254,7 +255,17 @@ class Engine:
             logits = torch.empty((want_rows.shape[0], self.model.vocab_size), dtype=torch.float32,
                                  device=self.device)
             before = ops.launch_count()
-            self.model.forward(ctx, want_rows, logits)
+            # a step of a shape that has run before hands the same kinds of tensors to the same kernels:
+            # the faces' checks of device, dtype and shape are made the first time only
+            shape = (ctx.n_tokens, ctx.n_seqs, ctx.max_q_len, ctx.max_kv_len_bound, want_rows.shape[0])
+            if shape in self._checked_shapes:
+                with ops.unchecked():
+                    self.model.forward(ctx, want_rows, logits)
+            else:
+                self.model.forward(ctx, want_rows, logits)
+                if len(self._checked_shapes) >= 4096:
+                    self._checked_shapes.clear()
+                self._checked_shapes.add(shape)
             self.last_graph_launches = ops.launch_count() - before
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
@@ -323,7 +334,7 @@ class Engine:
                     self._capture_stream = torch.cuda.Stream(device=self.device)
                 side = self._capture_stream
                 side.wait_stream(torch.cuda.current_stream(self.device))
-                with torch.cuda.stream(side):
+                with torch.cuda.stream(side), ops.unchecked():      # the direct run above made the checks
                     graph.capture_begin()
                     try:
                         rec.run_forward()

@@ -32,9 +32,9 @@ def dtype_code(dtype: torch.dtype) -> int:
 _scope_stream = [None]
 
 
-def _stream() -> ctypes.c_void_p:
+def _stream() -> int:
     s = _scope_stream[0]
-    return s if s is not None else ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    return s if s is not None else torch.cuda.current_stream().cuda_stream
 
 
 @contextlib.contextmanager
@@ -42,12 +42,30 @@ def stream_scope():
     """Within the scope every launch goes to the stream that was current on entry: the question is asked
     once for a whole forward pass instead of once per kernel."""
     before = _scope_stream[0]
-    _scope_stream[0] = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    _scope_stream[0] = torch.cuda.current_stream().cuda_stream
     try:
         yield
     finally:
         _scope_stream[0] = before
 
+
+# Argument types of the exported C functions: p pointer, i int, l long long, u unsigned long long, f float;
+# the last argument of every function is the stream.  Declared once per library, so that a launch passes
+# plain Python integers and floats (a pointer is `tensor.data_ptr()`, None is a null pointer).
+_SIGNATURES = {
+    "jb_embed_gather": "pippiippp", "jb_rmsnorm": "pppifpiiiplp", "jb_residual_add": "ppilp",
+    "jb_swiglu": "ppiiip", "jb_swiglu_f32_to_bf16": "piipiip", "jb_zero_f32": "plp",
+    "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
+    "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiifp",
+    "jb_gemm_bf16": "pplipiiiiiiplpipp", "jb_gemm_bf16_pair": "pplipiiiiiipp",
+    "jb_gemm_bf16_pair_qkv_rope": "ppliippppppiiiipp",
+    "jb_sample": "piipfiffppupppp",
+    "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
+    "jb_attention_bf16_decode_fused": "pipppppppppiiiiiiifiip",
+    "jb_attention_tc_prefill": "pppppppiiiiiiiiiifpp",
+}
+_CTYPES = {"p": ctypes.c_void_p, "i": ctypes.c_int, "l": ctypes.c_longlong, "u": ctypes.c_ulonglong,
+           "f": ctypes.c_float}
 
 _libs = {}
 
@@ -57,15 +75,39 @@ def _lib(stem: str, key=None, defines=None) -> ctypes.CDLL:
     asked for on every launch, so the answer is remembered here."""
     lib = _libs.get((stem, key))
     if lib is None:
-        lib = _libs[(stem, key)] = library(stem, defines(key) if callable(defines) else defines)
+        lib = library(stem, defines(key) if callable(defines) else defines)
+        for name, signature in _SIGNATURES.items():
+            fn = getattr(lib, name, None)
+            if fn is not None:
+                fn.argtypes = [_CTYPES[c] for c in signature]
+                fn.restype = ctypes.c_int
+        _libs[(stem, key)] = lib
     return lib
 
 
-def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
-    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+def _ptr(t: Optional[torch.Tensor]) -> Optional[int]:
+    return None if t is None else t.data_ptr()
+
+
+# Whether the faces below check their tensors (device, contiguity, dtype, shape).  The engine turns the
+# checks off for a step whose shape it has run before with the checks on: the same parts then hand the same
+# kinds of tensors to the same kernels.
+_checks = [True]
+
+
+@contextlib.contextmanager
+def unchecked():
+    before = _checks[0]
+    _checks[0] = False
+    try:
+        yield
+    finally:
+        _checks[0] = before
 
 
 def _need(t: torch.Tensor, name: str, dtype=None, shape=None) -> None:
+    if not _checks[0]:
+        return
     if not t.is_cuda:
         raise KernelError(f"{name}: tensor must be on a CUDA device (there is no CPU path)")
     if not t.is_contiguous():
@@ -127,8 +169,8 @@ def rmsnorm(x: torch.Tensor, gamma: torch.Tensor, eps: float, out: torch.Tensor,
     elif x.shape[0] < rows:
         raise KernelError("rmsnorm: fewer input rows than output rows")
     _check(_lib("elementwise").jb_rmsnorm(
-        _ptr(x), _ptr(row_index), _ptr(gamma), dtype_code(gamma.dtype), ctypes.c_float(eps), _ptr(out),
-        dtype_code(out.dtype), rows, H, _ptr(clear), ctypes.c_longlong(0 if clear is None else clear.numel()),
+        _ptr(x), _ptr(row_index), _ptr(gamma), dtype_code(gamma.dtype), eps, _ptr(out),
+        dtype_code(out.dtype), rows, H, _ptr(clear), 0 if clear is None else clear.numel(),
         _stream()), "rmsnorm")
 
 
@@ -137,7 +179,7 @@ def residual_add(residual: torch.Tensor, delta: torch.Tensor) -> None:
     _need(residual, "residual", torch.float32)
     _need(delta, "delta", None, residual.shape)
     _check(_lib("elementwise").jb_residual_add(
-        _ptr(residual), _ptr(delta), dtype_code(delta.dtype), ctypes.c_longlong(residual.numel()), _stream()),
+        _ptr(residual), _ptr(delta), dtype_code(delta.dtype), residual.numel(), _stream()),
         "residual_add")
 
 
@@ -164,7 +206,7 @@ def swiglu_f32_to_bf16(gate_up: torch.Tensor, out: torch.Tensor, up_col: int) ->
 def zero_f32(t: torch.Tensor) -> None:
     """Fill a float32 tensor with zeros (whole 16-byte vectors)."""
     _need(t, "zero target", torch.float32)
-    _check(_lib("elementwise").jb_zero_f32(_ptr(t), ctypes.c_longlong(t.numel()), _stream()), "zero_f32")
+    _check(_lib("elementwise").jb_zero_f32(_ptr(t), t.numel(), _stream()), "zero_f32")
 
 
 # -- rotary positions + cache append --------------------------------------------
@@ -219,7 +261,7 @@ def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
     _need(positions, "positions", torch.int32, (T,))
     _check(_lib("attention_f32").jb_attention_f32(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(token_slot), _ptr(positions),
-        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale), _stream()),
+        T, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale, _stream()),
         "attention_f32")
 
 
@@ -503,7 +545,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
         pair = False
     if pair:
         _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair(
-            _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
+            _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
             int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
     partials = tickets = None
@@ -519,8 +561,8 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
         else:
             partials, tickets = scratch
     _check(_lib("gemm_bf16_tc", _defines_key(_GEMM_DEFINES), _GEMM_DEFINES).jb_gemm_bf16(
-        _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), w.up_tile_offset, _ptr(y), T, N, K, N, code,
-        int(split_k), _ptr(partials), ctypes.c_longlong(0 if partials is None else partials.numel()), _ptr(tickets),
+        _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
+        int(split_k), _ptr(partials), 0 if partials is None else partials.numel(), _ptr(tickets),
         0 if tickets is None else tickets.numel(), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
 
 
@@ -554,7 +596,7 @@ def gemm_qkv_rope_cache(x: torch.Tensor, w: PackedWeight, q_out: torch.Tensor, c
     if k_cache.shape[1:] != (nkv, page_size, hd) or v_cache.shape != k_cache.shape:
         raise KernelError(f"qkv: cache shape {tuple(k_cache.shape)} is not [pages, {nkv}, {page_size}, {hd}]")
     _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair_qkv_rope(
-        _ptr(x), _ptr(w.tiles), ctypes.c_longlong(w.n_tiles), T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
+        _ptr(x), _ptr(w.tiles), w.n_tiles, T, K, _ptr(q_out), _ptr(k_cache), _ptr(v_cache),
         _ptr(cos_sin), _ptr(positions), _ptr(dest),
         nh, nkv, hd, page_size, _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair_qkv_rope")
 
@@ -577,9 +619,9 @@ def sample(logits: torch.Tensor, out_ids: torch.Tensor, temperature: float, top_
         if counts.shape[1] != V:
             raise KernelError("sample: counts width differs from the vocabulary")
     _check(_lib("sampling").jb_sample(
-        _ptr(logits), B, V, _ptr(out_ids), ctypes.c_float(temperature), int(top_k), ctypes.c_float(top_p),
-        ctypes.c_float(repetition_penalty), _ptr(counts), _ptr(count_rows),
-        ctypes.c_ulonglong(seed & ((1 << 64) - 1)), _ptr(seq_ids), _ptr(steps), _ptr(feedback), _stream()),
+        _ptr(logits), B, V, _ptr(out_ids), temperature, int(top_k), top_p,
+        repetition_penalty, _ptr(counts), _ptr(count_rows),
+        seed & ((1 << 64) - 1), _ptr(seq_ids), _ptr(steps), _ptr(feedback), _stream()),
         "sample")
 
 
@@ -610,7 +652,7 @@ def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
     _check(_attention_lib(hd).jb_attention_bf16_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
-        n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
+        n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
         _stream()), "attention_bf16_prefill")
 
 
@@ -662,7 +704,7 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
         _need(q, "attention q", torch.bfloat16, (B, nh * hd))
         _check(lib.jb_attention_bf16_decode(
             _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o), _ptr(part_ml), _ptr(block_table),
-            _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), ctypes.c_float(scale),
+            _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window), scale,
             int(n_splits), _stream()), "attention_bf16_decode", kernels=kernels)
         return
     _need(qkv, "qkv", torch.float32)
@@ -678,7 +720,7 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
     _check(lib.jb_attention_bf16_decode_fused(
         _ptr(qkv), qkv.shape[1], _ptr(cos_sin), _ptr(dest), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(part_o),
         _ptr(part_ml), _ptr(block_table), _ptr(kv_len), B, nh, nkv, hd, page_size, block_table.shape[1], int(window),
-        ctypes.c_float(scale), int(n_splits), int(write_kv), _stream()), "attention_bf16_decode_fused", kernels=kernels)
+        scale, int(n_splits), int(write_kv), _stream()), "attention_bf16_decode_fused", kernels=kernels)
 
 
 # -- tcgen05 prefill attention (head sizes 64 and 128, up to 128 query heads per kv head) ------------------
@@ -705,4 +747,4 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _check(_lib("attention_tc", int(hd), lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES)).jb_attention_tc_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
-        ctypes.c_float(scale), _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")
+        scale, _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")

@@ -214,3 +214,37 @@ def test_default_stop_tokens():
     assert LlamaConfig.from_dict(no_eos).stop_token_ids() == ()
     assert LlamaConfig.from_dict(dict(no_eos, vocab_size=128256)).stop_token_ids() == (128001, 128009)
     assert LlamaConfig.from_dict(dict(TINY_A, vocab_size=128256)).stop_token_ids() == (250, 251)
+
+
+def test_declared_argument_types_match_the_exported_c_functions():
+    """`ops._SIGNATURES` names the argument types of every exported kernel function; a launch passes plain
+    integers and floats, so a wrong letter would pass a pointer as an int.  Read the declarations from the
+    sources and compare."""
+    import re
+    from pathlib import Path
+    from janus_b200.kernels import ops
+    csrc = Path(ops.__file__).resolve().parent.parent / "csrc"
+    found = {}
+    for path in csrc.glob("*.cu"):
+        text = path.read_text()
+        for m in re.finditer(r"JB_EXPORT\s+int\s+(\w+)\s*\(([^)]*)\)", text):
+            name, args = m.group(1), m.group(2).strip()
+            letters = ""
+            for arg in [a.strip() for a in args.split(",") if a.strip()]:
+                if "*" in arg or "cudaStream_t" in arg:
+                    letters += "p"
+                elif "unsigned long long" in arg:
+                    letters += "u"
+                elif "long long" in arg:
+                    letters += "l"
+                elif re.match(r"(const\s+)?float\b", arg):
+                    letters += "f"
+                elif re.match(r"(const\s+)?int\b", arg):
+                    letters += "i"
+                else:
+                    raise AssertionError(f"{name}: unknown argument type in {arg!r}")
+            found[name] = letters
+    for name, signature in ops._SIGNATURES.items():
+        assert found.get(name) == signature, f"{name}: declared {signature}, the source says {found.get(name)}"
+    launched = {n for n, letters in found.items() if letters}      # everything but the head_dim queries
+    assert launched - set(ops._SIGNATURES) <= {"jb_attention_bf16_decode_noalloc"}
