@@ -433,19 +433,26 @@ def layer_weight_elems(cfg):
     return qkv + o + 3 * cfg["intermediate_size"] * cfg["hidden_size"]
 
 
-def run_kernels(contexts=None):
+KERNEL_SHAPES = {   # hidden, heads, kv heads, head size, intermediate, vocabulary
+    "8b": (4096, 32, 8, 128, 14336, 128256),
+    "1b": (2048, 32, 8, 64, 8192, 128256),
+    "13b": (5120, 40, 40, 128, 13824, 32000),
+}
+
+
+def run_kernels(contexts=None, shape="8b"):
     """The step's hot kernels alone at the 8B layer shapes, for the roofline figures under profiles/:
     each is captured 24 times into one CUDA graph (as the engine runs them: back to back, programmatic
     dependent launch) over several copies of its weights or cache, so that every launch reads from DRAM,
     and timed with CUDA events around 5 replays.  One line per kernel; nothing here is the headline.
-    With `contexts` (key counts), decode attention alone at those contexts, for 1 and 8 sequences."""
+    With `contexts` (key counts), decode attention alone at those contexts, for 1, 8 and 64 sequences."""
     import math
 
     import torch
 
     from janus_b200.kernels import ops
     dev = "cuda:0"
-    H, NH, NKV, HD, I, V = 4096, 32, 8, 128, 14336, 128256
+    H, NH, NKV, HD, I, V = KERNEL_SHAPES[shape]
 
     def timed(fn, reps=24):
         for _ in range(3):
@@ -511,7 +518,8 @@ def run_kernels(contexts=None):
             product("down (add)", T, H, I, "add")
         product("lm_head", 8, V, H, "store", copies=3)
 
-    for B, ctx in ([(b, c) for c in contexts for b in (1, 8)] if contexts else ((1, 2080), (8, 2080), (64, 2080))):
+    cases = [(b, c) for c in contexts for b in (1, 8, 64) if b * c <= 1 << 21] if contexts else ((1, 2080), (8, 2080), (64, 2080))
+    for B, ctx in cases:
         pages = (ctx + 63) // 64
         n_pages = B * pages
         copies = max(1, min(8, int(3e9 // (n_pages * NKV * 64 * HD * 4))))
@@ -677,6 +685,8 @@ def main():
                     help="time the step's hot kernels alone at the 8B layer shapes (one JSON line each)")
     ap.add_argument("--contexts", default=None, metavar="KEYS,...",
                     help="with --kernels: decode attention alone at these context lengths (1 and 8 sequences)")
+    ap.add_argument("--kernel-shape", default="8b", choices=sorted(KERNEL_SHAPES),
+                    help="with --kernels: the layer sizes (default: the 8B shape)")
     ap.add_argument("--plan-check", action="store_true",
                     help="time the kernel and K-split that `ops.gemm_plan` picks against its alternatives for the "
                          "products of 1B-, 8B- and 13B-sized layers (one JSON line each)")
@@ -698,7 +708,7 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.kernels:
-        run_kernels([int(c) for c in args.contexts.split(",")] if args.contexts else None)
+        run_kernels([int(c) for c in args.contexts.split(",")] if args.contexts else None, args.kernel_shape)
         return 0
     if args.plan_check:
         run_plan_check()
