@@ -47,7 +47,19 @@ namespace {
 constexpr int BM = 128;   // weight rows per tile = TMEM lanes
 constexpr int BK = 64;    // bf16 elements per k-tile = one 128-byte swizzle row
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+// Epilogue warps: one per quarter of the TMEM lanes and per 16 columns of the token tile, 16 at most: the warps
+// of a quarter share a tile's columns 16 by 16.  A tile of 64 tokens leaves TMEM in a quarter of the time that
+// four warps take (8B-sized layers at 64 tokens: 13.2 / 10.2 / 41.3 / 21.0 us with four warps, 11.7 / 8.8 /
+// 36.5 / 19.5 us with sixteen), while a tile of 16 tokens has one chunk of columns and runs fastest with four
+// (more threads only make the CTA slower to start and to end: +0.3 to 0.6 us).  JB_EPI_WARPS (4, 8, 16) forces a count.
+#ifndef JB_EPI_WARPS
+#define JB_EPI_WARPS 0
+#endif
+constexpr int epi_warps(int bn) {
+  return JB_EPI_WARPS ? JB_EPI_WARPS : bn <= 16 ? 4 : bn <= 32 ? 8 : 16;
+}
+static_assert(JB_EPI_WARPS == 0 || JB_EPI_WARPS == 4 || JB_EPI_WARPS == 8 || JB_EPI_WARPS == 16, "4, 8 or 16 epilogue warps");
+constexpr int threads_for(int bn) { return 64 + 32 * epi_warps(bn); }
 
 enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3, ADD_ORDERED = 4 };   // 4: ADD_F32 with K cut, slices summed in order
 
@@ -220,7 +232,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int n
 }
 
 template <int BN, int MODE, int STAGES>
-__global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
+__global__ void __launch_bounds__(threads_for(BN)) gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w,
                                                           const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                           int T, int N_out, int ldy, int k_tiles, int k_tiles_per_split,
                                                           int n_tiles, int n_tok_tiles, int n_w_tiles,
@@ -228,6 +240,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
                                                           float* __restrict__ partials, int* __restrict__ tickets,
                                                           int* __restrict__ status) {
   using C = Cfg<BN, MODE>;
+  constexpr int EPI_WARPS = epi_warps(BN), EPI_PARTS = EPI_WARPS / 4;
   extern __shared__ uint8_t smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -248,7 +261,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full0 + 8 * b, 1);
-      mbar_init(acc_empty0 + 8 * b, 4);  // one arrival per epilogue warp
+      mbar_init(acc_empty0 + 8 * b, EPI_WARPS);  // one arrival per epilogue warp
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -351,6 +364,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
     // ---------------- epilogue ----------------
     jb::pdl_wait();
     const int quarter = warp & 3;  // TMEM lanes this warp may read
+    const int part = (warp - 2) >> 2;   // which of the columns' 16-wide chunks (every EPI_PARTS-th) this warp takes
     int j = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
       const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
@@ -369,7 +383,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         const int row = quarter * 32 + lane;
         float* mine = partials + ((size_t)(out_tile * slices + slice) * BN) * BM + row;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
+        for (int c0 = 16 * part; c0 < BN; c0 += 16 * EPI_PARTS) {
           if (tc.t0 + c0 >= T) break;  // uniform
           uint32_t r[16];
           tmem_ld16(lane_base + c0, r);
@@ -382,14 +396,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         __syncwarp();
         if (lane == 0) mbar_arrive(acc_empty0 + 8 * buf);   // the MMA warp may go on with this buffer
         __threadfence();
-        asm volatile("bar.sync 1, 128;" ::: "memory");     // the four epilogue warps
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");     // the epilogue warps
         if (warp == 2 && lane == 0) {
           const int before = atomicAdd(tickets + out_tile, 1);
           const int last = before == slices - 1;
           if (last) tickets[out_tile] = 0;                 // every slice has arrived: ready for the next launch
           *last_flag = last;
         }
-        asm volatile("bar.sync 1, 128;" ::: "memory");
+        asm volatile("bar.sync 1, %0;" ::"n"(32 * EPI_WARPS) : "memory");
         if (*last_flag) {
           __threadfence();
           const float* all = partials + ((size_t)out_tile * slices * BN) * BM + row;
@@ -397,7 +411,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
           // eight columns at a time: their loads are in flight together; each column's slices are added in
           // slice order; the sum goes to Y by a reduction that nobody else adds to (so its order is fixed too)
 #pragma unroll 1
-          for (int c0 = 0; c0 < cols; c0 += 8) {
+          for (int c0 = 8 * part; c0 < cols; c0 += 8 * EPI_PARTS) {
             float sum[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll 4
             for (int sl = 0; sl < slices; ++sl) {
@@ -415,7 +429,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc_kernel(const __grid_constant_
         }
       } else {
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
+      for (int c0 = 16 * part; c0 < BN; c0 += 16 * EPI_PARTS) {
         if (tc.t0 + c0 >= T) break;  // uniform
         uint32_t r[16];
         tmem_ld16(lane_base + c0, r);
@@ -543,7 +557,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_o
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return (int)e;
     int occ = 0;
-    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemm_tc_kernel<BN, MODE, STAGES>, THREADS, smem);
+    e = cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, gemm_tc_kernel<BN, MODE, STAGES>, threads_for(BN), smem);
     if (e != cudaSuccess) return (int)e;
     // every resident CTA holds TMEM columns for the whole kernel: never more CTAs than the 512 columns serve
     ctas_per_sm = max(1, min(occ, 512 / C::TMEM_COLS));
@@ -567,7 +581,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, void* Y, int T, int N_o
               ordered.n_tickets);
   }
   const int grid = (int)min(n_tiles, (long long)sm_count() * ctas_per_sm);
-  jb::Launch cfg(dim3(grid), dim3(THREADS), smem, stream);
+  jb::Launch cfg(dim3(grid), dim3(threads_for(BN)), smem, stream);
   return (int)cudaLaunchKernelEx(&cfg.c, gemm_tc_kernel<BN, MODE, STAGES>, mw, mx, Y, T, N_out, ldy, k_tiles, per,
                                  (int)n_tiles, n_tok_tiles, n_w_tiles, up_tile_offset, splits > 1 ? 1 : 0,
                                  in_order ? ordered.partials : (float*)nullptr, in_order ? ordered.tickets : (int*)nullptr,

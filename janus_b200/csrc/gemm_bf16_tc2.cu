@@ -33,7 +33,15 @@ namespace {
 constexpr int BM = 128;   // weight rows per CTA (256 per pair)
 constexpr int BK = 64;
 constexpr int UMMA_K = 16;
-constexpr int THREADS = 192;
+// Epilogue warps per CTA: 4 (one per quarter of the TMEM lanes), 8 or 16 (two or four per quarter, which share
+// a tile's columns 16 by 16).
+#ifndef JB_PAIR_EPI_WARPS
+#define JB_PAIR_EPI_WARPS 16
+#endif
+constexpr int EPI_WARPS = JB_PAIR_EPI_WARPS;
+static_assert(EPI_WARPS == 4 || EPI_WARPS == 8 || EPI_WARPS == 16, "4, 8 or 16 epilogue warps");
+constexpr int EPI_PARTS = EPI_WARPS / 4;
+constexpr int THREADS = 64 + 32 * EPI_WARPS;
 constexpr uint32_t PEER_MASK = 0xFEFFFFFFu;  // clears the CTA-rank bit of a shared::cluster address: the pair's first CTA
 
 enum Mode { STORE_BF16 = 0, STORE_F32 = 1, ADD_F32 = 2, SWIGLU = 3, QKV_ROPE = 4 };
@@ -204,7 +212,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     }
     for (int b = 0; b < 2; ++b) {
       mbar_init(acc_full0 + 8 * b, 1);
-      mbar_init(acc_empty0 + 8 * b, 8);  // four epilogue warps of each CTA
+      mbar_init(acc_empty0 + 8 * b, 2 * EPI_WARPS);  // the epilogue warps of both CTAs
     }
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -283,6 +291,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
   } else {
     // ---------------- epilogue (this CTA's 128 rows) ----------------
     const int quarter = warp & 3;
+    const int part = (warp - 2) >> 2;   // which of the columns' 16-wide chunks (every EPI_PARTS-th) this warp takes
     int j = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
       const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
@@ -296,7 +305,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         __nv_bfloat16* yrow = (__nv_bfloat16*)Y + (size_t)t * ldy;
         const bool vec_ok = (ldy % 8) == 0 && (((uintptr_t)Y) & 15) == 0;
 #pragma unroll 1
-        for (int c0 = 0; c0 < 128; c0 += 16) {
+        for (int c0 = 16 * part; c0 < 128; c0 += 16 * EPI_PARTS) {
           if (tc.f0 + c0 >= N_out) break;
           uint32_t r[16], u[16];
           tmem_ld16(lane_base + c0, r);
@@ -348,7 +357,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
             out = base + (((size_t)(dst / rope.page_size) * rope.nkv + kvh) * rope.page_size + dst % rope.page_size) * hd;
           }
 #pragma unroll 1
-          for (int i = 0; i < half; i += 16) {
+          for (int i = 16 * part; i < half; i += 16 * EPI_PARTS) {   // (half is a multiple of 16 * EPI_PARTS or the parts idle)
             uint32_t lo[16], hi[16];
             tmem_ld16(lane_base + c + i, lo);
             tmem_ld16(lane_base + c + half + i, hi);
@@ -387,7 +396,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
         const int f = tc.f0 + (int)rank * BM + quarter * 32 + lane;
         const bool f_ok = f < N_out;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += 16) {
+        for (int c0 = 16 * part; c0 < BN; c0 += 16 * EPI_PARTS) {
           if (tc.t0 + c0 >= T) break;
           uint32_t r[16];
           tmem_ld16(lane_base + c0, r);
