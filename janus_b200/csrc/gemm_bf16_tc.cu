@@ -209,9 +209,12 @@ struct Cfg {
   static constexpr int B_BYTES = BN * BK * 2;
   static constexpr int STAGE_BYTES = A_TILES * A_BYTES + B_BYTES;
   static constexpr int ACC_COLS = A_TILES * BN;        // one accumulator buffer
-  static constexpr int WANT_COLS = 2 * ACC_COLS;       // two buffers
+  // two buffers, so that a tile's epilogue runs under the next tile's MMAs; one where two do not fit the 512
+  // TMEM columns (the gated product over 256 tokens: gate and up accumulators of 256 columns each)
+  static constexpr int N_BUF = 2 * ACC_COLS <= 512 ? 2 : 1;
+  static constexpr int WANT_COLS = N_BUF * ACC_COLS;
   static constexpr int TMEM_COLS = WANT_COLS <= 32 ? 32 : WANT_COLS <= 64 ? 64 : WANT_COLS <= 128 ? 128 : WANT_COLS <= 256 ? 256 : 512;
-  static_assert(WANT_COLS <= 512, "two accumulator buffers must fit the 512 TMEM columns");
+  static_assert(WANT_COLS <= 512, "the accumulators must fit the 512 TMEM columns");
 };
 
 struct TileCoord {
@@ -331,9 +334,9 @@ __global__ void __launch_bounds__(threads_for(BN)) gemm_tc_kernel(const __grid_c
       int it = 0, j = 0;
       for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++j) {
         const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
-        const int buf = j & 1;
-        // the epilogue must have drained this buffer (passes at once the first two times)
-        ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, status, 2);
+        const int buf = j % C::N_BUF;
+        // the epilogue must have drained this buffer (passes at once the first time a buffer is used)
+        ok = mbar_wait(acc_empty0 + 8 * buf, ((j / C::N_BUF) & 1) ^ 1, status, 2);
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc_addr = tmem_base + buf * C::ACC_COLS;
@@ -368,8 +371,8 @@ __global__ void __launch_bounds__(threads_for(BN)) gemm_tc_kernel(const __grid_c
     int j = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++j) {
       const TileCoord tc = tile_coord(tile, n_tok_tiles, n_w_tiles, k_tiles, k_tiles_per_split, BN);
-      const int buf = j & 1;
-      if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, status, 3)) break;
+      const int buf = j % C::N_BUF;
+      if (!mbar_wait(acc_full0 + 8 * buf, (j / C::N_BUF) & 1, status, 3)) break;
       tc_fence_after();
       const int f = tc.m0 + quarter * 32 + lane;
       const bool f_ok = f < N_out;
@@ -606,9 +609,9 @@ int dispatch(const CUtensorMap& mw, const void* X, void* Y, int T, int N_out, in
   if (T <= 16) JB_GO(16, JB_ST(16))
   else if (T <= 32) JB_GO(32, JB_ST(32))
   else if (T <= 64) JB_GO(64, JB_ST(64))
-  else if constexpr (MODE == SWIGLU) JB_GO(128, JB_ST(128))   // two accumulators per buffer: 128 tokens fill TMEM
   else if (T <= 128) JB_GO(128, JB_ST(128))
-  else JB_GO(256, JB_ST(256))
+  else if (MODE == SWIGLU && T > 256) JB_GO(128, JB_ST(128))   // gate and up accumulators: 128 tokens leave room for two buffers
+  else JB_GO(256, JB_ST(256))   // (the gated product of 129 to 256 tokens: one tile a CTA, one buffer)
 #undef JB_ST
 #undef JB_GO
 }

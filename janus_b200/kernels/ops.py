@@ -460,7 +460,9 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     gated = mode == "swiglu"
     w_rows = 2 * N if gated else N
     stream = w_rows * K * 2 / _PLAN_HBM_BYTES_PER_US
-    bn = 128 if (T <= 128 or gated) else 256               # token tile of the single-CTA kernel
+    # token tile of the single-CTA kernel (a gated product's two accumulators leave room for 256 tokens in one
+    # buffer only, which serves where a CTA has one tile: up to 256 tokens)
+    bn = 128 if (T <= 128 or (gated and T > 256)) else 256
     stage_rows = 256 if gated else 128                      # weight rows a step brings in
     step = max(2.0 * stage_rows * bn * 64 / _PLAN_SM_FLOPS_PER_US,
                (stage_rows + bn) * 64 * 2 / _PLAN_SM_FILL_BYTES_PER_US)
