@@ -39,10 +39,11 @@ constexpr int CHUNKS = HD / 8;        // 16-byte chunks per row that exist in gl
 constexpr int THREADS = 128;
 constexpr int KV_TILE = PAGE * LD;    // elements
 constexpr float LOG2E = 1.4426950408889634f;
+// K/V pages in the decode kernel's ring: picked at the launch from 2, 3 and 5 (`decode_stages_for`);
+// JB_DECODE_STAGES forces one depth.
 #ifndef JB_DECODE_STAGES
-#define JB_DECODE_STAGES 3
+#define JB_DECODE_STAGES 0
 #endif
-constexpr int DECODE_STAGES = JB_DECODE_STAGES;  // K/V pages in the decode kernel's ring
 constexpr int RED_LD = HD + 8;                   // row stride (floats) of the warps' exchange of partial outputs
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -327,6 +328,7 @@ __device__ __forceinline__ void rotate_pair(float x0, float x1, const float* cs,
 }
 
 // part_o: [seq][head][split][HD] float32 (unnormalised), part_ml: [seq][head][split][2] (max, sum).
+template <int DECODE_STAGES>
 __global__ void __launch_bounds__(THREADS) decode_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_cache, const bf16* __restrict__ v_cache,
     bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
@@ -537,9 +539,72 @@ __global__ void decode_combine_kernel(const float* __restrict__ part_o, const fl
 }
 
 constexpr int PREFILL_SMEM = (64 * LD + 4 * KV_TILE) * 2;
-constexpr int DECODE_KV_BYTES = 2 * DECODE_STAGES * KV_TILE * 2;
 constexpr int DECODE_RED_BYTES = (4 * 16 * RED_LD + 4 * 16 * 2) * 4;
-constexpr int DECODE_SMEM = (16 + 2) * LD * 2 + (DECODE_KV_BYTES > DECODE_RED_BYTES ? DECODE_KV_BYTES : DECODE_RED_BYTES);
+constexpr int decode_smem(int stages) {
+  const int kv = 2 * stages * KV_TILE * 2;
+  return (16 + 2) * LD * 2 + (kv > DECODE_RED_BYTES ? kv : DECODE_RED_BYTES);
+}
+constexpr int SMEM_PER_SM = 228 * 1024;   // of which every resident CTA takes 1 KB for the system besides its own
+constexpr int ctas_per_sm(int stages) { return SMEM_PER_SM / (decode_smem(stages) + 1024); }
+
+// How deep the ring of the decode kernel is for a launch of `ctas` CTAs.  Three pages (two loads in flight
+// while one page is computed) serve every head size.  Small heads move few bytes per page and per warp, so
+// what pays depends on how many CTAs there are: more than fit the SMs at once run fastest with a ring of two
+// pages (five CTAs an SM at head size 64 instead of three: 64 sequences of 704 keys 24.0 -> 18.4 us), few CTAs
+// of many pages with a ring of five (8 sequences of 2,816 keys 14.3 -> 12.2 us).
+int decode_stages_for(long long ctas, int pages_per_cta) {
+  if (JB_DECODE_STAGES) return JB_DECODE_STAGES;
+  if (HD > 64) return 3;
+  int dev = 0, sms = 148;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const long long fit3 = (long long)sms * ctas_per_sm(3);
+  const long long fit5 = (long long)sms * ctas_per_sm(5);
+  if (ctas > fit3) return 2;
+  if (ctas <= fit5 && pages_per_cta >= 8) return 5;
+  return 3;
+}
+
+template <int ST>
+cudaError_t decode_go(dim3 grid, cudaStream_t stream, bool pdl, const bf16* q, const bf16* k_cache, const bf16* v_cache,
+                      bf16* out, float* part_o, float* part_ml, const int* block_table, const int* kv_len, int nh,
+                      int nkv, int max_pages, int window, float scale_log2, int n_splits, const FusedInput& fused) {
+  static bool configured = false;   // one flag per ring depth
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(decode_kernel<ST>, cudaFuncAttributeMaxDynamicSharedMemorySize, decode_smem(ST));
+    if (e != cudaSuccess) return e;
+    configured = true;
+  }
+  if (pdl) {
+    jb::Launch cfg(grid, dim3(THREADS), decode_smem(ST), stream);
+    return cudaLaunchKernelEx(&cfg.c, decode_kernel<ST>, q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len,
+                              nh, nkv, max_pages, window, scale_log2, n_splits, fused);
+  }
+  decode_kernel<ST><<<grid, THREADS, decode_smem(ST), stream>>>(q, k_cache, v_cache, out, part_o, part_ml, block_table,
+                                                               kv_len, nh, nkv, max_pages, window, scale_log2, n_splits,
+                                                               fused);
+  return cudaGetLastError();
+}
+
+// The decode kernel with the ring depth that suits the launch (`max_pages` bounds a sequence's pages).
+cudaError_t decode_dispatch(dim3 grid, cudaStream_t stream, bool pdl, const bf16* q, const bf16* k_cache,
+                            const bf16* v_cache, bf16* out, float* part_o, float* part_ml, const int* block_table,
+                            const int* kv_len, int nh, int nkv, int max_pages, int window, float scale_log2,
+                            int n_splits, const FusedInput& fused) {
+  const long long ctas = (long long)grid.x * grid.y * grid.z;
+  const int stages = decode_stages_for(ctas, max(1, max_pages / max(1, n_splits)));
+#define JB_DECODE_GO(ST)                                                                                      \
+  return decode_go<ST>(grid, stream, pdl, q, k_cache, v_cache, out, part_o, part_ml, block_table, kv_len, nh, nkv, \
+                       max_pages, window, scale_log2, n_splits, fused)
+  switch (stages) {
+    case 2: JB_DECODE_GO(2);
+    case 5: JB_DECODE_GO(5);
+#if JB_DECODE_STAGES != 0 && JB_DECODE_STAGES != 2 && JB_DECODE_STAGES != 3 && JB_DECODE_STAGES != 5
+    case JB_DECODE_STAGES: JB_DECODE_GO(JB_DECODE_STAGES);
+#endif
+    default: JB_DECODE_GO(3);
+  }
+#undef JB_DECODE_GO
+}
 
 }  // namespace
 
@@ -581,19 +646,12 @@ int decode_launch(const void* q, const void* k_cache, const void* v_cache, void*
   JB_REFUSE(page_size != PAGE, "attention_bf16: page size %d (need %d)", page_size, PAGE);
   JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_bf16: %d heads are not a multiple of %d kv heads", nh, nkv);
   JB_REFUSE(n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml)), "attention_bf16 decode: bad split setup");
-  static bool configured = false;
-  if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
-    if (e != cudaSuccess) return (int)e;
-    configured = true;
-  }
   const int G = nh / nkv;
   const int n_rb = (G + 15) / 16;
   dim3 grid(n_seqs, nkv * n_rb, n_splits);
-  jb::Launch cfg(grid, dim3(THREADS), DECODE_SMEM, stream);
-  cudaError_t le = cudaLaunchKernelEx(&cfg.c, decode_kernel, (const bf16*)q, (const bf16*)k_cache,
-                                      (const bf16*)v_cache, (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
-                                      max_pages, window, scale * LOG2E, n_splits, fused);
+  cudaError_t le = decode_dispatch(grid, stream, true, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
+                                   (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv, max_pages, window,
+                                   scale * LOG2E, n_splits, fused);
   if (le != cudaSuccess) return (int)le;
   if (n_splits > 1) {
     jb::Launch cfg2(dim3(n_seqs * nh), dim3(HD >= 128 ? 128 : 64), 0, stream);
@@ -677,8 +735,6 @@ JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cach
     void* p = nullptr;
     e = cudaGetSymbolAddress(&p, noalloc_scratch);
     if (e != cudaSuccess) return (int)e;
-    e = cudaFuncSetAttribute(decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, DECODE_SMEM);
-    if (e != cudaSuccess) return (int)e;
     scratch = static_cast<float*>(p);
     noalloc_device_ptr[device].store(scratch);
   }
@@ -687,10 +743,12 @@ JB_EXPORT int jb_attention_bf16_decode_noalloc(const void* q, const void* k_cach
   const int G = nh / nkv;
   const int n_rb = (G + 15) / 16;
   dim3 grid(n_seqs, nkv * n_rb, n_splits);
-  decode_kernel<<<grid, THREADS, DECODE_SMEM, stream>>>((const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache,
-                                                        (bf16*)out, part_o, part_ml, block_table, kv_len, nh, nkv,
-                                                        max_pages, window, scale * LOG2E, n_splits, FusedInput{});
-  JB_CHECK_LAUNCH();
+  // the same kernel and ring depth as the ordinary entry point picks (a plain launch; the first launch of a
+  // ring depth also raises that kernel's shared-memory limit, which allocates nothing)
+  e = decode_dispatch(grid, stream, false, (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, (bf16*)out,
+                      part_o, part_ml, block_table, kv_len, nh, nkv, max_pages, window, scale * LOG2E, n_splits,
+                      FusedInput{});
+  if (e != cudaSuccess) return (int)e;
   if (n_splits > 1) {
     decode_combine_kernel<<<n_seqs * nh, HD >= 128 ? 128 : 64, 0, stream>>>(part_o, part_ml, (bf16*)out, n_splits);
     JB_CHECK_LAUNCH();
