@@ -26,10 +26,14 @@ def main(argv=None) -> int:
     import torch
 
     import janus_b200
+    from janus_b200.cache import PAGE_SIZE
     from janus_b200.engine.step import StepEntry
 
     os.makedirs(args.out, exist_ok=True)
+    # every live request holds at least one page: as many slots as pages serve any trace that
+    # keeps within --max-tokens
     model = janus_b200.load(args.model, dtype=args.dtype, max_tokens=args.max_tokens,
+                            max_slots=max(1, (args.max_tokens + PAGE_SIZE - 1) // PAGE_SIZE),
                             use_graphs=not args.no_graphs)
     slots: Dict[str, int] = {}
     for line in sys.stdin:
