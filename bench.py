@@ -398,6 +398,7 @@ def run_prompt_lengths(layers, which):
     from janus_b200.engine import StepEntry
     cfg = dict(CONFIG_8B, num_hidden_layers=layers, max_position_embeddings=8192)
     model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=16384, max_slots=16, norm_std=0.0)
+    torch.cuda.profiler.start()          # for `ncu --profile-from-start off`: nothing of the weights' set-up is captured
     g = torch.Generator().manual_seed(0)
     pk = peaks()
     for seqs, T in (tuple(int(v) for v in item.split("x")) for item in which.split(",")):
