@@ -592,10 +592,11 @@ def run_plan_check():
               ("13B o", 5120, 5120), ("13B down", 5120, 13824)]
     for name, N, K in shapes:
         ws = [ops.pack_weight((torch.randn(N, K, device=dev) * 0.02).to(torch.bfloat16)) for _ in range(4)]
-        for T in (8, 64, 256, 1024):
+        for T in (8, 64, 256, 1024, 2048):
             x = torch.randn(T, K, device=dev).to(torch.bfloat16)
             y = torch.zeros(T, N, device=dev, dtype=torch.float32)
-            pick = ops.gemm_plan(T, N, K, "add")
+            pick3 = ops.gemm_plan_whole(T, N, K, "add")
+            pick = pick3[:2]
             times = {}
             k_tiles = (K + 63) // 64
             for pair in ((False, True) if T >= ops.GEMM_PAIR_MIN_TOKENS else (False,)):
@@ -611,11 +612,22 @@ def run_plan_check():
                         ops.gemm_bf16(x, ws[turn[0] % 4], y, mode="add", split_k=split, pair=pair)
 
                     times[(pair, split)] = timed(fn)
+            if pick3[2]:      # only the last wave's tiles are cut: a variant of its own
+                turn = [0]
+
+                def fn():
+                    turn[0] += 1
+                    ops.gemm_bf16(x, ws[turn[0] % 4], y, mode="add", split_k=pick3[1], pair=True, whole_tiles=pick3[2])
+
+                pick_us = timed(fn)
+            else:
+                pick_us = times[pick]
             best = min(times, key=times.get)
-            print(json.dumps({"product": name, "tokens": T, "pick": {"pairs": pick[0], "splits": pick[1]},
-                              "pick_us": round(times[pick], 1), "best": {"pairs": best[0], "splits": best[1]},
+            print(json.dumps({"product": name, "tokens": T,
+                              "pick": {"pairs": pick[0], "splits": pick[1], "whole_tiles": pick3[2]},
+                              "pick_us": round(pick_us, 1), "best": {"pairs": best[0], "splits": best[1]},
                               "best_us": round(times[best], 1),
-                              "pick_off_by": round(times[pick] / times[best] - 1.0, 4)}), flush=True)
+                              "pick_off_by": round(pick_us / times[best] - 1.0, 4)}), flush=True)
     ops.check_kernel_status(torch.device(dev))
 
 

@@ -186,12 +186,37 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int k
   return c;
 }
 
+// The work of one pair, in the order all three roles walk it: items pair, pair + pairs, ...  An item is a tile,
+// or one of `splits` slices of K of a tile (an adding product cut along K).  With `n_whole` > 0 only the tiles
+// from n_whole on are cut: the tiles that fill whole waves of pairs run uncut, and the last, partial wave is cut
+// into slices so that its pieces fill the pairs again (128 tiles on 74 pairs: 74 whole tiles, then 54 tiles in
+// 4 slices each = 216 pieces in three rounds of a quarter tile: 1.75 waves' time instead of 2).
+template <int MODE>
+struct Walk {
+  int n_items, n_tok_tiles, k_tiles, k_per, splits, n_pairs, n_whole;
+  int item;
+  __device__ Walk(int pair, int n_pairs_, int n_items_, int n_tok_tiles_, int k_tiles_, int k_per_, int splits_,
+                  int n_whole_)
+      : n_items(n_items_), n_tok_tiles(n_tok_tiles_), k_tiles(k_tiles_), k_per(k_per_), splits(splits_),
+        n_pairs(n_pairs_), n_whole(n_whole_), item(pair) {}
+  __device__ __forceinline__ bool next(TileCoord& c) {
+    if (item >= n_items) return false;
+    if (item < n_whole) {
+      c = tile_coord<MODE>(item, n_tok_tiles, k_tiles, k_tiles, 1);
+    } else {
+      c = tile_coord<MODE>(n_whole * splits + (item - n_whole), n_tok_tiles, k_tiles, k_per, splits);
+    }
+    item += n_pairs;
+    return true;
+  }
+};
+
 template <int MODE>
 __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant__ CUtensorMap map_w,
                                                            const __grid_constant__ CUtensorMap map_x, void* __restrict__ Y,
                                                            int T, int N_out, int ldy, int k_tiles, int n_tiles,
-                                                           int n_tok_tiles, int k_per, int splits, int up_tile_offset,
-                                                           RopeOut rope, int* __restrict__ status) {
+                                                           int n_tok_tiles, int k_per, int splits, int n_whole,
+                                                           int up_tile_offset, RopeOut rope, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   uint64_t* bars = (uint64_t*)(smem + STAGES * STAGE_BYTES);
@@ -234,8 +259,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs) {
-        const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
+      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, k_tiles, k_per, splits, n_whole);
+      TileCoord tc;
+      while (ok && walk.next(tc)) {
         // rows of this CTA's two loads: its 128 rows of the pair's M side, its half of the column operand
         // this CTA's weight row tile (the weights are packed: a tile is one contiguous 16 KB block)
         const int w_tile = MODE == SWIGLU ? (rank ? up_tile_offset + tc.f0 / BM : tc.f0 / BM) : tc.f0 / BM + (int)rank;
@@ -265,13 +291,14 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       constexpr uint32_t idesc = instr_desc_pair(BN);
       bool ok = true;
       int it = 0, j = 0;
-      for (int tile = pair; tile < n_tiles && ok; tile += n_pairs, ++j) {
+      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, k_tiles, k_per, splits, n_whole);
+      TileCoord tc;
+      for (; ok && walk.next(tc); ++j) {
         const int buf = j & 1;
         ok = mbar_wait(acc_empty0 + 8 * buf, ((j >> 1) & 1) ^ 1, status, 22);
         if (!ok) break;
         tc_fence_after();
         const uint32_t acc_addr = tmem_base + buf * ACC_COLS;
-        const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
         for (int i = tc.k_lo; i < tc.k_hi; ++i, ++it) {
           const int s = it % STAGES;
           ok = mbar_wait(full0 + 8 * s, (it / STAGES) & 1, status, 22);
@@ -293,8 +320,9 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     const int quarter = warp & 3;
     const int part = (warp - 2) >> 2;   // which of the columns' 16-wide chunks (every EPI_PARTS-th) this warp takes
     int j = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++j) {
-      const TileCoord tc = tile_coord<MODE>(tile, n_tok_tiles, k_tiles, k_per, splits);
+    Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, k_tiles, k_per, splits, n_whole);
+    TileCoord tc;
+    for (; walk.next(tc); ++j) {
       const int buf = j & 1;
       if (!mbar_wait(acc_full0 + 8 * buf, (j >> 1) & 1, status, 23)) break;
       tc_fence_after();
@@ -488,7 +516,7 @@ int sm_count() {
 
 template <int MODE>
 int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T, int N_out, int K, int ldy,
-           const RopeOut& rope, int* status, cudaStream_t stream, int split_k = 1) {
+           const RopeOut& rope, int* status, cudaStream_t stream, int split_k = 1, int whole_tiles = 0) {
   constexpr int smem = STAGES * STAGE_BYTES + (2 * STAGES + 4) * 8 + 16 + 1024;
   static bool configured = false;
   if (!configured) {
@@ -509,13 +537,18 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
   constexpr int F_TILE = MODE == SWIGLU ? 128 : 256;
   const int n_tok_tiles = (T + 255) / 256, n_w_tiles = (N_out + F_TILE - 1) / F_TILE;
   // only a product that adds can be cut along K: its slices meet by atomic adds (no slice is empty)
+  const int half_sms = sm_count() / 2;
+  const int out_tiles_i = n_tok_tiles * n_w_tiles;
   const int want = MODE == ADD_F32 ? max(1, min(split_k, k_tiles)) : 1;
+  // `whole_tiles` of an adding product's tiles (those that fill whole waves of pairs) stay uncut, the rest is cut
+  const int n_whole = (MODE == ADD_F32 && want > 1) ? max(0, min(whole_tiles, out_tiles_i)) : 0;
   const int k_per = (k_tiles + want - 1) / want;
   const int splits = (k_tiles + k_per - 1) / k_per;
-  const long long all_tiles = (long long)n_tok_tiles * n_w_tiles * splits;
-  JB_REFUSE(all_tiles > 0x7fffffffLL, "gemm_bf16_pair: too many tiles (%lld)", all_tiles);
+  const long long all_tiles = n_whole + (long long)(out_tiles_i - n_whole) * splits;
+  JB_REFUSE(all_tiles > 0x7fffffffLL || (long long)n_tok_tiles * n_w_tiles > 0x7fffffffLL,
+            "gemm_bf16_pair: too many tiles (%lld)", all_tiles);
   const int n_tiles = (int)all_tiles;
-  const int pairs = n_tiles < sm_count() / 2 ? n_tiles : sm_count() / 2;
+  const int pairs = n_tiles < half_sms ? n_tiles : half_sms;
   cudaLaunchConfig_t cfg = cudaLaunchConfig_t{};
   cudaLaunchAttribute attrs[2];
   cfg.gridDim = dim3(2 * pairs);
@@ -534,23 +567,26 @@ int launch(const void* X, const void* W, long long w_tiles, int up_tile_offset, 
     cfg.numAttrs = 2;
   }
   return (int)cudaLaunchKernelEx(&cfg, gemm_tc2_kernel<MODE>, mw, mx, Y, T, N_out, ldy, k_tiles, n_tiles,
-                                 n_tok_tiles, k_per, splits, MODE == SWIGLU ? up_tile_offset : 0, rope, status);
+                                 n_tok_tiles, k_per, splits, n_whole, MODE == SWIGLU ? up_tile_offset : 0, rope, status);
 }
 
 }  // namespace
 
 // Same contract as jb_gemm_bf16: Y (+)= X . W^T with X [T, K] and W packed (jb_pack_weight_bf16); `split_k` > 1
-// cuts K of an adding product (mode ADD_F32) into that many slices, which meet in Y by atomic adds.
+// cuts K of an adding product (mode ADD_F32) into that many slices, which meet in Y by atomic adds; the first
+// `whole_tiles` output tiles (256 x 256, token tile fastest) stay uncut: the tiles that fill whole waves of CTA
+// pairs, so that only the last, partial wave is cut.
 // Meant for prompt-sized T.  status codes of a timed-out wait: 21 producer, 22 MMA, 23 epilogue.
 JB_EXPORT int jb_gemm_bf16_pair(const void* X, const void* W, long long w_tiles, int up_tile_offset, void* Y, int T,
-                                int N_out, int K, int ldy, int mode, int split_k, int* status, cudaStream_t stream) {
+                                int N_out, int K, int ldy, int mode, int split_k, int whole_tiles, int* status,
+                                cudaStream_t stream) {
   if (T <= 0 || N_out <= 0) return 0;
   JB_REFUSE(K <= 0 || K % 8 != 0, "gemm_bf16_pair: K = %d must be a positive multiple of 8 (16-byte rows for TMA)", K);
   JB_REFUSE(((uintptr_t)X | (uintptr_t)W) & 15, "gemm_bf16_pair: operands must be 16-byte aligned");
   switch (mode) {
     case STORE_BF16: return launch<STORE_BF16>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     case STORE_F32: return launch<STORE_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
-    case ADD_F32: return launch<ADD_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, split_k);
+    case ADD_F32: return launch<ADD_F32>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream, split_k, whole_tiles);
     case SWIGLU: return launch<SWIGLU>(X, W, w_tiles, up_tile_offset, Y, T, N_out, K, ldy, RopeOut{}, status, stream);
     default: JB_REFUSE(true, "gemm_bf16_pair: unknown mode %d", mode);
   }

@@ -57,7 +57,7 @@ _SIGNATURES = {
     "jb_swiglu": "ppiiip", "jb_swiglu_f32_to_bf16": "piipiip", "jb_zero_f32": "plp",
     "jb_pack_weight_bf16": "piipp", "jb_rope_cache_write": "piipipppppiiiiiiip",
     "jb_gemm_f32": "pppiiiiiip", "jb_attention_f32": "pppppppiiiiiiifp",
-    "jb_gemm_bf16": "pplipiiiiiiplpipp", "jb_gemm_bf16_pair": "pplipiiiiiipp",
+    "jb_gemm_bf16": "pplipiiiiiiplpipp", "jb_gemm_bf16_pair": "pplipiiiiiiipp",
     "jb_gemm_bf16_pair_qkv_rope": "ppliippppppiiiipp",
     "jb_sample": "piipfiffppupppp",
     "jb_attention_bf16_prefill": "pppppppiiiiiiiifp", "jb_attention_bf16_decode": "ppppppppiiiiiiifip",
@@ -426,10 +426,24 @@ _PLAN_DECODE_MAX_SPLIT = 24
 _PLAN_DECODE_STEPS_PER_ADD = 1e-4   # adds of a 128-row tile's token, in steps along K (fitted: 60 measured cases)
 _PLAN_PAIR_SPLITS = (1, 2, 3, 4, 6)
 _PLAN_ORDERED_TILE_US = 3.0         # deterministic mode: fence, ticket and ordered sum of a tile of a cut K
+_PLAN_TAIL_MIN_K = 32               # k-tiles a slice of a last wave's tile has at least (measured: the o projection
+                                    # of 8B layers, 64 k-tiles, loses 4 % with slices of 16; the down projection, 224, gains 12 %)
+
+
+def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tuple[bool, int]:
+    """(CTA pairs?, slices of K): see `gemm_plan_whole`, which also says how many tiles stay uncut."""
+    return gemm_plan_whole(T, N, K, mode, allow_pairs)[:2]
+
+
+def _plan_cache_clear() -> None:
+    gemm_plan_whole.cache_clear()
+
+
+gemm_plan.cache_clear = _plan_cache_clear
 
 
 @functools.lru_cache(maxsize=4096)
-def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tuple[bool, int]:
+def gemm_plan_whole(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tuple[bool, int, int]:
     """Which kernel runs x[T, K] . w[N, K]^T and into how many slices of K it is cut: (CTA pairs?, slices).
 
     Up to 64 tokens the product streams its weights: the single-CTA kernel, with K cut so that the waves of
@@ -446,7 +460,7 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     ordered = _deterministic[0]     # slices are summed in a fixed order: the single-CTA kernel can, CTA pairs cannot
     if T <= 64:
         if mode != "add" or tiles_w >= sms:
-            return False, 1      # a wave of tiles or more streams weights on every SM as it is
+            return False, 1, 0   # a wave of tiles or more streams weights on every SM as it is
         # the critical path in steps along K: waves of tiles over the SMs x steps of a slice; a little per add
         best = (float("inf"), 1)
         for split in range(1, max(1, min(k_tiles // 4, _PLAN_DECODE_MAX_SPLIT)) + 1):
@@ -456,7 +470,7 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
             cost = waves * ((k_tiles + split - 1) // split) + _PLAN_DECODE_STEPS_PER_ADD * split * T * tiles_w
             if cost < best[0] - 1e-9:
                 best = (cost, split)
-        return False, best[1]
+        return False, best[1], 0
     gated = mode == "swiglu"
     w_rows = 2 * N if gated else N
     stream = w_rows * K * 2 / _PLAN_HBM_BYTES_PER_US
@@ -466,7 +480,7 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
     stage_rows = 256 if gated else 128                      # weight rows a step brings in
     step = max(2.0 * stage_rows * bn * 64 / _PLAN_SM_FLOPS_PER_US,
                (stage_rows + bn) * 64 * 2 / _PLAN_SM_FILL_BYTES_PER_US)
-    best = (float("inf"), False, 1)
+    best = (float("inf"), False, 1, 0)
     for split in (_PLAN_SPLITS if mode == "add" else (1,)):
         if split > 1 and split > k_tiles // 4:
             break
@@ -475,7 +489,7 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
         cost = max(waves * (((k_tiles + split - 1) // split) * step + _PLAN_TILE_US), stream)
         if split > 1:
             cost += _PLAN_US_PER_ADD * T * N * split + (_PLAN_ORDERED_TILE_US * waves if ordered else 0.0)
-        best = min(best, (cost, False, split))
+        best = min(best, (cost, False, split, 0))
     if allow_pairs and _GEMM_PAIR and T >= GEMM_PAIR_MIN_TOKENS:
         clusters = ((T + 255) // 256) * (tiles_w if gated else (N + 255) // 256)
         for split in (_PLAN_PAIR_SPLITS if mode == "add" and not ordered else (1,)):
@@ -485,8 +499,22 @@ def gemm_plan(T: int, N: int, K: int, mode: str, allow_pairs: bool = True) -> Tu
             cost = max(waves * (((k_tiles + split - 1) // split) * _PLAN_PAIR_STEP_US + _PLAN_PAIR_TILE_US), stream)
             if split > 1:
                 cost += _PLAN_PAIR_US_PER_ADD * T * N * split
-            best = min(best, (cost, True, split))
-    return best[1], best[2]
+            best = min(best, (cost, True, split, 0))
+        pairs = sms // 2
+        whole, tail = clusters // pairs * pairs, clusters % pairs
+        if mode == "add" and not ordered and whole and tail:
+            # more than a wave of tiles and a last wave that is not full: only that wave's tiles are cut, into
+            # slices of at least _PLAN_TAIL_MIN_K k-tiles (shorter pieces are all epilogue)
+            for split in _PLAN_PAIR_SPLITS[1:] + (8,):
+                per = (k_tiles + split - 1) // split
+                if per < _PLAN_TAIL_MIN_K:
+                    break
+                rounds = (tail * split + pairs - 1) // pairs
+                cost = max(whole // pairs * (k_tiles * _PLAN_PAIR_STEP_US + _PLAN_PAIR_TILE_US)
+                           + rounds * (per * _PLAN_PAIR_STEP_US + _PLAN_PAIR_TILE_US), stream)
+                cost += _PLAN_PAIR_US_PER_ADD * T * N * split * tail / clusters
+                best = min(best, (cost, True, split, whole))
+    return best[1], best[2], best[3]
 
 
 def _defines_from_env(name: str) -> dict:
@@ -508,11 +536,13 @@ _ATTN_TC = os.environ.get("JANUS_ATTN_TC", "1") != "0"     # 0: prompts attend o
 
 
 def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "store",
-              split_k: Optional[int] = None, pair: Optional[bool] = None) -> None:
+              split_k: Optional[int] = None, pair: Optional[bool] = None, whole_tiles: int = 0) -> None:
     """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation; w packed (`pack_weight`).
     mode "store": y[T, N] = result (bf16 or float32 by y's dtype);
     mode "add":   y[T, N] += result, y float32 (K may be split, sums meet by atomic adds);
-    mode "swiglu": w a gated pair (`pack_gated`), y[T, N] = silu(gate) * up in bf16."""
+    mode "swiglu": w a gated pair (`pack_gated`), y[T, N] = silu(gate) * up in bf16.
+    `split_k`, `pair`, `whole_tiles`: as `gemm_plan_whole` picks them unless given (`whole_tiles`: CTA pairs
+    only, the first so many 256 x 256 output tiles of an adding product stay uncut)."""
     T, K = x.shape
     _need(x, "gemm x", torch.bfloat16)
     _need(y, "gemm y")
@@ -538,7 +568,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
         raise KernelError(f"gemm {mode}: output must be {want} [{T}, {N}], got {y.dtype} {tuple(y.shape)}")
     if split_k is None:
         if pair is not True:
-            pair, split_k = gemm_plan(T, N, K, mode, allow_pairs=pair is not False)
+            pair, split_k, whole_tiles = gemm_plan_whole(T, N, K, mode, allow_pairs=pair is not False)
         else:
             split_k = 1
         if code != 2:
@@ -548,7 +578,7 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     if pair:
         _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair(
             _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
-            int(split_k), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
+            int(split_k), int(whole_tiles), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
         return
     partials = tickets = None
     if split_k > 1 and _deterministic[0]:

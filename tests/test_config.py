@@ -113,7 +113,9 @@ def test_product_plan_picks_a_kernel_and_slices_that_the_kernels_take():
     assert ops.gemm_plan(64, 4096, 4096, "add") == (False, 4)       # more tokens, more adds: one wave of 16 steps
     assert ops.gemm_plan(256, 4096, 4096, "add") == (False, 4)       # 32 output tiles: K in four slices
     assert ops.gemm_plan(512, 4096, 4096, "add") == (True, 2)        # 32 tiles of CTA pairs: K in two
-    assert ops.gemm_plan(2048, 4096, 14336, "add") == (True, 1)
+    assert ops.gemm_plan(2048, 4096, 4096, "add") == (True, 1)        # 128 tiles on 74 pairs, but slices of 16 k-tiles are all epilogue
+    # 128 tiles of 224 k-tiles on 74 pairs: a wave of whole tiles, then the other 54 in 4 slices each
+    assert ops.gemm_plan_whole(2048, 4096, 14336, "add") == (True, 4, 74)
     assert ops.gemm_plan(2048, 14336, 4096, "swiglu") == (True, 1)
     assert ops.gemm_plan(64, 14336, 4096, "swiglu") == (False, 1)
     ops.set_deterministic(True)          # slices are summed in order: only the single-CTA kernel cuts K then

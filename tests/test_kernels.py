@@ -386,7 +386,7 @@ def test_gemm_bf16_swiglu(ops, T, I, K):
 
 
 @pytest.mark.parametrize("T", [70, 130, 256, 300, 513, 1100])
-@pytest.mark.parametrize("N, K", [(200, 120), (256, 64), (1000, 320), (640, 4096)])
+@pytest.mark.parametrize("N, K", [(200, 120), (256, 64), (1000, 320), (640, 4096), (4096, 1096)])
 def test_gemm_bf16_cta_pairs(ops, T, N, K):
     """The cta_group::2 kernel (256 weight rows per CTA pair, each CTA loads half of the token tile):
     ragged token counts, widths that are no multiple of 256, a K tail, several tiles per pair."""
@@ -406,6 +406,11 @@ def test_gemm_bf16_cta_pairs(ops, T, N, K):
     for split in (2, 5, 1000):                    # slices of K meet by atomic adds; never more slices than k-tiles
         acc = base.clone()
         ops.gemm_bf16(x, w, acc, mode="add", pair=True, split_k=split)
+        close(acc, ref + base.double().cpu(), 2e-5)
+    tiles = ((T + 255) // 256) * ((N + 255) // 256)
+    for whole in sorted({1, tiles // 2, tiles - 1, tiles, tiles + 5} - {0}):   # the first tiles whole, the others in slices
+        acc = base.clone()
+        ops.gemm_bf16(x, w, acc, mode="add", pair=True, split_k=3, whole_tiles=whole)
         close(acc, ref + base.double().cpu(), 2e-5)
     ops.check_kernel_status(torch.device(DEV))
 
