@@ -390,7 +390,9 @@ PROMPT_STEPS = "1x96,1x128,1x256,1x384,1x512,1x768,1x1024,1x1536,1x2048,1x4096,4
 
 def run_prompt_lengths(layers, which):
     """Prompt steps of 96 to 4,096 tokens at the 8B layer sizes (fewer layers, named in each line): device
-    time of `Model.step` with the logits of the last token, median of 5 after 3 warm-ups.  One JSON line per
+    time of `Model.step` with the logits of the last token, median of 5 after 3 warm-ups.  The device idles
+    50 ms before each measured step (JANUS_BENCH_GAP_S; long steps run into the power cap, and the clocks need
+    the pause to come back; steps of up to 256 tokens measure 5 to 8 % faster back to back).  One JSON line per
     length; nothing here is the headline."""
     import torch
 
@@ -408,7 +410,7 @@ def run_prompt_lengths(layers, which):
             entries = [StepEntry(s, torch.randint(0, cfg["vocab_size"], (T,), generator=g).tolist(), [T - 1])
                        for s in slots]
             torch.cuda.synchronize()
-            time.sleep(0.05)
+            time.sleep(float(os.environ.get("JANUS_BENCH_GAP_S", "0.05")))
             a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
             a.record()
             model.step(entries)
