@@ -89,7 +89,7 @@ def main(argv=None) -> int:
         ignore_eos=args.ignore_eos, batch_size=batch, return_reasons=True)
     if args.json:
         print(json.dumps({"tokens": out, "finish_reasons": reasons, "prefill_tokens_per_s": stats.prefill_tokens_per_s,
-                          "decode_tokens_per_s": stats.decode_tokens_per_s}))
+                          "decode_tokens_per_s": stats.decode_tokens_per_s, "graph_captures": stats.graph_captures}))
         return 0
     print("=== janus_b200 inference ===")
     print(f"Batch size: {batch}\nMax tokens per sequence: {args.max_tokens}\nTemperature: {args.temperature}\n")
@@ -98,7 +98,7 @@ def main(argv=None) -> int:
         print("    " + " ".join(map(str, o)))
     print(f"\nPrefill: {stats.prefill_tokens} tokens in {stats.prefill_ms:.1f} ms ({stats.prefill_tokens_per_s:.0f} tok/s)")
     print(f"Decode:  {stats.decode_tokens} tokens in {stats.decode_ms:.1f} ms ({stats.decode_tokens_per_s:.0f} tok/s, "
-          f"{stats.decode_steps} steps, {stats.batches} batches)")
+          f"{stats.decode_steps} steps, {stats.batches} batches, {stats.graph_captures} decode graphs recorded)")
     return 0
 
 
