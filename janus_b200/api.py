@@ -11,6 +11,7 @@ from typing import Callable, List, Optional, Sequence
 
 import torch
 
+from . import log
 from .cache import PAGE_SIZE
 from .config import read_config_json, resolve_architecture
 from .engine.generate import run_generation
@@ -96,6 +97,24 @@ class Model:
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         return self.engine.step(entries)
 
+    def profile(self, prompts: Sequence[Sequence[int]]) -> dict:
+        """Where a step's time goes: the prompts' step and one decode step after it, each with its kernels
+        launched one by one and timed by CUDA events (`Engine.profile_step`).  Takes and gives back one slot a
+        prompt.  Returns {"prefill": {...}, "decode": {...}} with a row per kernel face: launches and
+        milliseconds.  Decode steps of `generate` replay the same kernels from a CUDA graph, a little faster."""
+        slots = [self.alloc_slot() for _ in prompts]
+        try:
+            prefill = self.engine.profile_step([StepEntry(s, [int(t) for t in p], (len(p) - 1,))
+                                                for s, p in zip(slots, prompts)])
+            decode = self.engine.profile_step([StepEntry(s, (int(p[-1]),), (0,)) for s, p in zip(slots, prompts)])
+        finally:
+            for s in slots:
+                self.free_slot(s)
+        self.check()
+        return {"prefill": prefill, "decode": decode,
+                "how": "kernels launched one by one; a kernel's time is the time between the events after the "
+                       "launch before it and after its own on the stream"}
+
     def check(self) -> None:
         """Waits for the device and raises if a tensor-core kernel gave up on a wait (its result would
         be incomplete).  `generate` calls it before it returns; a caller of `step` calls it when it
@@ -142,6 +161,10 @@ class Model:
             cache.n_free_slots, PAGE_SIZE, callback)
         stats.graph_captures = self.engine.graph_captures - captures_before
         self.check()
+        log.log("info", f"generate: {stats.requests} requests in {stats.batches} batches; prefill {stats.prefill_tokens} "
+                        f"tokens at {stats.prefill_tokens_per_s:.0f} tok/s; decode {stats.decode_tokens} tokens in "
+                        f"{stats.decode_steps} steps at {stats.decode_tokens_per_s:.0f} tok/s; "
+                        f"{stats.graph_captures} decode graphs recorded")
         if return_reasons:
             return outputs, reasons, stats
         return outputs, stats
@@ -160,6 +183,12 @@ def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_se
         model.load(checkpoint_factory(arch, config))
         engine = Engine(model, EngineOptions(max_tokens=max_tokens, max_seq_len=max_seq_len,
                                              max_slots=max_slots, use_graphs=use_graphs))
+    if log.enabled("info"):
+        cache = engine.cache
+        log.log("info", f"loaded {type(config).__name__}: {len(model.layers)} layers, hidden {model.hidden_size}, "
+                        f"vocabulary {model.vocab_size}, dtype {torch_dtype}; cache of {cache.n_pages} pages of "
+                        f"{PAGE_SIZE} tokens in {len(cache.groups)} group(s), {cache.n_slots} slots, longest sequence "
+                        f"{engine.max_seq_len}; CUDA graphs {'on' if use_graphs else 'off'}")
     return Model(config, engine)
 
 

@@ -60,6 +60,9 @@ def main(argv=None) -> int:
                     help="the folder holds only config.json: run it with random weights")
     ap.add_argument("--seed-weights", type=int, default=0, help="seed of --random-weights")
     ap.add_argument("--json", action="store_true", help="print one JSON object instead of text")
+    ap.add_argument("--profile", metavar="FILE", default=None,
+                    help="after generating, time the kernels of the first batch's prompt step and of one decode "
+                         "step one by one and write them to FILE as JSON")
     args = ap.parse_args(argv)
 
     prompts = [parse_prompt(p) for p in list(args.prompts) + args.prompt_ids]
@@ -87,6 +90,9 @@ def main(argv=None) -> int:
         prompts, max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
         repetition_penalty=args.repetition_penalty, seed=args.seed, stop_token_ids=args.stop_id,
         ignore_eos=args.ignore_eos, batch_size=batch, return_reasons=True)
+    if args.profile:
+        with open(args.profile, "w") as f:
+            json.dump(model.profile(prompts[:batch]), f, indent=1)
     if args.json:
         print(json.dumps({"tokens": out, "finish_reasons": reasons, "prefill_tokens_per_s": stats.prefill_tokens_per_s,
                           "decode_tokens_per_s": stats.decode_tokens_per_s, "graph_captures": stats.graph_captures}))

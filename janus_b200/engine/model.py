@@ -11,6 +11,7 @@ from typing import Dict, List, Optional
 
 import torch
 
+from .. import log
 from ..kernels import ops
 from ..parts.base import CacheSpec, LayerSpec, ModelSpec, make_part
 from ..parts.linear import Linear
@@ -35,7 +36,7 @@ class DecoderModel:
         self.embedding_transforms = [make_part("transform", ps, dtype, device) for ps in spec.embedding_transforms]
         self.logit_transforms = [make_part("transform", ps, dtype, device) for ps in spec.logit_transforms]
         self.embedding: Optional[torch.Tensor] = None
-        self.head = Linear(spec.hidden_size, spec.vocab_size, dtype, device)
+        self.head = Linear(spec.hidden_size, spec.vocab_size, dtype, device, name="head")
         self.schedule = list(spec.schedule)
         for place, e in enumerate(self.schedule):
             if not 0 <= e.layer < len(self.layers):
@@ -100,7 +101,8 @@ class DecoderModel:
             transform.forward(residual, ctx)
         for place, entry in enumerate(self.schedule):
             view = ctx.cache_view(place if entry.reads_cache_of is None else entry.reads_cache_of)
-            self.layers[entry.layer].forward(residual, ctx, view, writes_cache=entry.reads_cache_of is None)
+            with log.nvtx_range(f"place {place}: layer {entry.layer}"):
+                self.layers[entry.layer].forward(residual, ctx, view, writes_cache=entry.reads_cache_of is None)
         n_want = want_rows.shape[0]
         if n_want == 0:
             return

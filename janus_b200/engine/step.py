@@ -17,6 +17,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import log
 from ..cache import PAGE_SIZE, CacheFull, CacheView, GroupStepView, SequenceCache
 from ..kernels import ops
 from .model import DecoderModel
@@ -244,8 +245,12 @@ class Engine:
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
         self._reserve(entries)
+        if log.enabled("debug"):
+            log.log("debug", f"step: {len(entries)} sequences, {sum(len(e.tokens) for e in entries)} tokens, "
+                             f"{sum(len(e.want) for e in entries)} wanted rows")
         if (self.options.use_graphs and all(len(e.tokens) == 1 and tuple(e.want) == (0,) for e in entries)):
-            logits = self._graph_decode(entries, None)[0]
+            with log.nvtx_range("decode step (graph)"):
+                logits = self._graph_decode(entries, None)[0]
             if not borrow:
                 logits = logits.clone()
         else:
@@ -259,10 +264,11 @@ class Engine:
             # the faces' checks of device, dtype and shape are made the first time only
             shape = (ctx.n_tokens, ctx.n_seqs, ctx.max_q_len, ctx.max_kv_len_bound, want_rows.shape[0])
             if shape in self._checked_shapes:
-                with ops.unchecked():
+                with ops.unchecked(), log.nvtx_range(f"step of {ctx.n_tokens} tokens"):
                     self.model.forward(ctx, want_rows, logits)
             else:
-                self.model.forward(ctx, want_rows, logits)
+                with log.nvtx_range(f"step of {ctx.n_tokens} tokens (first of its shape)"):
+                    self.model.forward(ctx, want_rows, logits)
                 if len(self._checked_shapes) >= 4096:
                     self._checked_shapes.clear()
                 self._checked_shapes.add(shape)
@@ -270,6 +276,31 @@ class Engine:
         for e in entries:
             self.cache.advance(e.slot, len(e.tokens))
         return logits
+
+    def profile_step(self, entries: Sequence[StepEntry]) -> dict:
+        """Run one step with its kernels launched one by one and timed by CUDA events: which kernels the step
+        launches, how often, and how long the stream spends on each.  The step counts (the cache takes its
+        tokens).  Returns {"tokens", "sequences", "kind", "total_ms", "kernels": [{"name", "launches", "ms"}]}
+        with the kernels in the order of their first launch."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        graphs, self.options.use_graphs = self.options.use_graphs, False
+        try:
+            torch.cuda.synchronize(self.device)
+            with ops.trace_launches() as events:
+                self.step(entries)
+            torch.cuda.synchronize(self.device)
+        finally:
+            self.options.use_graphs = graphs
+        rows: Dict[str, list] = {}
+        for (_, _, before), (name, kernels, after) in zip(events, events[1:]):
+            row = rows.setdefault(name, [0, 0.0])
+            row[0] += kernels
+            row[1] += before.elapsed_time(after)
+        lens = [len(e.tokens) for e in entries]
+        return {"tokens": sum(lens), "sequences": len(entries),
+                "kind": "decode" if all(n == 1 for n in lens) else "prompt",
+                "total_ms": round(events[0][2].elapsed_time(events[-1][2]), 4) if len(events) > 1 else 0.0,
+                "kernels": [{"name": k, "launches": v[0], "ms": round(v[1], 4)} for k, v in rows.items()]}
 
     def decode_sample(self, slots: Sequence[int], tokens: Sequence[int], sampler, requests: Sequence[int],
                       steps: Sequence[int]) -> torch.Tensor:

@@ -126,9 +126,33 @@ def launch_count() -> int:
     return _launches[0]
 
 
+_trace = [None]    # while a step is profiled: the list that takes (face, kernels, event after the launch)
+
+
+@contextlib.contextmanager
+def trace_launches():
+    """Within the scope every launch of this library is followed by a CUDA event on the current stream; the
+    list that is handed out holds (face, kernels, event), led by an event recorded on entry.  The time between
+    two events is the time the stream spent on the launch between them (kernels run one after another on a
+    stream; what overlaps under programmatic dependent launch is counted for the later kernel)."""
+    before = _trace[0]
+    start = torch.cuda.Event(enable_timing=True)
+    start.record()
+    events = [("start", 0, start)]
+    _trace[0] = events
+    try:
+        yield events
+    finally:
+        _trace[0] = before
+
+
 def _check(code: int, what: str, kernels: int = 1) -> None:
     if code == 0:
         _launches[0] += kernels
+        if _trace[0] is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            _trace[0].append((what, kernels, ev))
         return
     if code >= 10000:
         names = {10001: "size not supported (see stderr)", 10002: "dtype not supported",
@@ -237,15 +261,15 @@ def rope_cache_write(qkv: torch.Tensor, q_out: torch.Tensor, cos_sin: Optional[t
 
 
 # -- float32 matrix product and attention ------------------------------------------
-def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool = False) -> None:
-    """y[T, N] (+)= x[T, K] . w[N, K]^T in true float32"""
+def gemm_f32(x: torch.Tensor, w: torch.Tensor, y: torch.Tensor, accumulate: bool = False, label: str = "") -> None:
+    """y[T, N] (+)= x[T, K] . w[N, K]^T in true float32 (`label`: what a profile of a step calls this product)"""
     T, K = x.shape
     N = w.shape[0]
     _need(x, "gemm x", torch.float32)
     _need(w, "gemm w", torch.float32, (N, K))
     _need(y, "gemm y", torch.float32, (T, N))
     _check(_lib("gemm_f32").jb_gemm_f32(_ptr(x), _ptr(w), _ptr(y), T, N, K, K, N, int(accumulate), _stream()),
-           "gemm_f32")
+           "gemm_f32 " + label if label else "gemm_f32")
 
 
 def attention_f32(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -536,7 +560,8 @@ _ATTN_TC = os.environ.get("JANUS_ATTN_TC", "1") != "0"     # 0: prompts attend o
 
 
 def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "store",
-              split_k: Optional[int] = None, pair: Optional[bool] = None, whole_tiles: int = 0) -> None:
+              split_k: Optional[int] = None, pair: Optional[bool] = None, whole_tiles: int = 0,
+              label: str = "") -> None:
     """bf16 x[T, K] . w[N, K]^T on tcgen05 with float32 accumulation; w packed (`pack_weight`).
     mode "store": y[T, N] = result (bf16 or float32 by y's dtype);
     mode "add":   y[T, N] += result, y float32 (K may be split, sums meet by atomic adds);
@@ -578,7 +603,8 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     if pair:
         _check(_lib("gemm_bf16_tc2", _defines_key(_PAIR_DEFINES), _PAIR_DEFINES).jb_gemm_bf16_pair(
             _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
-            int(split_k), int(whole_tiles), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16_pair")
+            int(split_k), int(whole_tiles), _ptr(kernel_status(x.device)), _stream()),
+            "gemm_bf16_pair " + label if label else "gemm_bf16_pair")
         return
     partials = tickets = None
     if split_k > 1 and _deterministic[0]:
@@ -595,7 +621,8 @@ def gemm_bf16(x: torch.Tensor, w: PackedWeight, y: torch.Tensor, mode: str = "st
     _check(_lib("gemm_bf16_tc", _defines_key(_GEMM_DEFINES), _GEMM_DEFINES).jb_gemm_bf16(
         _ptr(x), _ptr(w.tiles), w.n_tiles, w.up_tile_offset, _ptr(y), T, N, K, N, code,
         int(split_k), _ptr(partials), 0 if partials is None else partials.numel(), _ptr(tickets),
-        0 if tickets is None else tickets.numel(), _ptr(kernel_status(x.device)), _stream()), "gemm_bf16")
+        0 if tickets is None else tickets.numel(), _ptr(kernel_status(x.device)), _stream()),
+        "gemm_bf16 " + label if label else "gemm_bf16")
 
 
 def gemm_qkv_rope_supported(T: int, hd: int) -> bool:

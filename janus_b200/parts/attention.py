@@ -55,9 +55,9 @@ class GQAttention(Mixer):
         # layers that name the same position encoding share one object (one table on the device)
         self.position = shared_part("position", position, dtype, device) if position is not None else None
         self.q_width, self.kv_width = num_heads * head_dim, num_kv_heads * head_dim
-        self.qkv = Linear(hidden_size, self.q_width + 2 * self.kv_width, dtype, device)
+        self.qkv = Linear(hidden_size, self.q_width + 2 * self.kv_width, dtype, device, name="qkv")
         self.q_only: Optional[Linear] = None             # view of the q rows, for layers that read another cache
-        self.o = Linear(self.q_width, hidden_size, dtype, device)
+        self.o = Linear(self.q_width, hidden_size, dtype, device, name="o")
 
     def cache_spec(self) -> KVSpec:
         return KVSpec(self.nkv, self.hd, self.window)

@@ -15,7 +15,7 @@ class SwiGLUFeedForward(FeedForward):
         self.hidden_size, self.intermediate_size = hidden_size, intermediate_size
         self.dtype, self.device = dtype, device
         self.gate_up = GatedLinear(hidden_size, intermediate_size, dtype, device)
-        self.down = Linear(intermediate_size, hidden_size, dtype, device)
+        self.down = Linear(intermediate_size, hidden_size, dtype, device, name="down")
 
     def weight_shapes(self):
         return {"gate": ((self.intermediate_size, self.hidden_size), "normal"),

@@ -31,10 +31,12 @@ class Linear:
     """One weight matrix, possibly the row-wise stack of several tensors of the
     checkpoint (q, k, v stacked so that one product serves all three)."""
 
-    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device):
+    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device,
+                 name: str = ""):
         _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
+        self.name = name     # what a profile of a step calls this product
         self.weight = None   # float32: [out, in] row-major; bfloat16: ops.PackedWeight
 
     def load(self, tensors: Sequence[torch.Tensor]) -> None:
@@ -55,7 +57,7 @@ class Linear:
 
     def first_rows(self, rows: int) -> "Linear":
         """The product with the first `rows` output features only (shares storage)."""
-        sub = Linear(self.in_features, rows, self.dtype, self.device)
+        sub = Linear(self.in_features, rows, self.dtype, self.device, self.name)
         sub.weight = self.weight.first_rows(rows) if self.dtype == torch.bfloat16 else self.weight[:rows]
         return sub
 
@@ -68,7 +70,7 @@ class Linear:
     # y = x W^T, stored in y's dtype (engine dtype, or float32 for logits)
     def forward(self, x: torch.Tensor, y: torch.Tensor, y_is_zero: bool = False) -> None:
         if self.dtype == torch.float32:
-            ops.gemm_f32(x, self.weight, y, accumulate=False)
+            ops.gemm_f32(x, self.weight, y, accumulate=False, label=self.name)
         elif self.meets_by_adds(x.shape[0], y.dtype):
             # few tokens and few output tiles: slices of K run as CTAs of their own and meet in y
             if y_is_zero:
@@ -77,26 +79,28 @@ class Linear:
                 ops.zero_f32(y)
             else:
                 y.zero_()
-            ops.gemm_bf16(x, self.weight, y, mode="add")
+            ops.gemm_bf16(x, self.weight, y, mode="add", label=self.name)
         else:
-            ops.gemm_bf16(x, self.weight, y, mode="store")
+            ops.gemm_bf16(x, self.weight, y, mode="store", label=self.name)
 
     # residual += x W^T, the sum made in float32
     def forward_add(self, x: torch.Tensor, residual: torch.Tensor) -> None:
         if self.dtype == torch.float32:
-            ops.gemm_f32(x, self.weight, residual, accumulate=True)
+            ops.gemm_f32(x, self.weight, residual, accumulate=True, label=self.name)
         else:
-            ops.gemm_bf16(x, self.weight, residual, mode="add")
+            ops.gemm_bf16(x, self.weight, residual, mode="add", label=self.name)
 
 
 class GatedLinear:
     """out = silu(x Wg^T) * (x Wu^T) with Wg stacked over Wu
     (crates/janus-engine/src/model/block.rs:383-430)."""
 
-    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device):
+    def __init__(self, in_features: int, out_features: int, dtype: torch.dtype, device: torch.device,
+                 name: str = "gate_up"):
         _check_width(in_features, dtype)
         self.in_features, self.out_features = in_features, out_features
         self.dtype, self.device = dtype, device
+        self.name = name
         self.weight = None   # float32: [2 * out, in] row-major; bfloat16: a packed gated pair
         self._stacked = None  # bfloat16: the same tiles as one plain matrix (gate rows, then up rows)
 
@@ -112,14 +116,14 @@ class GatedLinear:
     def forward(self, x: torch.Tensor, out: torch.Tensor, ctx) -> None:
         if self.dtype == torch.float32:
             gu = ctx.workspace.get("gate_up", (x.shape[0], 2 * self.out_features), torch.float32)
-            ops.gemm_f32(x, self.weight, gu, accumulate=False)
+            ops.gemm_f32(x, self.weight, gu, accumulate=False, label=self.name)
             ops.swiglu(gu, out)
         elif ops.gated_runs_unfused(x.shape[0], self.out_features):
             # few tokens, narrow layer: twice the tiles stream the weights as a plain product; the gate is applied after
             if self._stacked is None:
                 self._stacked = self.weight.stacked()
             gu = ctx.workspace.get("gate_up", (x.shape[0], self._stacked.rows), torch.float32)
-            ops.gemm_bf16(x, self._stacked, gu, mode="store", pair=False)
+            ops.gemm_bf16(x, self._stacked, gu, mode="store", pair=False, label=self.name)
             ops.swiglu_f32_to_bf16(gu, out, 128 * self.weight.up_tile_offset)
         else:
-            ops.gemm_bf16(x, self.weight, out, mode="swiglu")
+            ops.gemm_bf16(x, self.weight, out, mode="swiglu", label=self.name)

@@ -250,3 +250,16 @@ def test_declared_argument_types_match_the_exported_c_functions():
         assert found.get(name) == signature, f"{name}: declared {signature}, the source says {found.get(name)}"
     launched = {n for n, letters in found.items() if letters}      # everything but the head_dim queries
     assert launched - set(ops._SIGNATURES) <= {"jb_attention_bf16_decode_noalloc"}
+
+
+def test_log_levels():
+    from janus_b200 import log
+    assert log.parse_level("debug") == 3 and log.parse_level("INFO") == 2 and log.parse_level(None) == 1
+    assert log.parse_level("nonsense") == log.parse_level("warn")
+    log.set_level("error")
+    try:
+        assert log.enabled("error") and not log.enabled("warn") and not log.enabled("debug")
+    finally:
+        log.set_level("warn")
+    with log.nvtx_range("nothing happens without JANUS_NVTX=1"):
+        pass

@@ -183,3 +183,27 @@ def test_errors_before_launch(tmp_path):
     model.engine.cache.check()
     model.free_slot(s)
     assert model.step([StepEntry(t, [1] * 10, [9])]).shape == (1, 256)
+
+
+def test_profile_lists_the_kernels_of_a_prompt_step_and_of_a_decode_step(tmp_path):
+    """`Model.profile` (the command line's --profile): every kernel face of the two steps with its launches and
+    its time on the stream; the times add up to the step's; the slots come back; logits are untouched by it."""
+    model, (cfg, w) = load(tmp_path, "A", "bfloat16")
+    prompts = [random_tokens(n, 256, 80 + n) for n in (70, 9)]
+    before, _ = model.generate(prompts, max_tokens=4, ignore_eos=True)
+    prof = model.profile(prompts)
+    for part, kind, tokens in (("prefill", "prompt", 79), ("decode", "decode", 2)):
+        step = prof[part]
+        assert step["kind"] == kind and step["tokens"] == tokens and step["sequences"] == 2
+        names = [k["name"] for k in step["kernels"]]
+        assert names[0] == "embed_gather" and "rmsnorm" in names
+        for product in ("qkv", "o", "gate_up", "down", "head"):
+            assert any(n.startswith("gemm_bf16") and n.endswith(" " + product) for n in names), (product, names)
+        assert any(n.startswith("attention") for n in names)
+        layers = cfg["num_hidden_layers"]
+        assert next(k for k in step["kernels"] if k["name"] == "rmsnorm")["launches"] == 2 * layers + 1
+        assert all(k["ms"] >= 0.0 and k["launches"] >= 1 for k in step["kernels"])
+        assert abs(sum(k["ms"] for k in step["kernels"]) - step["total_ms"]) < 1e-2 * max(1.0, step["total_ms"])
+    assert model.engine.cache.n_free_slots == model.engine.cache.n_slots
+    after, _ = model.generate(prompts, max_tokens=4, ignore_eos=True)
+    assert after == before
