@@ -543,7 +543,7 @@ def run_kernels(contexts=None, shape="8b"):
 
         us = timed(fn)
         print(json.dumps({"kernel": "decode attention + combine", "sequences": B, "keys": ctx,
-                          "splits": ops.decode_splits_for(B, NKV, cap * 64, 64), "us": round(us, 1),
+                          "splits": ops.decode_splits_for(B, NKV * ((NH // NKV + 15) // 16), cap * 64, 64, HD), "us": round(us, 1),
                           "kv_GBps": round(B * ctx * NKV * HD * 4 / us / 1e3, 1)}), flush=True)
 
     for B, L in (() if contexts else ((1, 2048), (1, 8192))):

@@ -715,22 +715,76 @@ def attention_bf16_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torc
         _stream()), "attention_bf16_prefill")
 
 
-def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: int) -> int:
-    """Splits of the key range per (sequence, kv head).  The kernel runs two CTAs per SM.  With at most
-    half as many (sequence, kv head) pairs as such places the keys are cut so that one wave of CTAs fills
-    them (at least about four pages of the longest sequence per split); with about as many pairs as
-    places one wave would leave no room to even out sequences of unequal length, so splits of 16 pages;
-    with more pairs than places only long sequences are cut (64 pages per split).  Measured at 8 kv
-    heads, 2,080 keys: 1 sequence 16 splits, 8 sequences 4, 64 sequences 1."""
-    pages = max(1, (max_kv_len + page_size - 1) // page_size)
+# Constants of the estimate in `decode_splits_for` (microseconds, bytes per microsecond), read off measurements
+# of the decode kernel at head sizes 64 and 128 (1 to 64 sequences of 1,024 to 4,000 keys, 8 and 40 kv heads,
+# 1 to 8 splits): they rank split counts, they forecast no time.
+_SPLIT_CTA_US = 3.0                 # a CTA's start, its queries, its last exchange and write
+_SPLIT_PAGE_US = {64: 0.6, 128: 0.85}   # a CTA alone walks a page of 64 keys in this time (head size up to 64 / above)
+_SPLIT_HBM_BYTES_PER_US = 6.2e6
+_SPLIT_COMBINE_US = 3.0             # the kernel that joins the splits, plus 0.05 a split
+_SPLIT_SHARED_SM = 0.2              # a CTA that shares its SM with another walks its pages this much slower
+_SPLIT_CHOICES = (1, 2, 3, 4, 6, 8, 12, 16, 24, 32)
+
+
+def _decode_ctas_per_sm(head_dim: int, ctas: int, pages_per_cta: int) -> int:
+    """CTAs of the decode kernel that share an SM: its ring of pages is picked at the launch (in step with
+    `decode_stages_for` of csrc/attention_bf16.cu): three pages for large heads (two CTAs an SM at head size
+    128); small heads take two pages when there are more CTAs than fit at once (five an SM at head size 64),
+    five pages for few CTAs of many pages (two an SM), else three (three an SM)."""
+    ld = (head_dim + 15) // 16 * 16 + 8
+
+    def fit(stages: int) -> int:
+        smem = 18 * ld * 2 + max(2 * stages * 64 * ld * 2, (4 * 16 * (head_dim + 8) + 128) * 4)
+        return max(1, min(16, 228 * 1024 // (smem + 1024)))
+
+    if head_dim > 64:
+        return fit(3)
+    sms = SM_COUNT_TARGET // 2
+    if ctas > sms * fit(3):
+        return fit(2)
+    if ctas <= sms * fit(5) and pages_per_cta >= 8:
+        return fit(5)
+    return fit(3)
+
+
+@functools.lru_cache(maxsize=4096)
+def decode_splits_for(n_seqs: int, nkv_blocks: int, max_kv_len: int, page_size: int, head_dim: int = 128) -> int:
+    """Splits of the key range per (sequence, kv head), from an estimate of the kernel's time for each count.
+
+    A launch is `n_seqs * nkv_blocks * splits` CTAs of about `pages / splits` pages each; as many CTAs as fit the
+    SMs run at once (a wave).  A wave takes as long as its bytes need at the memory's rate, but no less than one
+    CTA needs to walk its pages (a little longer where CTAs share an SM); the waves add up, and more than one
+    split costs the kernel that joins them.  So few sequences want many splits (one sequence of 2,080 keys: 16), a batch that fills the SMs wants
+    none (64 sequences over 8 kv heads: 1), and a batch that overfills them a little wants its CTAs small, so
+    that the last wave is short (8 sequences over 40 kv heads, 320 CTAs for 296 places: 4 splits, 62 us against
+    76 us uncut).  `max_kv_len` is the bound a step was laid out for (a power of two of pages); sequences are
+    taken to be three quarters of it."""
+    cap_pages = max(1, (max_kv_len + page_size - 1) // page_size)
+    pages = max(1, (3 * cap_pages + 3) // 4)
     base = max(1, n_seqs * nkv_blocks)
-    places = SM_COUNT_TARGET
-    if base >= places:
-        return max(1, pages // 64)
-    wave = places // base
-    if wave < 2:
-        return max(1, pages // 16)
-    return max(1, min(wave, max(1, pages // 4)))
+    sms = SM_COUNT_TARGET // 2
+    page_us = _SPLIT_PAGE_US[64 if head_dim <= 64 else 128]
+    page_bytes = page_size * head_dim * 2 * 2
+    best = (float("inf"), 1)
+    for splits in _SPLIT_CHOICES:
+        if splits > 1 and splits > max(1, cap_pages // 2):
+            break
+        per = (pages + splits - 1) // splits
+        ctas = base * splits
+        places = sms * _decode_ctas_per_sm(head_dim, ctas, per)
+        alone = _SPLIT_CTA_US + per * page_us
+
+        def wave(n: int) -> float:      # n CTAs at once: on how many SMs, at the memory's rate or a CTA's own pace
+            sharing = 1.0 + _SPLIT_SHARED_SM * ((n + sms - 1) // sms - 1)
+            return max(alone * sharing, n * per * page_bytes / _SPLIT_HBM_BYTES_PER_US)
+
+        full, rest = divmod(ctas, places)
+        cost = full * wave(places) + (wave(rest) if rest else 0.0)
+        if splits > 1:
+            cost += _SPLIT_COMBINE_US + 0.05 * splits
+        if cost < best[0] - 1e-9:
+            best = (cost, splits)
+    return best[1]
 
 
 def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -752,7 +806,7 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
     _need(kv_len, "kv_len", torch.int32, (B,))
     n_rb = (nh // nkv + 15) // 16
     if n_splits is None:
-        n_splits = decode_splits_for(B, nkv * n_rb, max_kv_len, page_size)
+        n_splits = decode_splits_for(B, nkv * n_rb, max_kv_len, page_size, hd)
     part_o = part_ml = None
     if n_splits > 1:
         part_o = workspace.get("attn_part_o", (B * nh * n_splits * hd,), torch.float32)
