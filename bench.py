@@ -443,12 +443,14 @@ KERNEL_SHAPES = {   # hidden, heads, kv heads, head size, intermediate, vocabula
 }
 
 
-def run_kernels(contexts=None, shape="8b"):
+def run_kernels(contexts=None, shape="8b", head_sizes=None):
     """The step's hot kernels alone at the 8B layer shapes, for the roofline figures under profiles/:
     each is captured 24 times into one CUDA graph (as the engine runs them: back to back, programmatic
     dependent launch) over several copies of its weights or cache, so that every launch reads from DRAM,
     and timed with CUDA events around 5 replays.  One line per kernel; nothing here is the headline.
-    With `contexts` (key counts), decode attention alone at those contexts, for 1, 8 and 64 sequences."""
+    With `contexts` (key counts), decode attention alone at those contexts, for 1, 8 and 64 sequences.
+    With `head_sizes`, prompt attention alone at those head sizes (the shape's heads, 2,048 tokens) on both of
+    its kernels: tcgen05 (head sizes up to 128) and mma.sync."""
     import math
 
     import torch
@@ -513,7 +515,7 @@ def run_kernels(contexts=None, shape="8b"):
                           "weights_GBps": round(rows * K * 2 / us / 1e3, 1),
                           "TFLOPs": round(2 * T * rows * K / us / 1e6, 1)}), flush=True)
 
-    if not contexts:
+    if not contexts and not head_sizes:
         for T in (8, 64, 2048):
             product("qkv", T, (NH + 2 * NKV) * HD, H, "store")
             product("o (add)", T, H, NH * HD, "add")
@@ -522,6 +524,8 @@ def run_kernels(contexts=None, shape="8b"):
         product("lm_head", 8, V, H, "store", copies=3)
 
     cases = [(b, c) for c in contexts for b in (1, 8, 64) if b * c <= 1 << 21] if contexts else ((1, 2080), (8, 2080), (64, 2080))
+    if head_sizes:
+        cases = ()
     for B, ctx in cases:
         pages = (ctx + 63) // 64
         n_pages = B * pages
@@ -546,7 +550,26 @@ def run_kernels(contexts=None, shape="8b"):
                           "splits": ops.decode_splits_for(B, NKV * ((NH // NKV + 15) // 16), cap * 64, 64, HD), "us": round(us, 1),
                           "kv_GBps": round(B * ctx * NKV * HD * 4 / us / 1e3, 1)}), flush=True)
 
-    for B, L in (() if contexts else ((1, 2048), (1, 8192))):
+    for hd in head_sizes or ():
+        B, L = 1, 2048
+        pages = L // 64
+        kc = torch.randn(B * pages, NKV, 64, hd, device=dev).to(torch.bfloat16)
+        vc = torch.randn_like(kc)
+        table = torch.arange(B * pages, device=dev, dtype=torch.int32).view(B, pages)
+        q = torch.randn(B * L, NH * hd, device=dev).to(torch.bfloat16)
+        out = torch.empty_like(q)
+        q_start = torch.arange(B + 1, device=dev, dtype=torch.int32) * L
+        kv_len = torch.full((B,), L, device=dev, dtype=torch.int32)
+        faces = [("mma.sync", ops.attention_bf16_prefill)]
+        if ops.attention_tc_supported(NH, NKV, hd):
+            faces.insert(0, ("tcgen05", ops.attention_tc_prefill))
+        for name, face in faces:
+            us = timed(lambda: face(q, kc, vc, out, table, q_start, kv_len, B, L, NH, NKV, hd, 64, 0,
+                                    1 / math.sqrt(hd)), reps=6)
+            print(json.dumps({"kernel": f"prefill attention ({name})", "head_size": hd, "tokens": L,
+                              "us": round(us, 1),
+                              "TFLOPs": round(B * 4 * NH * hd * L * (L + 1) / 2 / us / 1e6, 1)}), flush=True)
+    for B, L in (() if contexts or head_sizes else ((1, 2048), (1, 8192))):
         pages = (L + 63) // 64
         kc = torch.randn(B * pages, NKV, 64, HD, device=dev).to(torch.bfloat16)
         vc = torch.randn_like(kc)
@@ -700,6 +723,8 @@ def main():
                     help="time the step's hot kernels alone at the 8B layer shapes (one JSON line each)")
     ap.add_argument("--contexts", default=None, metavar="KEYS,...",
                     help="with --kernels: decode attention alone at these context lengths (1 and 8 sequences)")
+    ap.add_argument("--head-sizes", default=None, metavar="DIMS,...",
+                    help="with --kernels: prompt attention alone at these head sizes, on each kernel that takes them")
     ap.add_argument("--kernel-shape", default="8b", choices=sorted(KERNEL_SHAPES),
                     help="with --kernels: the layer sizes (default: the 8B shape)")
     ap.add_argument("--plan-check", action="store_true",
@@ -723,7 +748,8 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.kernels:
-        run_kernels([int(c) for c in args.contexts.split(",")] if args.contexts else None, args.kernel_shape)
+        run_kernels([int(c) for c in args.contexts.split(",")] if args.contexts else None, args.kernel_shape,
+                    [int(c) for c in args.head_sizes.split(",")] if args.head_sizes else None)
         return 0
     if args.plan_check:
         run_plan_check()

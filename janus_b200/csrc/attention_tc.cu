@@ -1,8 +1,11 @@
 // Causal grouped-query flash attention for prefill on the 5th-generation tensor
-// cores (tcgen05) of sm_100a, over the paged cache.  Built for one head size
-// (-DJB_HEAD_DIM = 64 or 128) and any number of query heads per kv head up to 128: a tile holds
+// cores (tcgen05) of sm_100a, over the paged cache.  Built for a row of 64 or 128 dims in shared memory
+// (-DJB_HEAD_DIM); the head size itself is an argument, any multiple of 8 up to that: the tensor maps
+// have the true extent, so the copy engine fills the rest of a row with zeros, the score product skips
+// the 16-dim steps that are all zero, the P.V product has N = the head size rounded up to 16, and the
+// epilogue stores the true columns only.  Any number of query heads per kv head up to 128: a tile holds
 // floor(128 / G) tokens x G heads, and the rows left over (2 of 128 with 3, 6 or 7 heads per kv head)
-// belong to no token.  Other head sizes take the mma.sync kernel of attention_bf16.cu.
+// belong to no token.  Larger head sizes take the mma.sync kernel of attention_bf16.cu.
 //
 // Two kernels.  prefill_tc_kernel: one CTA owns a tile of 128 rows = (token, query head of one kv group)
 // pairs of one sequence and walks its causal range of 64-key pages:
@@ -39,7 +42,7 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 constexpr int HD = JB_HEAD_DIM;
-static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel is built for head sizes 64 and 128");
+static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel is built for rows of 64 or 128 dims");
 constexpr int NH64 = HD / 64;          // 64-column halves of a row
 constexpr int BM = 128;                // rows per CTA = TMEM lanes
 constexpr int PAGE = 64;               // keys per block
@@ -269,7 +272,7 @@ template <int NT>
 __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
-    const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window,
+    const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
     float scale_log2, int* __restrict__ status) {
   constexpr int N_BARS = bars_for(NT), TMEM_COLS = NT * 256, TMEM_S0 = 0, TMEM_O0 = NT * 128;
   extern __shared__ uint8_t smem_raw[];
@@ -360,7 +363,8 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   } else if (active && warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc_s = instr_desc(PAGE, 0), idesc_o = instr_desc(HD, 1);
+      constexpr uint32_t idesc_s = instr_desc(PAGE, 0);
+      const uint32_t idesc_o = instr_desc((hd + 15) & ~15, 1);
       bool ok = mbar_wait(q_full, 0, status, 12);
       auto issue_s = [&](int j) -> bool {
         const int s = j % STAGES, b = j & 1;
@@ -374,7 +378,8 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
             const uint64_t a = desc_k_sw128(q_s + w * Q_BYTES + h * BM * 128), k = desc_k_sw128(stage + h * PAGE * 128);
 #pragma unroll
             for (int ks = 0; ks < 4; ++ks)
-              umma(tmem + TMEM_S0 + w * 128 + b * 64, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
+              if (h * 64 + ks * 16 < hd)   // dims past the head size are zeros in both operands
+                umma(tmem + TMEM_S0 + w * 128 + b * 64, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
           }
           umma_commit(s_full(w, b));   // a tile's softmax starts while the other tile's scores are computed
         }
@@ -442,6 +447,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
           const float corr = m_new == -CUDART_INF_F ? 1.0f : exp2f(m_ref - m_new);  // 0 if nothing was seen before
 #pragma unroll
           for (int c0 = 0; c0 < HD; c0 += 16) {
+            if (c0 >= hd) break;
             uint32_t r[16];
             tmem_ld16(lane_addr + o_col + c0, r);
             tmem_ld_wait();
@@ -466,9 +472,10 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     if (ok) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * HD;
+      bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * hd;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 16) {
+        if (c0 >= hd) break;
         uint32_t r[16];
         tmem_ld16(lane_addr + o_col + c0, r);   // warp-wide: rows without a token load too and store nothing
         tmem_ld_wait();
@@ -483,7 +490,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
           w1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
           w1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
           *reinterpret_cast<uint4*>(dst + c0) = w0;
-          *reinterpret_cast<uint4*>(dst + c0 + 8) = w1;
+          if (c0 + 8 < hd) *reinterpret_cast<uint4*>(dst + c0 + 8) = w1;
         }
       }
     }
@@ -515,7 +522,7 @@ static_assert(T2_SMEM <= 232448, "shared memory of one CTA");
 __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
-    const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int max_pages, int window,
+    const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
     float scale_log2, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -604,7 +611,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
   } else if (active && warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc_s = instr_desc(KB, 0), idesc_o = instr_desc(HD, 1);
+      constexpr uint32_t idesc_s = instr_desc(KB, 0);
+      const uint32_t idesc_o = instr_desc((hd + 15) & ~15, 1);
       bool ok = mbar_wait(q_full, 0, status, 12);
       auto issue_s = [&](int w, int j) -> bool {
         const int st = j & 1;
@@ -615,7 +623,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
           const uint64_t a = desc_k_sw128(q_s + w * Q_BYTES + h * BM * 128);
           const uint64_t k = desc_k_sw128(k_s + st * K128_BYTES + h * KB * 128);
 #pragma unroll
-          for (int ks = 0; ks < 4; ++ks) umma(tmem + w * 128, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
+          for (int ks = 0; ks < 4; ++ks)
+            if (h * 64 + ks * 16 < hd) umma(tmem + w * 128, a + 2 * ks, k + 2 * ks, idesc_s, (h | ks) ? 1u : 0u);
         }
         umma_commit(s_full(w));
         if (w == 1) umma_commit(k_empty + 8 * st);   // both tiles' score products have read these keys
@@ -682,6 +691,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
           const float corr = m_new == -CUDART_INF_F ? 1.0f : exp2f(m_ref - m_new);
 #pragma unroll
           for (int c0 = 0; c0 < HD; c0 += 16) {
+            if (c0 >= hd) break;
             uint32_t r[16];
             tmem_ld16(lane_addr + o_col + c0, r);
             tmem_ld_wait();
@@ -705,9 +715,10 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     if (ok) {
       tc_fence_after();
       const float inv = 1.0f / l;
-      bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * HD;
+      bf16* dst = out + ((size_t)(qs + tok_first + (valid ? tl : 0)) * nh + kvh * G + row % G) * hd;
 #pragma unroll
       for (int c0 = 0; c0 < HD; c0 += 16) {
+        if (c0 >= hd) break;
         uint32_t r[16];
         tmem_ld16(lane_addr + o_col + c0, r);
         tmem_ld_wait();
@@ -722,7 +733,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
           w1.z = pack_bf16(__uint_as_float(r[12]) * inv, __uint_as_float(r[13]) * inv);
           w1.w = pack_bf16(__uint_as_float(r[14]) * inv, __uint_as_float(r[15]) * inv);
           *reinterpret_cast<uint4*>(dst + c0) = w0;
-          *reinterpret_cast<uint4*>(dst + c0 + 8) = w1;
+          if (c0 + 8 < hd) *reinterpret_cast<uint4*>(dst + c0 + 8) = w1;
         }
       }
     }
@@ -755,14 +766,16 @@ EncodeTiledFn encode_fn() {
 
 JB_EXPORT int jb_attention_tc_head_dim() { return HD; }
 
-// q, out: [T, nh * hd] bf16; caches: [n_pages, nkv, 64, hd] bf16.  Needs nh / nkv <= 128.
+// q, out: [T, nh * hd] bf16; caches: [n_pages, nkv, 64, hd] bf16.  Needs nh / nkv <= 128 and a head size
+// that is a multiple of 8 (rows of 16 bytes for the tensor maps) up to the build's row.
 JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const void* v_cache, void* out,
                                       const int* block_table, const int* q_start, const int* kv_len, int T,
                                       int n_pages, int n_seqs, int max_q_len, int nh, int nkv, int hd,
                                       int page_size, int max_pages, int window, float scale, int* status,
                                       cudaStream_t stream) {
   if (n_seqs <= 0 || max_q_len <= 0 || T <= 0) return 0;
-  JB_REFUSE(hd != HD, "attention_tc: built for head_dim %d, called with %d", HD, hd);
+  JB_REFUSE(hd <= 0 || hd > HD || hd % 8 != 0,
+            "attention_tc: built for head sizes up to %d in steps of 8, called with %d", HD, hd);
   JB_REFUSE(page_size != PAGE, "attention_tc: page size %d (need %d)", page_size, PAGE);
   JB_REFUSE(nkv <= 0 || nh % nkv != 0, "attention_tc: %d heads are not a multiple of %d kv heads", nh, nkv);
   const int G = nh / nkv;
@@ -773,8 +786,9 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
   const int tpt = BM / G;
   CUtensorMap mq, mk, mv;
   {
-    const cuuint64_t dims[4] = {(cuuint64_t)HD, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)T};
-    const cuuint64_t strides[3] = {(cuuint64_t)HD * 2, (cuuint64_t)G * HD * 2, (cuuint64_t)nh * HD * 2};
+    // the innermost extent is the true head size: what a 64-dim box holds beyond it arrives as zeros
+    const cuuint64_t dims[4] = {(cuuint64_t)hd, (cuuint64_t)G, (cuuint64_t)nkv, (cuuint64_t)T};
+    const cuuint64_t strides[3] = {(cuuint64_t)hd * 2, (cuuint64_t)G * hd * 2, (cuuint64_t)nh * hd * 2};
     const cuuint32_t box[4] = {64, (cuuint32_t)G, 1, (cuuint32_t)tpt};
     const cuuint32_t el[4] = {1, 1, 1, 1};
     if (enc(&mq, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(q), dims, strides, box, el,
@@ -783,8 +797,8 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
       return JB_ERR_TENSORMAP;
   }
   for (int which = 0; which < 2; ++which) {
-    const cuuint64_t dims[2] = {(cuuint64_t)HD, (cuuint64_t)n_pages * nkv * PAGE};
-    const cuuint64_t strides[1] = {(cuuint64_t)HD * 2};
+    const cuuint64_t dims[2] = {(cuuint64_t)hd, (cuuint64_t)n_pages * nkv * PAGE};
+    const cuuint64_t strides[1] = {(cuuint64_t)hd * 2};
     const cuuint32_t box[2] = {64, PAGE};
     const cuuint32_t el[2] = {1, 1};
     if (enc(which ? &mv : &mk, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(which ? v_cache : k_cache), dims,
@@ -815,10 +829,10 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
     dim3 grid(nkv, (n_tiles + 1) / 2, n_seqs);
     jb::Launch cfg(grid, dim3(T2_THREADS), T2_SMEM, stream);
     return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc128_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
-                                   nkv, max_pages, window, scale * LOG2E, status);
+                                   nkv, hd, max_pages, window, scale * LOG2E, status);
   }
   dim3 grid(nkv, n_tiles, n_seqs);
   jb::Launch cfg(grid, dim3(threads_for(1)), smem_for(1), stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<1>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
-                                 nkv, max_pages, window, scale * LOG2E, status);
+                                 nkv, hd, max_pages, window, scale * LOG2E, status);
 }

@@ -836,10 +836,19 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
         scale, int(n_splits), int(write_kv), _stream()), "attention_bf16_decode_fused", kernels=kernels)
 
 
-# -- tcgen05 prefill attention (head sizes 64 and 128, up to 128 query heads per kv head) ------------------
+# -- tcgen05 prefill attention (head sizes up to 128 in steps of 8, up to 128 query heads per kv head) -----
+ATTENTION_TC_MAX_HEAD_DIM = 128
+
+
 def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
     g = nh // max(nkv, 1)
-    return _ATTN_TC and hd in (64, 128) and nkv > 0 and nh % nkv == 0 and g <= 128
+    return (_ATTN_TC and 0 < hd <= ATTENTION_TC_MAX_HEAD_DIM and hd % 8 == 0 and nkv > 0 and nh % nkv == 0
+            and g <= 128)
+
+
+def _attention_tc_row(hd: int) -> int:
+    """The build that takes head size `hd`: rows of 64 or of 128 dims in shared memory."""
+    return 64 if hd <= 64 else 128
 
 
 def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
@@ -857,7 +866,8 @@ def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.
     _need(kv_len, "kv_len", torch.int32, (n_seqs,))
     if tuple(k_cache.shape[1:]) != (nkv, page_size, hd) or k_cache.shape != v_cache.shape:
         raise KernelError(f"attention_tc: cache shape {tuple(k_cache.shape)} does not fit [pages, {nkv}, {page_size}, {hd}]")
-    _check(_lib("attention_tc", int(hd), lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES)).jb_attention_tc_prefill(
+    _check(_lib("attention_tc", _attention_tc_row(hd),
+                lambda h: dict({"JB_HEAD_DIM": h}, **_ATTN_TC_DEFINES)).jb_attention_tc_prefill(
         _ptr(q), _ptr(k_cache), _ptr(v_cache), _ptr(out), _ptr(block_table), _ptr(q_start), _ptr(kv_len),
         T, k_cache.shape[0], n_seqs, max_q_len, nh, nkv, hd, page_size, block_table.shape[1], int(window),
         scale, _ptr(kernel_status(q.device)), _stream()), "attention_tc_prefill")

@@ -151,7 +151,7 @@ class GQAttention(Mixer):
         group = cache_view.group
         attn = ctx.workspace.get("attn_out", (q.shape[0], self.q_width), self.dtype)
         if ops.attention_tc_supported(self.nh, self.nkv, self.hd):
-            # head sizes 64 / 128: flash attention on the tcgen05 tensor cores
+            # head sizes up to 128: flash attention on the tcgen05 tensor cores
             ops.attention_tc_prefill(q, cache_view.k, cache_view.v, attn, group.block_table, ctx.q_start,
                                      ctx.kv_len, ctx.n_seqs, ctx.max_q_len, self.nh, self.nkv, self.hd,
                                      group.page_size, self.window, self.scale)

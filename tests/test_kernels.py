@@ -232,7 +232,12 @@ def test_attention_bf16_prefill(ops, nh, nkv, hd, window):
                                                  (2, 1, 64, 0), (64, 1, 128, 0),
                                                  # groups that do not divide the 128 rows of a tile: 3, 5, 6, 7, 100
                                                  (24, 8, 128, 0), (10, 2, 128, 90), (6, 1, 64, 50), (12, 4, 64, 0),
-                                                 (7, 1, 128, 0), (100, 1, 64, 0)])
+                                                 (7, 1, 128, 0), (100, 1, 64, 0),
+                                                 # head sizes that fill a row of 64 or 128 dims only in part: the
+                                                 # rest arrives as zeros, a last 16-dim step or store may be half
+                                                 (6, 2, 96, 0), (4, 1, 40, 70), (8, 8, 80, 0), (5, 1, 120, 0),
+                                                 (9, 3, 24, 0), (4, 2, 8, 0), (12, 4, 104, 90), (8, 2, 56, 0),
+                                                 (16, 4, 112, 0), (4, 4, 72, 0), (3, 1, 48, 30)])
 def test_attention_tc_prefill(ops, nh, nkv, hd, window, tiles, monkeypatch):
     """The tcgen05 kernel against the plain attention: ragged batch, chunked prompts
     (queries are the last q_len positions), a far key that stands out; the one-tile kernel and the
