@@ -398,12 +398,14 @@ def run_prompt_lengths(layers, which):
 
     import janus_b200
     from janus_b200.engine import StepEntry
-    cfg = dict(CONFIG_8B, num_hidden_layers=layers, max_position_embeddings=8192)
-    model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=16384, max_slots=16, norm_std=0.0)
+    cases = [tuple(int(v) for v in item.split("x")) for item in which.split(",")]
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers, max_position_embeddings=max(8192, max(t for _, t in cases)))
+    model = janus_b200.load_random(cfg, seed=2, dtype="bfloat16", max_tokens=max(16384, max(s * t for s, t in cases)),
+                                   max_slots=16, norm_std=0.0)
     torch.cuda.profiler.start()          # for `ncu --profile-from-start off`: nothing of the weights' set-up is captured
     g = torch.Generator().manual_seed(0)
     pk = peaks()
-    for seqs, T in (tuple(int(v) for v in item.split("x")) for item in which.split(",")):
+    for seqs, T in cases:
         times = []
         for _ in range(8):
             slots = [model.alloc_slot() for _ in range(seqs)]
@@ -449,8 +451,8 @@ def run_kernels(contexts=None, shape="8b", head_sizes=None):
     dependent launch) over several copies of its weights or cache, so that every launch reads from DRAM,
     and timed with CUDA events around 5 replays.  One line per kernel; nothing here is the headline.
     With `contexts` (key counts), decode attention alone at those contexts, for 1, 8 and 64 sequences.
-    With `head_sizes`, prompt attention alone at those head sizes (the shape's heads, 2,048 tokens) on both of
-    its kernels: tcgen05 (head sizes up to 128) and mma.sync."""
+    With `head_sizes`, prompt attention alone at those head sizes (the shape's heads; 2,048 tokens, or one
+    prompt of each of `contexts`) on both of its kernels: tcgen05 (head sizes up to 128) and mma.sync."""
     import math
 
     import torch
@@ -550,9 +552,9 @@ def run_kernels(contexts=None, shape="8b", head_sizes=None):
                           "splits": ops.decode_splits_for(B, NKV * ((NH // NKV + 15) // 16), cap * 64, 64, HD), "us": round(us, 1),
                           "kv_GBps": round(B * ctx * NKV * HD * 4 / us / 1e3, 1)}), flush=True)
 
-    for hd in head_sizes or ():
-        B, L = 1, 2048
-        pages = L // 64
+    for hd, L in ((h, c) for h in head_sizes or () for c in contexts or (2048,)):
+        B = 1
+        pages = (L + 63) // 64
         kc = torch.randn(B * pages, NKV, 64, hd, device=dev).to(torch.bfloat16)
         vc = torch.randn_like(kc)
         table = torch.arange(B * pages, device=dev, dtype=torch.int32).view(B, pages)
@@ -564,8 +566,10 @@ def run_kernels(contexts=None, shape="8b", head_sizes=None):
         if ops.attention_tc_supported(NH, NKV, hd):
             faces.insert(0, ("tcgen05", ops.attention_tc_prefill))
         for name, face in faces:
+            if name == "mma.sync" and L > 8192:
+                continue
             us = timed(lambda: face(q, kc, vc, out, table, q_start, kv_len, B, L, NH, NKV, hd, 64, 0,
-                                    1 / math.sqrt(hd)), reps=6)
+                                    1 / math.sqrt(hd)), reps=6 if L <= 8192 else 2)
             print(json.dumps({"kernel": f"prefill attention ({name})", "head_size": hd, "tokens": L,
                               "us": round(us, 1),
                               "TFLOPs": round(B * 4 * NH * hd * L * (L + 1) / 2 / us / 1e6, 1)}), flush=True)

@@ -174,13 +174,23 @@ struct TileCoord {
   int t0, f0;
   int k_lo, k_hi;   // k-tiles of this tile's slice of K (the whole of K unless an adding product is cut)
 };
+// Output tiles are numbered token tile fastest inside bands of TOK_BAND token tiles: the pairs that run at the
+// same time then work on a few token tiles times a few weight tiles, and a band's tokens (2,048 rows of X) stay
+// in L2 while the weight tiles pass by.  With one number space over all token tiles a prompt of 65,536 tokens
+// would fetch X (0.5 to 1.9 GB a product) from DRAM once per weight tile; banded, X is read once and the
+// weights once per band.  Up to TOK_BAND token tiles the order is the plain one.
+constexpr int TOK_BAND = 8;
 template <int MODE>
-__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int k_tiles, int k_per, int splits) {
+__device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int n_w_tiles, int k_tiles, int k_per,
+                                                int splits) {
   TileCoord c;
   const int slice = tile % splits;   // slices of one output tile are neighbours: they run at the same time
   tile /= splits;
-  c.t0 = (tile % n_tok_tiles) * 256;
-  c.f0 = (tile / n_tok_tiles) * (MODE == SWIGLU ? 128 : 256);
+  const int band_tiles = TOK_BAND * n_w_tiles;
+  const int band = tile / band_tiles, rem = tile - band * band_tiles;
+  const int in_band = min(TOK_BAND, n_tok_tiles - band * TOK_BAND);   // the last band may hold fewer token tiles
+  c.t0 = (band * TOK_BAND + rem % in_band) * 256;
+  c.f0 = (rem / in_band) * (MODE == SWIGLU ? 128 : 256);
   c.k_lo = slice * k_per;
   c.k_hi = min(k_tiles, c.k_lo + k_per);
   return c;
@@ -193,18 +203,18 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int n_tok_tiles, int k
 // 4 slices each = 216 pieces in three rounds of a quarter tile: 1.75 waves' time instead of 2).
 template <int MODE>
 struct Walk {
-  int n_items, n_tok_tiles, k_tiles, k_per, splits, n_pairs, n_whole;
+  int n_items, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_pairs, n_whole;
   int item;
-  __device__ Walk(int pair, int n_pairs_, int n_items_, int n_tok_tiles_, int k_tiles_, int k_per_, int splits_,
-                  int n_whole_)
-      : n_items(n_items_), n_tok_tiles(n_tok_tiles_), k_tiles(k_tiles_), k_per(k_per_), splits(splits_),
-        n_pairs(n_pairs_), n_whole(n_whole_), item(pair) {}
+  __device__ Walk(int pair, int n_pairs_, int n_items_, int n_tok_tiles_, int n_w_tiles_, int k_tiles_, int k_per_,
+                  int splits_, int n_whole_)
+      : n_items(n_items_), n_tok_tiles(n_tok_tiles_), n_w_tiles(n_w_tiles_), k_tiles(k_tiles_), k_per(k_per_),
+        splits(splits_), n_pairs(n_pairs_), n_whole(n_whole_), item(pair) {}
   __device__ __forceinline__ bool next(TileCoord& c) {
     if (item >= n_items) return false;
     if (item < n_whole) {
-      c = tile_coord<MODE>(item, n_tok_tiles, k_tiles, k_tiles, 1);
+      c = tile_coord<MODE>(item, n_tok_tiles, n_w_tiles, k_tiles, k_tiles, 1);
     } else {
-      c = tile_coord<MODE>(n_whole * splits + (item - n_whole), n_tok_tiles, k_tiles, k_per, splits);
+      c = tile_coord<MODE>(n_whole * splits + (item - n_whole), n_tok_tiles, n_w_tiles, k_tiles, k_per, splits);
     }
     item += n_pairs;
     return true;
@@ -228,6 +238,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int n_w_tiles = (N_out + (MODE == SWIGLU ? 128 : 256) - 1) / (MODE == SWIGLU ? 128 : 256);
   jb::pdl_launch_dependents();
 
   if (threadIdx.x == 0) {
@@ -259,7 +270,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     if (lane == 0) {
       int it = 0;
       bool ok = true;
-      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, k_tiles, k_per, splits, n_whole);
+      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole);
       TileCoord tc;
       while (ok && walk.next(tc)) {
         // rows of this CTA's two loads: its 128 rows of the pair's M side, its half of the column operand
@@ -291,7 +302,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
       constexpr uint32_t idesc = instr_desc_pair(BN);
       bool ok = true;
       int it = 0, j = 0;
-      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, k_tiles, k_per, splits, n_whole);
+      Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole);
       TileCoord tc;
       for (; ok && walk.next(tc); ++j) {
         const int buf = j & 1;
@@ -320,7 +331,7 @@ __global__ void __launch_bounds__(THREADS) gemm_tc2_kernel(const __grid_constant
     const int quarter = warp & 3;
     const int part = (warp - 2) >> 2;   // which of the columns' 16-wide chunks (every EPI_PARTS-th) this warp takes
     int j = 0;
-    Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, k_tiles, k_per, splits, n_whole);
+    Walk<MODE> walk(pair, n_pairs, n_tiles, n_tok_tiles, n_w_tiles, k_tiles, k_per, splits, n_whole);
     TileCoord tc;
     for (; walk.next(tc); ++j) {
       const int buf = j & 1;

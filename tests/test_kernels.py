@@ -420,7 +420,27 @@ def test_gemm_bf16_cta_pairs(ops, T, N, K):
     ops.check_kernel_status(torch.device(DEV))
 
 
-@pytest.mark.parametrize("T", [70, 130, 256, 700])
+@pytest.mark.parametrize("T, N, K", [(2500, 200, 120), (2500, 1000, 320), (4400, 700, 64), (2049, 520, 96)])
+def test_gemm_bf16_cta_pairs_beyond_one_band_of_token_tiles(ops, T, N, K):
+    """More than eight token tiles: output tiles are numbered in bands of eight token tiles, the last band holds
+    fewer (2,500 tokens: 8 + 2 tiles; 4,400: 8 + 8 + 2; 2,049: 8 + 1).  Every tile is computed once, whole or in
+    slices, whichever of them are the uncut ones."""
+    x, w = bf16_inputs(T, N, K, T + N + 1)
+    ref = x.double().cpu() @ w.double().cpu().T
+    w = ops.pack_weight(w)
+    y32 = torch.full((T, N), float("nan"), device=DEV)
+    ops.gemm_bf16(x, w, y32, pair=True)
+    close(y32, ref, 2e-5)
+    base = torch.randn(T, N, device=DEV)
+    tiles = ((T + 255) // 256) * ((N + 255) // 256)
+    for split, whole in ((1, 0), (2, 0), (3, 5), (3, tiles - 3), (2, 17)):
+        acc = base.clone()
+        ops.gemm_bf16(x, w, acc, mode="add", pair=True, split_k=split, whole_tiles=whole)
+        close(acc, ref + base.double().cpu(), 2e-5)
+    ops.check_kernel_status(torch.device(DEV))
+
+
+@pytest.mark.parametrize("T", [70, 130, 256, 700, 2500])
 @pytest.mark.parametrize("I, K", [(192, 64), (320, 96), (1000, 2048)])
 def test_gemm_bf16_cta_pairs_swiglu(ops, T, I, K):
     x, w = bf16_inputs(T, 2 * I, K, T + I + 1)
@@ -432,7 +452,7 @@ def test_gemm_bf16_cta_pairs_swiglu(ops, T, I, K):
     ops.check_kernel_status(torch.device(DEV))
 
 
-@pytest.mark.parametrize("T", [256, 700])
+@pytest.mark.parametrize("T", [256, 700, 2500])
 @pytest.mark.parametrize("nh, nkv, hd, K", [(3, 1, 128, 320), (6, 3, 64, 96), (5, 5, 32, 2048), (2, 1, 256, 64)])
 def test_gemm_qkv_with_rotation_and_cache_append(ops, T, nh, nkv, hd, K):
     """The stacked q/k/v projection whose epilogue rotates q and k and writes k, v into the paged cache:
