@@ -14,7 +14,7 @@ import torch
 from . import log
 from .cache import PAGE_SIZE
 from .config import read_config_json, resolve_architecture
-from .engine.generate import run_generation
+from .engine.generate import plan_prompt_steps, run_generation
 from .engine.step import Engine, EngineOptions, StepEntry
 from .sampling import DeviceSampler, SamplerConfig
 from .weights import FolderCheckpoint, RandomCheckpoint, parse_dtype
@@ -49,8 +49,17 @@ class _EngineBackend:
         return ids.cpu().tolist()
 
     def prefill(self, slots, prompts, requests) -> List[int]:
-        logits = self.engine.step([StepEntry(s, p, (len(p) - 1,)) for s, p in zip(slots, prompts)])
-        return self._sample(logits, slots, requests, [0] * len(slots))
+        steps = plan_prompt_steps([len(p) for p in prompts], self.engine.options.max_step_tokens)
+        rows = [None] * len(prompts)     # the logits at each prompt's last token, from the step that held it
+        for pieces in steps:
+            logits = self.engine.step([StepEntry(slots[i], prompts[i][a:b], (b - a - 1,) if b == len(prompts[i]) else ())
+                                       for i, a, b in pieces])
+            if len(steps) == 1:
+                return self._sample(logits, slots, requests, [0] * len(slots))
+            done = [i for i, _, b in pieces if b == len(prompts[i])]
+            for row, i in enumerate(done):
+                rows[i] = logits[row].clone()    # the next step writes its logits to the same place
+        return self._sample(torch.stack(rows), slots, requests, [0] * len(slots))
 
     def decode(self, slots, last_tokens, requests, steps) -> List[int]:
         ids = self.engine.decode_sample(slots, last_tokens, self.sampler, requests, steps)
@@ -170,8 +179,11 @@ class Model:
         return outputs, stats
 
 
+_WHOLE = object()        # max_step_tokens left at the engine's default
+
+
 def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_seq_len: Optional[int],
-           max_slots: Optional[int], device, use_graphs: bool) -> Model:
+           max_slots: Optional[int], device, use_graphs: bool, max_step_tokens=_WHOLE) -> Model:
     if not torch.cuda.is_available():
         raise RuntimeError("janus_b200 needs a CUDA device (sm_100a); there is no CPU path")
     device = torch.device(device)
@@ -181,8 +193,11 @@ def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_se
     with torch.cuda.device(device):
         model = arch.build(config, torch_dtype, device)
         model.load(checkpoint_factory(arch, config))
-        engine = Engine(model, EngineOptions(max_tokens=max_tokens, max_seq_len=max_seq_len,
-                                             max_slots=max_slots, use_graphs=use_graphs))
+        options = EngineOptions(max_tokens=max_tokens, max_seq_len=max_seq_len, max_slots=max_slots,
+                                use_graphs=use_graphs)
+        if max_step_tokens is not _WHOLE:
+            options.max_step_tokens = max_step_tokens
+        engine = Engine(model, options)
     if log.enabled("info"):
         cache = engine.cache
         log.log("info", f"loaded {type(config).__name__}: {len(model.layers)} layers, hidden {model.hidden_size}, "
@@ -193,19 +208,21 @@ def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_se
 
 
 def load(model_dir: str, dtype="bfloat16", max_tokens: int = 8192, max_seq_len: Optional[int] = None,
-         max_slots: Optional[int] = None, device="cuda:0", use_graphs: bool = True) -> Model:
+         max_slots: Optional[int] = None, device="cuda:0", use_graphs: bool = True,
+         max_step_tokens=_WHOLE) -> Model:
     """Load `model_dir` (config.json + model.safetensors).  `dtype` is the engine
     dtype: "bfloat16" (tensor-core kernels) or "float32" (true 32-bit path).
     `max_tokens` sizes the cache: the most tokens live sequences hold at any
-    time, each sequence rounded up to a multiple of 64."""
+    time, each sequence rounded up to a multiple of 64.  `max_step_tokens`: `generate` cuts a batch's
+    prompts into steps of at most that many tokens (default 32,768; None: one step whatever the size)."""
     return _build(read_config_json(model_dir), lambda arch, config: FolderCheckpoint(model_dir), dtype,
-                  max_tokens, max_seq_len, max_slots, device, use_graphs)
+                  max_tokens, max_seq_len, max_slots, device, use_graphs, max_step_tokens)
 
 
 def load_random(config_dict: dict, seed: int, dtype="bfloat16", max_tokens: int = 8192,
                 max_seq_len: Optional[int] = None, max_slots: Optional[int] = None, device="cuda:0",
                 std: float = 0.02, norm_std: float = 0.0, use_graphs: bool = True,
-                stored_dtype=None) -> Model:
+                stored_dtype=None, max_step_tokens=_WHOLE) -> Model:
     """A model with seeded random weights made on the device, without a folder.  `stored_dtype` is the
     dtype the weights are "stored" in (default: the engine dtype): "bfloat16" under a float32 engine gives
     the 32-bit engine exactly the weights that the bfloat16 engine has.  The values are a function of the
@@ -213,4 +230,5 @@ def load_random(config_dict: dict, seed: int, dtype="bfloat16", max_tokens: int 
     def factory(arch, config):
         return RandomCheckpoint(arch.weight_specs(config), seed, dtype=stored_dtype or dtype, std=std,
                                 norm_std=norm_std, device=device)
-    return _build(config_dict, factory, dtype, max_tokens, max_seq_len, max_slots, device, use_graphs)
+    return _build(config_dict, factory, dtype, max_tokens, max_seq_len, max_slots, device, use_graphs,
+                  max_step_tokens)

@@ -56,6 +56,8 @@ def main(argv=None) -> int:
     ap.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32", "bf16", "fp32"])
     ap.add_argument("--context-size", "--max-seq-len", type=int, default=None,
                     help="longest sequence (default: the model's)")
+    ap.add_argument("--max-step-tokens", type=int, default=32768,
+                    help="prompts of a batch run in steps of at most this many tokens (default: 32768; 0 = one step)")
     ap.add_argument("--random-weights", action="store_true",
                     help="the folder holds only config.json: run it with random weights")
     ap.add_argument("--seed-weights", type=int, default=0, help="seed of --random-weights")
@@ -82,10 +84,12 @@ def main(argv=None) -> int:
         with open(os.path.join(args.model_dir, "config.json")) as f:
             config = json.load(f)
         model = janus_b200.load_random(config, seed=args.seed_weights, dtype=dtype, max_tokens=sum(room[:batch]),
-                                       max_seq_len=args.context_size, max_slots=batch)
+                                       max_seq_len=args.context_size, max_slots=batch,
+                                       max_step_tokens=args.max_step_tokens or None)
     else:
         model = janus_b200.load(args.model_dir, dtype=dtype, max_tokens=sum(room[:batch]),
-                                max_seq_len=args.context_size, max_slots=batch)
+                                max_seq_len=args.context_size, max_slots=batch,
+                                max_step_tokens=args.max_step_tokens or None)
     out, reasons, stats = model.generate(
         prompts, max_tokens=args.max_tokens, temperature=args.temperature, top_k=args.top_k, top_p=args.top_p,
         repetition_penalty=args.repetition_penalty, seed=args.seed, stop_token_ids=args.stop_id,

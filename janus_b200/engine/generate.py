@@ -80,6 +80,29 @@ def plan_batch(pending: Sequence[int], prompt_lens: Sequence[int], max_new_token
     return chosen
 
 
+def plan_prompt_steps(prompt_lens: Sequence[int], max_step_tokens: Optional[int]) -> List[List[Tuple[int, int, int]]]:
+    """How a batch's prompts are cut into steps of at most `max_step_tokens` tokens (None or 0: one step
+    whatever the size): a list of steps, each a list of (prompt index, first token, end) pieces.  Prompts are
+    taken in order and a step is filled before the next begins, so a step holds the end of one prompt, whole
+    prompts and the beginning of another; each prompt's pieces follow one another in consecutive steps.  What
+    a step's activations need is then bounded by the limit, not by the batch."""
+    if not max_step_tokens or sum(prompt_lens) <= max_step_tokens:
+        return [[(i, 0, n) for i, n in enumerate(prompt_lens)]]
+    steps: List[List[Tuple[int, int, int]]] = [[]]
+    room = max_step_tokens
+    for i, n in enumerate(prompt_lens):
+        start = 0
+        while start < n:
+            if room == 0:
+                steps.append([])
+                room = max_step_tokens
+            end = min(n, start + room)
+            steps[-1].append((i, start, end))
+            room -= end - start
+            start = end
+    return steps
+
+
 def run_generation(backend: GenerationBackend, prompts: Sequence[Sequence[int]], max_new_tokens: int,
                    stop_token_ids: Sequence[int], batch_size: int, capacity_tokens: int, max_seq_len: int,
                    free_slots: int, page_size: int,

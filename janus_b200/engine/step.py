@@ -39,6 +39,10 @@ class EngineOptions:
     max_seq_len: Optional[int] = None  # longest sequence; default: the model's max positions
     max_slots: Optional[int] = None    # live sequences at most; default: one per page, at most 1024
     use_graphs: bool = True            # replay decode steps from CUDA graphs
+    # the generation loop cuts a batch's prompts into steps of at most this many tokens (None: one step whatever
+    # the size); a step's activations are sized by its tokens, so this bounds them.  The step function itself
+    # takes what it is given.
+    max_step_tokens: Optional[int] = 32768
 
 
 @dataclass

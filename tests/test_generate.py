@@ -50,6 +50,24 @@ def test_greedy_generation_of_unequal_prompts(tmp_path, name, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("limit", [1, 7, 40])
+def test_prompts_cut_into_steps_of_limited_size_give_the_same_tokens(tmp_path, dtype, limit):
+    """`max_step_tokens`: the batch's prompts run in steps of at most that many tokens (a step holds the end of
+    one prompt, whole prompts and the beginning of another; with a limit of 1 every token is a step of its
+    own).  The first sampled tokens come from different steps' logits; everything matches the plain
+    implementation as the uncut prompts do."""
+    model, (cfg, w) = load(tmp_path, "B", dtype, max_step_tokens=limit)
+    lens = [1, 7, 33, 64, 2]
+    prompts = [random_tokens(n, cfg["vocab_size"], 11 + n) for n in lens]
+    out, stats = model.generate(prompts, max_tokens=6, ignore_eos=True)
+    assert stats.prefill_tokens == sum(lens)
+    for p, o in zip(prompts, out):
+        check_greedy_against_plain(cfg, w, p, o, dtype)
+        if dtype == "float32":
+            assert o == P.generate(cfg, w, p, 6)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding(tmp_path, dtype):
     model, (cfg, w) = load(tmp_path, "A", dtype)
     prompt = random_tokens(3, 256, 1)

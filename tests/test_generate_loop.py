@@ -240,3 +240,30 @@ def test_every_slot_comes_back_when_a_batch_ends_in_an_error(fail_in):
     ok.free, ok.held = b.free, b.held
     toks, reasons, stats = run_generation(ok, [[1, 2]] * 4, 3, [], 4, 10_000, 1000, 4, 64, None)
     assert toks == [[r + 1] * 3 for r in range(4)] and not ok.held
+
+
+def test_prompt_steps_hold_every_token_once_in_order_within_the_limit():
+    """`plan_prompt_steps`: each prompt's pieces are consecutive, in order and complete; no step exceeds the
+    limit; every step but the last is full; without a limit (or under it) there is one step of whole prompts."""
+    import random
+
+    from janus_b200.engine.generate import plan_prompt_steps
+    assert plan_prompt_steps([5, 3], None) == [[(0, 0, 5), (1, 0, 3)]]
+    assert plan_prompt_steps([5, 3], 8) == [[(0, 0, 5), (1, 0, 3)]]
+    assert plan_prompt_steps([5, 3], 4) == [[(0, 0, 4)], [(0, 4, 5), (1, 0, 3)]]
+    assert plan_prompt_steps([2, 9, 1], 3) == [[(0, 0, 2), (1, 0, 1)], [(1, 1, 4)], [(1, 4, 7)], [(1, 7, 9), (2, 0, 1)]]
+    rng = random.Random(4)
+    for _ in range(200):
+        lens = [rng.randint(1, 50) for _ in range(rng.randint(1, 8))]
+        limit = rng.randint(1, 60)
+        steps = plan_prompt_steps(lens, limit)
+        sizes = [sum(b - a for _, a, b in st) for st in steps]
+        assert all(0 < n <= limit for n in sizes) and (sum(lens) <= limit or all(n == limit for n in sizes[:-1]))
+        pieces = [piece for st in steps for piece in st]
+        assert [i for i, _, _ in pieces] == sorted(i for i, _, _ in pieces)
+        for i, n in enumerate(lens):
+            mine = [(a, b) for j, a, b in pieces if j == i]
+            assert mine[0][0] == 0 and mine[-1][1] == n and all(x[1] == y[0] for x, y in zip(mine, mine[1:]))
+            assert all(b > a for a, b in mine)
+            where = [k for k, st in enumerate(steps) for j, _, _ in st if j == i]
+            assert where == list(range(where[0], where[0] + len(where)))
