@@ -9,6 +9,7 @@ from __future__ import annotations
 
 from typing import Callable, List, Optional, Sequence
 
+import numpy as np
 import torch
 
 from . import log
@@ -165,7 +166,8 @@ class Model:
         free_tokens = min((g.pool.n_free for g in cache.groups), default=cache.n_pages) * PAGE_SIZE
         captures_before = self.engine.graph_captures
         outputs, reasons, stats = run_generation(
-            _EngineBackend(self.engine, sampler), [list(map(int, p)) for p in prompts], max_tokens, stop,
+            _EngineBackend(self.engine, sampler), [np.asarray(p, dtype=np.int64).reshape(-1) for p in prompts],
+            max_tokens, stop,
             batch_size or cache.n_slots, free_tokens, self.engine.max_seq_len,
             cache.n_free_slots, PAGE_SIZE, callback)
         stats.graph_captures = self.engine.graph_captures - captures_before

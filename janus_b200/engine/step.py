@@ -48,7 +48,7 @@ class EngineOptions:
 @dataclass
 class StepEntry:
     slot: int
-    tokens: Sequence[int]
+    tokens: Sequence[int]              # a list, tuple or array of ids (the engine keeps several as an int64 array)
     want: Sequence[int] = ()           # places among `tokens` whose logits are wanted
 
 
@@ -138,9 +138,19 @@ class Engine:
             n = len(e.tokens)
             if n == 0:
                 raise StepError(f"slot {e.slot} brings no tokens")
-            bad = [t for t in e.tokens if not (0 <= int(t) < V or (device_tokens and int(t) == FROM_DEVICE))]
-            if bad:
-                raise StepError(f"token id {bad[0]} is outside the vocabulary of {V}")
+            if n == 1:
+                t = int(e.tokens[0])
+                if not (0 <= t < V or (device_tokens and t == FROM_DEVICE)):
+                    raise StepError(f"token id {t} is outside the vocabulary of {V}")
+            else:
+                # one pass over an array, not a Python loop per token (a batch's prompts are tens of
+                # thousands); the array stays with the entry for the step's index buffer
+                toks = e.tokens = np.asarray(e.tokens, dtype=np.int64).reshape(-1)
+                outside = (toks < 0) | (toks >= V)
+                if device_tokens:
+                    outside &= toks != FROM_DEVICE
+                if outside.any():
+                    raise StepError(f"token id {int(toks[outside][0])} is outside the vocabulary of {V}")
             if self.cache.lengths[e.slot] + n > self.max_seq_len:
                 raise StepError(
                     f"slot {e.slot} would reach {self.cache.lengths[e.slot] + n} tokens, the longest "
