@@ -273,8 +273,10 @@ class _WS:
 
 @pytest.mark.parametrize("nh, nkv, hd, window", [(4, 2, 16, 0), (3, 1, 40, 0), (32, 8, 128, 0), (5, 5, 72, 70),
                                                  (40, 2, 32, 0), (4, 4, 256, 0)])
-@pytest.mark.parametrize("n_splits", [1, 3, None])
+@pytest.mark.parametrize("n_splits", [1, 3, None, 8, 16, 20])
 def test_attention_bf16_decode(ops, nh, nkv, hd, window, n_splits):
+    """One split writes the result itself, more meet in scratch and a joining kernel; a sequence of one key
+    leaves most of 8 to 20 splits without a page."""
     lens = [130, 5, 64, 1, 700, 65]
     q_lens = [1] * len(lens)
     qs, ks, vs = attention_case(nh, nkv, hd, lens, q_lens, torch.bfloat16, seed=1)
