@@ -77,7 +77,18 @@ __device__ void block_argmax(float v, int i, float* smem_val, int* smem_idx) {
   __syncthreads();
 }
 
-__global__ void __launch_bounds__(THREADS) sample_kernel(
+// Inclusive sums over a warp's lanes (lane 31 ends with the sum of all).
+__device__ __forceinline__ float warp_inclusive(float v) {
+  const int lane = threadIdx.x & 31;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const float t = __shfl_up_sync(0xffffffffu, v, o);
+    if (lane >= o) v += t;
+  }
+  return v;
+}
+
+__global__ void __launch_bounds__(THREADS, 1) sample_kernel(
     const float* __restrict__ logits, int V, int* __restrict__ out_ids, float temperature, int top_k,
     float top_p, float penalty, int* __restrict__ counts, const int* __restrict__ count_rows,
     unsigned long long seed, const int* __restrict__ seq_ids, const int* __restrict__ steps,
@@ -89,8 +100,9 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   __shared__ float s_fhist[256];
   __shared__ unsigned s_sel[2];   // chosen digit, remaining rank
   __shared__ float s_fsel;        // mass above the chosen digit
-  __shared__ float s_scan[THREADS];
+  __shared__ float s_warp[THREADS / 32];
   __shared__ int s_result;
+  extern __shared__ float s_iter[];   // [THREADS / 32][ceil(V / (4 THREADS))]: sums of pieces of 128 indices
 
   const int row = blockIdx.x, tid = threadIdx.x;
   int* my_counts = (counts && penalty != 1.0f) ? counts + (size_t)count_rows[row] * V : nullptr;
@@ -99,9 +111,23 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
   // ---- maximum and argmax (needed by both modes) -------------------------
   float best = -CUDART_INF_F;
   int best_i = 0x7fffffff;
-  for (int v = tid; v < V; v += THREADS) {
-    const float x = view.at(v);
-    if (x > best) { best = x; best_i = v; }
+  if (my_counts == nullptr && (V & 3) == 0) {
+    // plain logits in rows of whole 16-byte vectors: four at a time, several vectors in flight per thread
+    // (a thread's indices still rise, so the first of equal values stays)
+    const float4* row4 = reinterpret_cast<const float4*>(view.logits);
+#pragma unroll 4
+    for (int i = tid; i < (V >> 2); i += THREADS) {
+      const float4 x = row4[i];
+      if (x.x > best) { best = x.x; best_i = 4 * i; }
+      if (x.y > best) { best = x.y; best_i = 4 * i + 1; }
+      if (x.z > best) { best = x.z; best_i = 4 * i + 2; }
+      if (x.w > best) { best = x.w; best_i = 4 * i + 3; }
+    }
+  } else {
+    for (int v = tid; v < V; v += THREADS) {
+      const float x = view.at(v);
+      if (x > best) { best = x; best_i = v; }
+    }
   }
   block_argmax(best, best_i, s_val, s_idx);
   const float x_max = s_val[0];
@@ -138,16 +164,20 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
       }
       thr_key = prefix;
     }
-    const float inv_shift = x_max / temperature;
-    auto weight = [&](int v) -> float {
-      const float x = view.at(v);
-      if (ordered_key(x) < thr_key || !(x == x) || x == -CUDART_INF_F) return 0.0f;
-      return expf(x / temperature - inv_shift);
+    // weight = exp((x - max) / temperature) as 2^(x a - max a), a = log2(e) / temperature: one fused
+    // multiply-add and one exponential a value; the same code in every pass, so passes agree bit for bit
+    const float w_a = 1.4426950408889634f / temperature, w_b = x_max * w_a;
+    auto weight_of = [&](float x) -> float {
+      if (ordered_key(x) < thr_key || !(x == x)) return 0.0f;
+      return exp2f(fmaf(x, w_a, -w_b));   // -inf gives 0
     };
-    // ---- normaliser --------------------------------------------------------
+    auto weight = [&](int v) -> float { return weight_of(view.at(v)); };
+    // ---- normaliser (only the top-p threshold needs it) ----------------------
     float z = 0.0f;
-    for (int v = tid; v < V; v += THREADS) z += weight(v);
-    z = jb::block_sum(z, s_red);
+    if (top_p < 1.0f) {
+      for (int v = tid; v < V; v += THREADS) z += weight(v);
+      z = jb::block_sum(z, s_red);
+    }
     // ---- top-p threshold on the weights -------------------------------------
     unsigned thr_bits = 0u;
     if (top_p < 1.0f) {
@@ -181,45 +211,87 @@ __global__ void __launch_bounds__(THREADS) sample_kernel(
       }
       thr_bits = prefix;
     }
-    auto kept = [&](int v) -> float {
-      const float w = weight(v);
+    auto kept_of = [&](float x) -> float {
+      const float w = weight_of(x);
       return (__float_as_uint(w) >= thr_bits) ? w : 0.0f;
     };
     // ---- inverse CDF in index order ------------------------------------------
-    const int chunk = (V + THREADS - 1) / THREADS;
-    const int lo = min(V, tid * chunk), hi = min(V, lo + chunk);
-    float local = 0.0f;
-    for (int v = lo; v < hi; ++v) local += kept(v);
-    s_scan[tid] = local;
-    __syncthreads();
-    if (tid == 0) {
-      // Serial scan over 1024 partial sums keeps the order of the sum fixed.
-      float run = 0.0f;
-      for (int i = 0; i < THREADS; ++i) {
-        const float t = s_scan[i];
-        s_scan[i] = run;
-        run += t;
+    // Warp w owns the indices [w * iters * 128, (w + 1) * iters * 128) in pieces of 128 consecutive ones, four
+    // to a lane (one 16-byte load).  A piece's sum is the lanes' own sums of four, scanned over the warp; the
+    // running sums of a warp's pieces and then of the warps are added up in index order by the same code for
+    // every thread, so the interval that holds the target has exactly one owner.
+    const int warp = tid >> 5, lane = tid & 31;
+    const int iters = (V + 4 * THREADS - 1) / (4 * THREADS);
+    const bool vec = my_counts == nullptr && (V & 3) == 0;
+    auto four = [&](int v0, float* w) {   // the kept weights of indices v0 .. v0 + 3
+      if (vec) {
+        float4 x = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+        if (v0 < V) x = *reinterpret_cast<const float4*>(view.logits + v0);
+        w[0] = kept_of(x.x), w[1] = kept_of(x.y), w[2] = kept_of(x.z), w[3] = kept_of(x.w);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) w[j] = v0 + j < V ? kept_of(view.at(v0 + j)) : 0.0f;
       }
-      s_red[0] = run;
-      s_result = -1;
+    };
+    float* my_iter = s_iter + warp * iters;
+#pragma unroll 4
+    for (int k = 0; k < iters; ++k) {
+      float w[4];
+      four(((warp * iters + k) * 32 + lane) * 4, w);
+      const float t = warp_inclusive(((w[0] + w[1]) + w[2]) + w[3]);
+      if (lane == 31) my_iter[k] = t;
+    }
+    __syncwarp();
+    if (lane == 0) {
+      float run = 0.0f;
+      for (int k = 0; k < iters; ++k) {
+        run += my_iter[k];
+        my_iter[k] = run;   // the warp's pieces up to and with piece k
+      }
+      s_warp[warp] = run;
+      if (tid == 0) s_result = -1;
     }
     __syncthreads();
-    const float total = s_red[0];
+    float before = 0.0f, my_before = 0.0f;
+    for (int w2 = 0; w2 < THREADS / 32; ++w2) {
+      if (w2 == warp) my_before = before;
+      before += s_warp[w2];
+    }
+    const float total = before;
     const float u = uniform_for(seed, (unsigned long long)seq_ids[row], (unsigned long long)steps[row]);
     const float target = u * total;
-    const float before = s_scan[tid];
-    if (local > 0.0f && target >= before && target < before + local) {
-      float run = before;
-      int pick = -1, last_kept = -1;
-      for (int v = lo; v < hi; ++v) {
-        const float w = kept(v);
-        if (w > 0.0f) {
-          last_kept = v;
-          run += w;
-          if (target < run) { pick = v; break; }
+    const float my_total = s_warp[warp];
+    // my_before + my_total is, bit for bit, the next warp's my_before: one warp owns the target
+    if (my_total > 0.0f && target >= my_before && target < my_before + my_total) {
+      int k_pick = iters - 1;
+      for (int k0 = 0; k0 < iters; k0 += 32) {
+        const int k = k0 + lane;
+        const unsigned hit = __ballot_sync(0xffffffffu, k < iters && target < my_before + my_iter[k]);
+        if (hit) {
+          k_pick = k0 + __ffs(hit) - 1;
+          break;
         }
       }
-      s_result = pick >= 0 ? pick : last_kept;
+      const float run0 = my_before + (k_pick > 0 ? my_iter[k_pick - 1] : 0.0f);
+      const int v0 = ((warp * iters + k_pick) * 32 + lane) * 4;
+      float w[4];
+      four(v0, w);
+      const float mine = ((w[0] + w[1]) + w[2]) + w[3];
+      float run = run0 + (warp_inclusive(mine) - mine);   // what lies before this lane's four
+      // the first kept index whose running sum passes the target; if rounding lets none pass, the piece's last
+      int hit_j = -1, last_j = -1;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (w[j] > 0.0f) {
+          run += w[j];
+          last_j = j;
+          if (hit_j < 0 && target < run) hit_j = j;
+        }
+      }
+      const unsigned passed = __ballot_sync(0xffffffffu, hit_j >= 0);
+      const unsigned any_kept = __ballot_sync(0xffffffffu, last_j >= 0);
+      const int pick_lane = passed ? __ffs(passed) - 1 : (any_kept ? 31 - __clz(any_kept) : -1);
+      if (pick_lane == lane) s_result = v0 + (passed ? hit_j : last_j);
     }
     __syncthreads();
     if (s_result >= 0) token = s_result;  // else rounding left no owner: keep the argmax
@@ -246,8 +318,17 @@ JB_EXPORT int jb_sample(const float* logits, int B, int V, int* out_ids, float t
   JB_REFUSE(temperature < 0.0f, "sample: negative temperature %f", temperature);
   JB_REFUSE(penalty <= 0.0f, "sample: repetition penalty %f must be positive", penalty);
   JB_REFUSE(feedback != nullptr && count_rows == nullptr, "sample: feedback needs the rows' slots");
-  sample_kernel<<<B, THREADS, 0, stream>>>(logits, V, out_ids, temperature, top_k, top_p, penalty, counts,
-                                           count_rows, seed, seq_ids, steps, feedback);
+  // shared memory for the sums of the pieces of 128 indices (used when temperature > 0)
+  const size_t smem = temperature > 0.0f ? (size_t)((V + 4 * THREADS - 1) / (4 * THREADS)) * (THREADS / 32) * sizeof(float) : 0;
+  JB_REFUSE(smem > 200 * 1024, "sample: a vocabulary of %d is too large for temperature sampling", V);
+  static size_t smem_allowed = 48 * 1024;
+  if (smem > smem_allowed) {
+    const cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return (int)e;
+    smem_allowed = smem;
+  }
+  sample_kernel<<<B, THREADS, smem, stream>>>(logits, V, out_ids, temperature, top_k, top_p, penalty, counts,
+                                              count_rows, seed, seq_ids, steps, feedback);
   JB_CHECK_LAUNCH();
   return 0;
 }
