@@ -20,6 +20,7 @@
 namespace {
 
 constexpr int THREADS = 1024;
+constexpr int DIGITS0 = 4096;   // digits of the radix select's first pass (12 bits; then 10 and 10)
 
 __device__ __forceinline__ float uniform_for(unsigned long long seed, unsigned long long sequence,
                                              unsigned long long step) {
@@ -38,16 +39,44 @@ __device__ __forceinline__ unsigned ordered_key(float x) {
   return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+// A row of logits with the repetition penalty applied where a token has been generated before.
 struct RowView {
   const float* logits;
   const int* counts;  // occurrences of each token among the generated ones, or null
   float penalty;
+  int V;
+  __device__ __forceinline__ float penalised(float x, int c) const {
+    for (; c > 0; --c) x = x > 0.0f ? x / penalty : x * penalty;
+    return x;
+  }
   __device__ __forceinline__ float at(int v) const {
-    float x = logits[v];
+    const float x = logits[v];
+    return counts ? penalised(x, counts[v]) : x;
+  }
+  // rows of whole 16-byte vectors are read four values at a time
+  __device__ __forceinline__ bool vectors() const { return (V & 3) == 0; }
+  __device__ __forceinline__ float4 at4(int v0) const {   // v0 a multiple of 4, v0 + 3 < V
+    float4 x = *reinterpret_cast<const float4*>(logits + v0);
     if (counts) {
-      for (int c = counts[v]; c > 0; --c) x = x > 0.0f ? x / penalty : x * penalty;
+      const int4 c = *reinterpret_cast<const int4*>(counts + v0);
+      if (c.x | c.y | c.z | c.w) {
+        x.x = penalised(x.x, c.x), x.y = penalised(x.y, c.y), x.z = penalised(x.z, c.z), x.w = penalised(x.w, c.w);
+      }
     }
     return x;
+  }
+  // f(index, value) for every index, each thread's indices rising
+  template <typename F>
+  __device__ __forceinline__ void for_all(F&& f) const {
+    if (vectors()) {
+#pragma unroll 4
+      for (int i = threadIdx.x; i < (V >> 2); i += THREADS) {
+        const float4 x = at4(4 * i);
+        f(4 * i, x.x), f(4 * i + 1, x.y), f(4 * i + 2, x.z), f(4 * i + 3, x.w);
+      }
+    } else {
+      for (int v = threadIdx.x; v < V; v += THREADS) f(v, at(v));
+    }
   }
 };
 
@@ -88,6 +117,51 @@ __device__ __forceinline__ float warp_inclusive(float v) {
   return v;
 }
 
+// Radix select, one digit: `value(d)` is what digit d holds (a count or a mass), d < n_digits = per * THREADS.
+// Picks the highest digit d such that the digits >= d, together with `above0`, reach `target` (digit 0 if none
+// does), and what lies above d.  Every thread gets both.  A thread owns `per` neighbouring digits; sums over the
+// threads above it come from warp scans and the warps' totals.
+template <typename F>
+__device__ __forceinline__ void pick_digit(F&& value, int per, unsigned long long above0, unsigned long long target,
+                                           unsigned long long* s_warp_tot, unsigned* s_pick, unsigned long long* s_above,
+                                           unsigned& digit, unsigned long long& above) {
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  unsigned long long mine = 0ull;
+  for (int j = 0; j < per; ++j) mine += value(tid * per + j);
+  unsigned long long at_or_above = mine;   // over the lanes >= this one
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const unsigned long long t = __shfl_down_sync(0xffffffffu, at_or_above, o);
+    if (lane + o < 32) at_or_above += t;
+  }
+  if (lane == 0) s_warp_tot[warp] = at_or_above;
+  if (tid == 0) {
+    *s_pick = 0u;
+    *s_above = 0ull;
+  }
+  __syncthreads();
+  unsigned long long higher = above0 + (at_or_above - mine);   // above this thread's digits
+  for (int w = warp + 1; w < THREADS / 32; ++w) higher += s_warp_tot[w];
+  int found = -1;
+  unsigned long long found_above = 0ull;
+  for (int j = per - 1; j >= 0; --j) {
+    const unsigned long long v = value(tid * per + j);
+    if (found < 0 && higher + v >= target) {
+      found = tid * per + j;
+      found_above = higher;
+    }
+    higher += v;
+  }
+  if (found > 0) atomicMax(s_pick, (unsigned)found);
+  __syncthreads();
+  digit = *s_pick;
+  if (found >= 0 && (unsigned)found == digit) *s_above = found_above;
+  if (digit == 0u && tid == 0 && found != 0) *s_above = higher - value(0);   // nothing reached the target
+  __syncthreads();
+  above = *s_above;
+  __syncthreads();
+}
+
 __global__ void __launch_bounds__(THREADS, 1) sample_kernel(
     const float* __restrict__ logits, int V, int* __restrict__ out_ids, float temperature, int top_k,
     float top_p, float penalty, int* __restrict__ counts, const int* __restrict__ count_rows,
@@ -95,25 +169,26 @@ __global__ void __launch_bounds__(THREADS, 1) sample_kernel(
     int* __restrict__ feedback) {
   __shared__ float s_val[32];
   __shared__ int s_idx[32];
-  __shared__ float s_red[33];
-  __shared__ unsigned s_hist[256];
-  __shared__ float s_fhist[256];
-  __shared__ unsigned s_sel[2];   // chosen digit, remaining rank
-  __shared__ float s_fsel;        // mass above the chosen digit
+  __shared__ unsigned long long s_warp_tot[THREADS / 32];
+  __shared__ unsigned s_pick;
+  __shared__ unsigned long long s_above;
   __shared__ float s_warp[THREADS / 32];
   __shared__ int s_result;
-  extern __shared__ float s_iter[];   // [THREADS / 32][ceil(V / (4 THREADS))]: sums of pieces of 128 indices
+  // dynamic: the radix select's histograms [3][4096] (counts use the first; masses three limbs), then
+  // [THREADS / 32][ceil(V / (4 THREADS))] sums of pieces of 128 indices
+  extern __shared__ unsigned s_dyn[];
+  unsigned* s_hist = s_dyn;
+  float* s_iter = reinterpret_cast<float*>(s_dyn + 3 * DIGITS0);
 
   const int row = blockIdx.x, tid = threadIdx.x;
   int* my_counts = (counts && penalty != 1.0f) ? counts + (size_t)count_rows[row] * V : nullptr;
-  RowView view{logits + (size_t)row * V, my_counts, penalty};
+  const RowView view{logits + (size_t)row * V, my_counts, penalty, V};
 
   // ---- maximum and argmax (needed by both modes) -------------------------
   float best = -CUDART_INF_F;
   int best_i = 0x7fffffff;
-  if (my_counts == nullptr && (V & 3) == 0) {
-    // plain logits in rows of whole 16-byte vectors: four at a time, several vectors in flight per thread
-    // (a thread's indices still rise, so the first of equal values stays)
+  if (my_counts == nullptr && view.vectors()) {
+    // plain logits, four at a time (a thread's indices rise, so the first of equal values stays)
     const float4* row4 = reinterpret_cast<const float4*>(view.logits);
 #pragma unroll 4
     for (int i = tid; i < (V >> 2); i += THREADS) {
@@ -124,10 +199,9 @@ __global__ void __launch_bounds__(THREADS, 1) sample_kernel(
       if (x.w > best) { best = x.w; best_i = 4 * i + 3; }
     }
   } else {
-    for (int v = tid; v < V; v += THREADS) {
-      const float x = view.at(v);
+    view.for_all([&](int v, float x) {
       if (x > best) { best = x; best_i = v; }
-    }
+    });
   }
   block_argmax(best, best_i, s_val, s_idx);
   const float x_max = s_val[0];
@@ -135,32 +209,27 @@ __global__ void __launch_bounds__(THREADS, 1) sample_kernel(
 
   if (temperature > 0.0f) {
     // ---- top-k threshold: key of the k-th largest value -------------------
+    // three passes over digits of 12, 10 and 10 bits of the ordered keys
     unsigned thr_key = 0u;
     if (top_k > 0 && top_k < V) {
-      unsigned prefix = 0u, mask = 0u, rank = (unsigned)top_k;
-      for (int shift = 24; shift >= 0; shift -= 8) {
-        if (tid < 256) s_hist[tid] = 0u;
+      unsigned prefix = 0u, mask = 0u;
+      unsigned long long rank = (unsigned long long)top_k;
+      for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 20 : pass == 1 ? 10 : 0, n_digits = pass == 0 ? DIGITS0 : 1024;
+        for (int i = tid; i < n_digits; i += THREADS) s_hist[i] = 0u;
         __syncthreads();
-        for (int v = tid; v < V; v += THREADS) {
-          const unsigned key = ordered_key(view.at(v));
-          if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & 255u], 1u);
-        }
+        view.for_all([&](int, float x) {
+          const unsigned key = ordered_key(x);
+          if ((key & mask) == prefix) atomicAdd(&s_hist[(key >> shift) & (n_digits - 1)], 1u);
+        });
         __syncthreads();
-        if (tid == 0) {
-          unsigned above = 0u;
-          int b = 255;
-          for (; b > 0; --b) {
-            if (above + s_hist[b] >= rank) break;
-            above += s_hist[b];
-          }
-          s_sel[0] = (unsigned)b;
-          s_sel[1] = rank - above;
-        }
-        __syncthreads();
-        prefix |= s_sel[0] << shift;
-        mask |= 255u << shift;
-        rank = s_sel[1];
-        __syncthreads();
+        unsigned digit;
+        unsigned long long above;
+        pick_digit([&](int d) { return (unsigned long long)s_hist[d]; }, n_digits / THREADS, 0ull, rank, s_warp_tot,
+                   &s_pick, &s_above, digit, above);
+        prefix |= digit << shift;
+        mask |= (unsigned)(n_digits - 1) << shift;
+        rank -= above;
       }
       thr_key = prefix;
     }
@@ -171,43 +240,47 @@ __global__ void __launch_bounds__(THREADS, 1) sample_kernel(
       if (ordered_key(x) < thr_key || !(x == x)) return 0.0f;
       return exp2f(fmaf(x, w_a, -w_b));   // -inf gives 0
     };
-    auto weight = [&](int v) -> float { return weight_of(view.at(v)); };
-    // ---- normaliser (only the top-p threshold needs it) ----------------------
-    float z = 0.0f;
-    if (top_p < 1.0f) {
-      for (int v = tid; v < V; v += THREADS) z += weight(v);
-      z = jb::block_sum(z, s_red);
-    }
     // ---- top-p threshold on the weights -------------------------------------
+    // The smallest weight t such that the weights >= t together reach top_p of all the mass: a radix
+    // select over the weights' bit patterns in digits of 12, 10 and 10 bits, with the mass of each digit
+    // in a histogram.  Masses are added as integers: a weight (at most 1) in units of 2^-33, as three
+    // limbs of 11 bits in 32-bit histograms (2^20 limbs fit), because shared memory adds 32-bit integers
+    // natively, and integer sums are exact whatever their order: the threshold is the same every run.
     unsigned thr_bits = 0u;
     if (top_p < 1.0f) {
-      const float target = top_p * z;
       unsigned prefix = 0u, mask = 0u;
-      float above_mass = 0.0f;
-      for (int shift = 24; shift >= 0; shift -= 8) {
-        if (tid < 256) s_fhist[tid] = 0.0f;
+      unsigned long long above = 0ull, target = 0ull;
+      for (int pass = 0; pass < 3; ++pass) {
+        const int shift = pass == 0 ? 20 : pass == 1 ? 10 : 0, n_digits = pass == 0 ? DIGITS0 : 1024;
+        for (int i = tid; i < 3 * DIGITS0; i += THREADS) s_hist[i] = 0u;
         __syncthreads();
-        for (int v = tid; v < V; v += THREADS) {
-          const float w = weight(v);
+        view.for_all([&](int, float x) {
+          const float w = weight_of(x);
           const unsigned key = __float_as_uint(w);
-          if (w > 0.0f && (key & mask) == prefix) atomicAdd(&s_fhist[(key >> shift) & 255u], w);
-        }
-        __syncthreads();
-        if (tid == 0) {
-          float above = above_mass;
-          int b = 255;
-          for (; b > 0; --b) {
-            if (above + s_fhist[b] >= target) break;
-            above += s_fhist[b];
+          if (w > 0.0f && (key & mask) == prefix) {
+            const unsigned long long fx = __float2ull_rn(w * 8589934592.0f);
+            unsigned* h = s_hist + ((key >> shift) & (n_digits - 1));
+            atomicAdd(h, (unsigned)(fx & 2047u));
+            atomicAdd(h + DIGITS0, (unsigned)((fx >> 11) & 2047u));
+            atomicAdd(h + 2 * DIGITS0, (unsigned)(fx >> 22));
           }
-          s_sel[0] = (unsigned)b;
-          s_fsel = above;
+        });
+        __syncthreads();
+        auto mass = [&](int d) {
+          return ((unsigned long long)s_hist[2 * DIGITS0 + d] << 22) + ((unsigned long long)s_hist[DIGITS0 + d] << 11) +
+                 (unsigned long long)s_hist[d];
+        };
+        if (pass == 0) {   // the first pass has seen every weight: the mass to reach
+          unsigned dummy;
+          unsigned long long all;
+          pick_digit(mass, n_digits / THREADS, 0ull, ~0ull, s_warp_tot, &s_pick, &s_above, dummy, all);
+          all += mass(0);
+          target = (unsigned long long)((double)top_p * (double)all);
         }
-        __syncthreads();
-        prefix |= s_sel[0] << shift;
-        mask |= 255u << shift;
-        above_mass = s_fsel;
-        __syncthreads();
+        unsigned digit;
+        pick_digit(mass, n_digits / THREADS, above, target, s_warp_tot, &s_pick, &s_above, digit, above);
+        prefix |= digit << shift;
+        mask |= (unsigned)(n_digits - 1) << shift;
       }
       thr_bits = prefix;
     }
@@ -222,11 +295,10 @@ __global__ void __launch_bounds__(THREADS, 1) sample_kernel(
     // every thread, so the interval that holds the target has exactly one owner.
     const int warp = tid >> 5, lane = tid & 31;
     const int iters = (V + 4 * THREADS - 1) / (4 * THREADS);
-    const bool vec = my_counts == nullptr && (V & 3) == 0;
     auto four = [&](int v0, float* w) {   // the kept weights of indices v0 .. v0 + 3
-      if (vec) {
+      if (view.vectors()) {
         float4 x = make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
-        if (v0 < V) x = *reinterpret_cast<const float4*>(view.logits + v0);
+        if (v0 < V) x = view.at4(v0);
         w[0] = kept_of(x.x), w[1] = kept_of(x.y), w[2] = kept_of(x.z), w[3] = kept_of(x.w);
       } else {
 #pragma unroll
@@ -318,8 +390,11 @@ JB_EXPORT int jb_sample(const float* logits, int B, int V, int* out_ids, float t
   JB_REFUSE(temperature < 0.0f, "sample: negative temperature %f", temperature);
   JB_REFUSE(penalty <= 0.0f, "sample: repetition penalty %f must be positive", penalty);
   JB_REFUSE(feedback != nullptr && count_rows == nullptr, "sample: feedback needs the rows' slots");
-  // shared memory for the sums of the pieces of 128 indices (used when temperature > 0)
-  const size_t smem = temperature > 0.0f ? (size_t)((V + 4 * THREADS - 1) / (4 * THREADS)) * (THREADS / 32) * sizeof(float) : 0;
+  // shared memory (used when temperature > 0): the radix select's histograms and the sums of the pieces of
+  // 128 indices
+  const size_t smem = temperature > 0.0f ? 3 * DIGITS0 * sizeof(unsigned) +
+                                               (size_t)((V + 4 * THREADS - 1) / (4 * THREADS)) * (THREADS / 32) * sizeof(float)
+                                         : 0;
   JB_REFUSE(smem > 200 * 1024, "sample: a vocabulary of %d is too large for temperature sampling", V);
   static size_t smem_allowed = 48 * 1024;
   if (smem > smem_allowed) {
