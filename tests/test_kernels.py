@@ -648,6 +648,33 @@ def test_temperature_sampling_follows_the_plain_distribution(ops, V, top_k, top_
     assert again != got
 
 
+@pytest.mark.parametrize("V", [5003, 32000])
+def test_sampling_with_every_option_draws_from_the_plain_kept_set_at_every_step(ops, V):
+    """Repetition penalty, top-k, temperature and top-p together, 40 steps of 16 rows: every drawn token has a
+    probability above zero in the plain distribution over the same context, its interval of the cumulative
+    distribution holds the step's number, and the kernel's own counts follow what it drew."""
+    B, T, top_k, top_p, pen = 16, 0.9, 60, 0.85, 1.3
+    g = torch.Generator().manual_seed(V)
+    counts = torch.zeros(B, V, dtype=torch.int32, device=DEV)
+    context = [[] for _ in range(B)]
+    for step in range(40):
+        logits = (torch.randn(B, V, generator=g) * 2.0).to(DEV)
+        got = run_sample(ops, logits, T, top_k, top_p, penalty=pen, counts=counts, seed=9,
+                         steps=torch.full((B,), step, dtype=torch.int32, device=DEV))
+        for b in range(B):
+            probs = P.sampling_distribution(logits[b].cpu(), T, top_k, top_p, pen, context[b]).double()
+            assert probs[got[b]] > 0, f"step {step} row {b}: token {got[b]} is outside the kept set"
+            cdf = torch.cumsum(probs, 0)
+            u = P.uniform_for(9, b, step)
+            assert float(cdf[got[b]] - probs[got[b]]) - 2e-4 <= u < float(cdf[got[b]]) + 2e-4
+            context[b].append(got[b])
+    want = torch.zeros(B, V, dtype=torch.int32)
+    for b in range(B):
+        for t in context[b]:
+            want[b, t] += 1
+    assert torch.equal(counts.cpu(), want)
+
+
 def test_repetition_penalty_counts(ops):
     V = 300
     logits = torch.zeros(2, V, device=DEV)
