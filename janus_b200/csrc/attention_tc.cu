@@ -273,7 +273,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
-    float scale_log2, int* __restrict__ status) {
+    float scale_log2, int heads_slowest, int* __restrict__ status) {
   constexpr int N_BARS = bars_for(NT), TMEM_COLS = NT * 256, TMEM_S0 = 0, TMEM_O0 = NT * 128;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
@@ -325,9 +325,11 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   // ---- which rows, which keys ----
   const int G = nh / nkv;
   const int tpt = BM / G;  // tokens per tile
-  // kv heads run fastest in the order CTAs are handed out, so that across all heads the longest key ranges start first
-  const int seq = blockIdx.z, kvh = blockIdx.x;
-  const int pair = gridDim.y - 1 - blockIdx.y;
+  // kv heads run fastest in the order CTAs are handed out, so that across all heads the longest key ranges start
+  // first; a prompt so long that the keys and values of all heads together overflow L2 runs head after head
+  // (heads_slowest: the grid's x and y change places), so that the CTAs at work share one head's keys
+  const int seq = blockIdx.z, kvh = heads_slowest ? blockIdx.y : blockIdx.x;
+  const int pair = heads_slowest ? gridDim.x - 1 - blockIdx.x : gridDim.y - 1 - blockIdx.y;
   const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
   const int tok_first = pair * NT * tpt;        // first token of the first tile
   const bool active = tok_first < q_len;        // uniform for the CTA
@@ -523,7 +525,7 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
     const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
-    float scale_log2, int* __restrict__ status) {
+    float scale_log2, int heads_slowest, int* __restrict__ status) {
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_s = smem_u32(smem);
@@ -568,9 +570,11 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
 
   const int G = nh / nkv;
   const int tpt = BM / G;
-  // kv heads run fastest in the order CTAs are handed out, so that across all heads the longest key ranges start first
-  const int seq = blockIdx.z, kvh = blockIdx.x;
-  const int pair = gridDim.y - 1 - blockIdx.y;
+  // kv heads run fastest in the order CTAs are handed out, so that across all heads the longest key ranges start
+  // first; a prompt so long that the keys and values of all heads together overflow L2 runs head after head
+  // (heads_slowest: the grid's x and y change places), so that the CTAs at work share one head's keys
+  const int seq = blockIdx.z, kvh = heads_slowest ? blockIdx.y : blockIdx.x;
+  const int pair = heads_slowest ? gridDim.x - 1 - blockIdx.x : gridDim.y - 1 - blockIdx.y;
   const int qs = q_start[seq], q_len = q_start[seq + 1] - qs;
   const int tok_first = pair * 2 * tpt;
   const bool active = tok_first < q_len;
@@ -825,14 +829,18 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
+  // keys and values of the longest sequence over all kv heads against L2 (126 MB; the rest is for Q, O and
+  // the other sequences' traffic)
+  const bool heads_slowest = (long long)max_pages * PAGE * nkv * hd * 4 > 96ll * 1024 * 1024;
   if (pairs) {
-    dim3 grid(nkv, (n_tiles + 1) / 2, n_seqs);
+    const int n_pairs = (n_tiles + 1) / 2;
+    dim3 grid(heads_slowest ? n_pairs : nkv, heads_slowest ? nkv : n_pairs, n_seqs);
     jb::Launch cfg(grid, dim3(T2_THREADS), T2_SMEM, stream);
     return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc128_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
-                                   nkv, hd, max_pages, window, scale * LOG2E, status);
+                                   nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status);
   }
-  dim3 grid(nkv, n_tiles, n_seqs);
+  dim3 grid(heads_slowest ? n_tiles : nkv, heads_slowest ? nkv : n_tiles, n_seqs);
   jb::Launch cfg(grid, dim3(threads_for(1)), smem_for(1), stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<1>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
-                                 nkv, hd, max_pages, window, scale * LOG2E, status);
+                                 nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status);
 }

@@ -262,6 +262,28 @@ def test_attention_tc_prefill(ops, nh, nkv, hd, window, tiles, monkeypatch):
         close(out, ref, 1.5e-2)
 
 
+@pytest.mark.parametrize("tiles", ["1", "2"])
+@pytest.mark.parametrize("nh, nkv, hd, window", [(32, 8, 128, 0), (6, 2, 96, 90), (8, 1, 64, 0)])
+def test_attention_tc_prefill_head_after_head(ops, nh, nkv, hd, window, tiles, monkeypatch):
+    """A block table wide enough for sequences whose keys and values would overflow L2 makes the kernel hand
+    its CTAs out head after head instead of kv heads fastest (the grid's x and y change places): the same
+    results."""
+    monkeypatch.setenv("JANUS_ATTN_TC_TILES", tiles)
+    lens, q_lens = [130, 5, 300, 257], [130, 2, 17, 257]
+    qs, ks, vs = attention_case(nh, nkv, hd, lens, q_lens, torch.bfloat16, seed=4)
+    kc, vc, bt = paged(ks, vs, torch.bfloat16, seed=4)
+    width = 96 * 1024 * 1024 // (PAGE * nkv * hd * 4) + 8
+    bt = torch.cat([bt, torch.full((bt.shape[0], width), -1, dtype=bt.dtype, device=bt.device)], 1).contiguous()
+    q = torch.cat([x[n - nq:].reshape(nq, -1) for x, n, nq in zip(qs, lens, q_lens)]).to(DEV).to(torch.bfloat16)
+    q_start = torch.tensor([0] + torch.tensor(q_lens).cumsum(0).tolist(), device=DEV, dtype=torch.int32)
+    kv_len = torch.tensor(lens, device=DEV, dtype=torch.int32)
+    out = torch.full_like(q, float("nan"))
+    ops.attention_tc_prefill(q, kc, vc, out, bt, q_start, kv_len, len(lens), max(q_lens), nh, nkv, hd, PAGE,
+                             window, 1 / math.sqrt(hd))
+    ops.check_kernel_status(torch.device(DEV))
+    close(out, plain_attention_rows(qs, ks, vs, q_lens, window), 1.5e-2)
+
+
 class _WS:
     def __init__(self):
         self.bufs = {}
