@@ -1,11 +1,12 @@
 // Causal grouped-query flash attention for prefill on the 5th-generation tensor
-// cores (tcgen05) of sm_100a, over the paged cache.  Built for a row of 64 or 128 dims in shared memory
-// (-DJB_HEAD_DIM); the head size itself is an argument, any multiple of 8 up to that: the tensor maps
+// cores (tcgen05) of sm_100a, over the paged cache.  Built for a row of 64, 128 or 256 dims in shared memory
+// (-DJB_HEAD_DIM; rows of 256 have the one-tile kernel only, with a ring of two pages: O alone takes 256
+// columns of tensor memory); the head size itself is an argument, any multiple of 8 up to that: the tensor maps
 // have the true extent, so the copy engine fills the rest of a row with zeros, the score product skips
 // the 16-dim steps that are all zero, the P.V product has N = the head size rounded up to 16, and the
 // epilogue stores the true columns only.  Any number of query heads per kv head up to 128: a tile holds
 // floor(128 / G) tokens x G heads, and the rows left over (2 of 128 with 3, 6 or 7 heads per kv head)
-// belong to no token.  Larger head sizes take the mma.sync kernel of attention_bf16.cu.
+// belong to no token.
 //
 // Two kernels.  prefill_tc_kernel: one CTA owns a tile of 128 rows = (token, query head of one kv group)
 // pairs of one sequence and walks its causal range of 64-key pages:
@@ -42,11 +43,11 @@ namespace {
 typedef __nv_bfloat16 bf16;
 
 constexpr int HD = JB_HEAD_DIM;
-static_assert(HD == 64 || HD == 128, "the tcgen05 attention kernel is built for rows of 64 or 128 dims");
+static_assert(HD == 64 || HD == 128 || HD == 256, "the tcgen05 attention kernel is built for rows of 64, 128 or 256 dims");
 constexpr int NH64 = HD / 64;          // 64-column halves of a row
 constexpr int BM = 128;                // rows per CTA = TMEM lanes
 constexpr int PAGE = 64;               // keys per block
-constexpr int STAGES = 3;
+constexpr int STAGES = HD > 128 ? 2 : 3;
 constexpr int MAX_NT = 1;              // row tiles per CTA of prefill_tc_kernel<NT> (written for 1 or 2; 1 is what runs)
 constexpr int threads_for(int nt) { return 64 + nt * 128; }
 constexpr int Q_BYTES = NH64 * BM * 128;
@@ -274,7 +275,9 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const __grid_constant__ CUtensorMap map_v, bf16* __restrict__ out, const int* __restrict__ block_table,
     const int* __restrict__ q_start, const int* __restrict__ kv_len, int nh, int nkv, int hd, int max_pages, int window,
     float scale_log2, int heads_slowest, int* __restrict__ status) {
-  constexpr int N_BARS = bars_for(NT), TMEM_COLS = NT * 256, TMEM_S0 = 0, TMEM_O0 = NT * 128;
+  // S of tile w: two buffers of 64 columns at w * 128; O behind them (HD columns a tile; 512 in all for rows of 256)
+  constexpr int N_BARS = bars_for(NT), TMEM_COLS = HD > 128 ? 512 : NT * 256, TMEM_S0 = 0, TMEM_O0 = NT * 128;
+  static_assert(NT * 128 + NT * HD <= TMEM_COLS, "tensor memory of one CTA");
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
   const uint32_t q_s = smem_u32(smem);                       // [NT] Q tiles
@@ -399,7 +402,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
           tc_fence_after();
 #pragma unroll
           for (int ks = 0; ks < 4; ++ks)  // P lies over the first 32 columns of its S buffer: 8 columns per 16 keys
-            umma_ts(tmem + TMEM_O0 + w * 128, tmem + TMEM_S0 + w * 128 + b * 64 + ks * 8,
+            umma_ts(tmem + TMEM_O0 + w * HD, tmem + TMEM_S0 + w * 128 + b * 64 + ks * 8,
                     desc_mn_sw128(v_base + ks * 2048, PAGE * 128, 1024), idesc_o, (j | ks) ? 1u : 0u);
           umma_commit(o_full(w));
           if (j == nb - 1) umma_commit(o_done(w));
@@ -417,7 +420,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
     const int row_pos = valid ? pos_first + tl : -1;
     const int row_lo = window > 0 ? max(0, row_pos - window + 1) : 0;
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
-    const uint32_t s_col = TMEM_S0 + w * 128, o_col = TMEM_O0 + w * 128;
+    const uint32_t s_col = TMEM_S0 + w * 128, o_col = TMEM_O0 + w * HD;
     float m_ref = -CUDART_INF_F, l = 0.0f;   // l is the row sum relative to m_ref
     bool ok = true;
     for (int j = 0; j < nb && ok; ++j) {
@@ -505,6 +508,7 @@ __global__ void __launch_bounds__(threads_for(NT), 1) prefill_tc_kernel(
   }
 }
 
+#if JB_HEAD_DIM <= 128
 // ---------------------------------------------------------------------------
 // Two row tiles per CTA over blocks of 128 keys (two pages): every MMA has N = 128 (an MMA of N = 64 takes as
 // long), S has one 128-column buffer per tile and P lies over its first half, so the two tiles take turns on
@@ -750,6 +754,8 @@ __global__ void __launch_bounds__(T2_THREADS, 1) prefill_tc128_kernel(
   }
 }
 
+#endif  // JB_HEAD_DIM <= 128
+
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -816,7 +822,7 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
   const long long ctas_of_pairs = (long long)((n_tiles + 1) / 2) * nkv * n_seqs;
   int dev = 0, sms = 148;
   if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-  bool pairs = ctas_of_pairs >= sms;
+  [[maybe_unused]] bool pairs = ctas_of_pairs >= sms;
   if (const char* e = getenv("JANUS_ATTN_TC_TILES")) {   // 1 or 2: tiles per CTA whatever the size (for tests and measurements)
     if (e[0] == '1') pairs = false;
     if (e[0] == '2') pairs = true;
@@ -824,14 +830,17 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(prefill_tc_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem_for(1));
+#if JB_HEAD_DIM <= 128
     if (e == cudaSuccess)
       e = cudaFuncSetAttribute(prefill_tc128_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, T2_SMEM);
+#endif
     if (e != cudaSuccess) return (int)e;
     configured = true;
   }
   // keys and values of the longest sequence over all kv heads against L2 (126 MB; the rest is for Q, O and
   // the other sequences' traffic)
   const bool heads_slowest = (long long)max_pages * PAGE * nkv * hd * 4 > 96ll * 1024 * 1024;
+#if JB_HEAD_DIM <= 128
   if (pairs) {
     const int n_pairs = (n_tiles + 1) / 2;
     dim3 grid(heads_slowest ? n_pairs : nkv, heads_slowest ? nkv : n_pairs, n_seqs);
@@ -839,6 +848,7 @@ JB_EXPORT int jb_attention_tc_prefill(const void* q, const void* k_cache, const 
     return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc128_kernel, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,
                                    nkv, hd, max_pages, window, scale * LOG2E, heads_slowest ? 1 : 0, status);
   }
+#endif
   dim3 grid(heads_slowest ? n_tiles : nkv, heads_slowest ? nkv : n_tiles, n_seqs);
   jb::Launch cfg(grid, dim3(threads_for(1)), smem_for(1), stream);
   return (int)cudaLaunchKernelEx(&cfg.c, prefill_tc_kernel<1>, mq, mk, mv, (bf16*)out, block_table, q_start, kv_len, nh,

@@ -836,8 +836,8 @@ def attention_bf16_decode(q: Optional[torch.Tensor], k_cache: torch.Tensor, v_ca
         scale, int(n_splits), int(write_kv), _stream()), "attention_bf16_decode_fused", kernels=kernels)
 
 
-# -- tcgen05 prefill attention (head sizes up to 128 in steps of 8, up to 128 query heads per kv head) -----
-ATTENTION_TC_MAX_HEAD_DIM = 128
+# -- tcgen05 prefill attention (head sizes up to 256 in steps of 8, up to 128 query heads per kv head) -----
+ATTENTION_TC_MAX_HEAD_DIM = 256
 
 
 def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
@@ -847,8 +847,8 @@ def attention_tc_supported(nh: int, nkv: int, hd: int) -> bool:
 
 
 def _attention_tc_row(hd: int) -> int:
-    """The build that takes head size `hd`: rows of 64 or of 128 dims in shared memory."""
-    return 64 if hd <= 64 else 128
+    """The build that takes head size `hd`: rows of 64, 128 or 256 dims in shared memory."""
+    return 64 if hd <= 64 else 128 if hd <= 128 else 256
 
 
 def attention_tc_prefill(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,

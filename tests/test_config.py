@@ -164,8 +164,7 @@ def test_keys_the_kernels_cannot_honour_are_refused_by_name():
 def test_sizes_the_attention_kernels_cannot_take_are_refused_when_the_model_is_built():
     """head sizes and group sizes that a kernel would refuse at the first step are refused by the part's
     constructor: bfloat16 needs head_dim % 8 == 0 and at most 64 query heads per kv head unless the tensor-core
-    prompt kernel takes the shape (head sizes up to 128, groups up to 128); float32 takes them all up to
-    head_dim 256."""
+    prompt kernel takes the shape (groups up to 128); float32 takes them all up to head_dim 256."""
     import torch
     from janus_b200.config import resolve_architecture
     from helpers import TINY_A
@@ -179,15 +178,13 @@ def test_sizes_the_attention_kernels_cannot_take_are_refused_when_the_model_is_b
     build(torch.float32, head_dim=12)
     with pytest.raises(ValueError, match="multiple of 8"):
         build(torch.bfloat16, head_dim=12)
-    # 96 query heads on one kv head: with a head of 136 no kernel of the bfloat16 prompt path takes that group,
-    # with a head of 16 the tensor-core kernel does; 136 heads on one kv head are too many for it too
-    build(torch.float32, hidden_size=96, num_attention_heads=96, num_key_value_heads=1, head_dim=136)
-    with pytest.raises(ValueError, match="query heads per key/value head"):
-        build(torch.bfloat16, hidden_size=96, num_attention_heads=96, num_key_value_heads=1, head_dim=136)
+    # 96 query heads on one kv head: the tensor-core prompt kernel takes groups of up to 128 at every head size
+    # that the bfloat16 path has; 136 heads on one kv head are too many for it
+    build(torch.bfloat16, hidden_size=96, num_attention_heads=96, num_key_value_heads=1, head_dim=136)
     build(torch.bfloat16, hidden_size=96, num_attention_heads=96, num_key_value_heads=1, head_dim=16)
+    build(torch.float32, hidden_size=136, num_attention_heads=136, num_key_value_heads=1, head_dim=16)
     with pytest.raises(ValueError, match="query heads per key/value head"):
         build(torch.bfloat16, hidden_size=136, num_attention_heads=136, num_key_value_heads=1, head_dim=16)
-    build(torch.bfloat16, hidden_size=64, num_attention_heads=64, num_key_value_heads=1, head_dim=136)
 
 
 def test_layers_share_one_rotary_table_no_longer_than_the_engine_needs():

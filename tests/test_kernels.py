@@ -237,7 +237,10 @@ def test_attention_bf16_prefill(ops, nh, nkv, hd, window):
                                                  # rest arrives as zeros, a last 16-dim step or store may be half
                                                  (6, 2, 96, 0), (4, 1, 40, 70), (8, 8, 80, 0), (5, 1, 120, 0),
                                                  (9, 3, 24, 0), (4, 2, 8, 0), (12, 4, 104, 90), (8, 2, 56, 0),
-                                                 (16, 4, 112, 0), (4, 4, 72, 0), (3, 1, 48, 30)])
+                                                 (16, 4, 112, 0), (4, 4, 72, 0), (3, 1, 48, 30),
+                                                 # rows of 256 dims: the one-tile kernel with a ring of two pages
+                                                 (4, 2, 256, 0), (6, 2, 192, 100), (5, 1, 136, 0), (8, 8, 200, 0),
+                                                 (3, 3, 248, 70)])
 def test_attention_tc_prefill(ops, nh, nkv, hd, window, tiles, monkeypatch):
     """The tcgen05 kernel against the plain attention: ragged batch, chunked prompts
     (queries are the last q_len positions), a far key that stands out; the one-tile kernel and the
