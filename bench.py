@@ -524,6 +524,35 @@ def run_kernels(contexts=None, shape="8b", head_sizes=None):
             product("gate_up (SiLU gate)", T, I, H, "swiglu")
             product("down (add)", T, H, I, "add")
         product("lm_head", 8, V, H, "store", copies=3)
+        # the RMS norm (float32 rows in, bfloat16 out) at a decode step's and at prompts' row counts
+        gamma = torch.ones(H, device=dev, dtype=torch.bfloat16)
+        for T in (8, 2048, 16384):
+            xs = [torch.randn(T, H, device=dev) for _ in range(4)]
+            y = torch.empty(T, H, device=dev, dtype=torch.bfloat16)
+            turn = [0]
+
+            def norm():
+                ops.rmsnorm(xs[turn[0] % 4], gamma, 1e-5, y)
+                turn[0] += 1
+
+            us = timed(norm)
+            print(json.dumps({"kernel": "rmsnorm", "rows": T, "us": round(us, 1),
+                              "GBps": round(T * H * 6 / us / 1e3, 1)}), flush=True)
+        # the sampling kernel over a decode step's logits (8 rows of the vocabulary), option by option
+        from janus_b200.sampling import DeviceSampler, SamplerConfig
+        logits = torch.randn(8, V, device=dev) * 3
+        rows = torch.arange(8, device=dev, dtype=torch.int32)
+        for name, kw in (("greedy", dict(temperature=0.0)),
+                         ("greedy, repetition penalty 1.15", dict(temperature=0.0, repetition_penalty=1.15)),
+                         ("temperature 0.8", dict(temperature=0.8)),
+                         ("temperature 0.8, top-k 50", dict(temperature=0.8, top_k=50)),
+                         ("temperature 0.8, top-p 0.9", dict(temperature=0.8, top_p=0.9)),
+                         ("temperature 0.8, top-k 50, top-p 0.9, repetition penalty 1.15",
+                          dict(temperature=0.8, top_k=50, top_p=0.9, repetition_penalty=1.15))):
+            sampler = DeviceSampler(SamplerConfig(max_tokens=8, **kw), V, 8, 0, torch.device(dev))
+            us = timed(lambda: sampler.sample(logits, rows, rows, rows))
+            print(json.dumps({"kernel": f"sample ({name})", "rows": 8, "vocabulary": V, "us": round(us, 1)}),
+                  flush=True)
 
     cases = [(b, c) for c in contexts for b in (1, 8, 64) if b * c <= 1 << 21] if contexts else ((1, 2080), (8, 2080), (64, 2080))
     if head_sizes:
