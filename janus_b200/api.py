@@ -189,6 +189,8 @@ def _build(config_dict: dict, checkpoint_factory, dtype, max_tokens: int, max_se
     if not torch.cuda.is_available():
         raise RuntimeError("janus_b200 needs a CUDA device (sm_100a); there is no CPU path")
     device = torch.device(device)
+    from .kernels import ops
+    ops.bind_device(device)
     torch_dtype = parse_dtype(dtype)
     arch = resolve_architecture(config_dict)
     config = arch.config_class.from_dict(config_dict)

@@ -396,11 +396,16 @@ JB_EXPORT int jb_sample(const float* logits, int B, int V, int* out_ids, float t
                                                (size_t)((V + 4 * THREADS - 1) / (4 * THREADS)) * (THREADS / 32) * sizeof(float)
                                          : 0;
   JB_REFUSE(smem > 200 * 1024, "sample: a vocabulary of %d is too large for temperature sampling", V);
-  static size_t smem_allowed = 48 * 1024;
-  if (smem > smem_allowed) {
-    const cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+  if (smem > 48 * 1024) {   // the limit is raised per device, the first time a launch on it needs more
+    static size_t smem_allowed[64];
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
-    smem_allowed = smem;
+    if (device < 0 || device >= 64 || smem > smem_allowed[device]) {
+      e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+      if (e != cudaSuccess) return (int)e;
+      if (device >= 0 && device < 64) smem_allowed[device] = smem;
+    }
   }
   sample_kernel<<<B, THREADS, smem, stream>>>(logits, V, out_ids, temperature, top_k, top_p, penalty, counts,
                                               count_rows, seed, seq_ids, steps, feedback);

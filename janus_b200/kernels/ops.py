@@ -294,6 +294,22 @@ _status = {}
 SM_COUNT_TARGET = 296      # CTAs wanted in flight for a weight-streaming product (two per SM)
 
 
+_bound_device = []
+
+
+def bind_device(device: torch.device) -> None:
+    """One process drives one GPU: the kernel libraries set their kernels up (shared-memory limits, occupancy,
+    SM count) for the device of their first launch and keep that.  The first model names the device; a model
+    on another device is refused here, not at some launch."""
+    index = torch.device(device).index
+    index = torch.cuda.current_device() if index is None else index
+    if not _bound_device:
+        _bound_device.append(index)
+    elif _bound_device[0] != index:
+        raise KernelError(f"this process already runs its kernels on cuda:{_bound_device[0]}; a model on "
+                          f"cuda:{index} needs a process of its own (the library drives one GPU per process)")
+
+
 def kernel_status(device: torch.device) -> torch.Tensor:
     """Device int that a kernel sets when one of its bounded waits ran out."""
     st = _status.get(device)

@@ -265,3 +265,19 @@ def test_log_levels():
         log.set_level("warn")
     with log.nvtx_range("nothing happens without JANUS_NVTX=1"):
         pass
+
+
+def test_a_second_gpu_in_one_process_is_refused_by_name():
+    """The kernel libraries are set up for the device of their first launch: the first model binds the process to
+    its GPU, a model on another one is refused when it is built."""
+    import torch
+    from janus_b200.kernels import ops
+    saved = list(ops._bound_device)
+    try:
+        ops._bound_device.clear()
+        ops.bind_device(torch.device("cuda:1"))
+        ops.bind_device(torch.device("cuda:1"))
+        with pytest.raises(ops.KernelError, match="cuda:1.*cuda:0|cuda:0.*process of its own"):
+            ops.bind_device(torch.device("cuda:0"))
+    finally:
+        ops._bound_device[:] = saved
