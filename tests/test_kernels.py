@@ -37,10 +37,13 @@ def test_embed_gather(ops, dtype):
     assert torch.equal(out.cpu(), P.embed(table.float().cpu(), ids.cpu()))
 
 
-@pytest.mark.parametrize("H", [200, 4100])
+@pytest.mark.parametrize("H", [200, 201, 2048, 3000, 4096, 4100, 9000])
 @pytest.mark.parametrize("gdt, odt", [(torch.float32, torch.float32), (torch.float32, torch.bfloat16),
                                       (torch.bfloat16, torch.bfloat16)])
 def test_rmsnorm(ops, H, gdt, odt):
+    """Every build of the kernel: rows of up to 2,048 floats (blocks of 128 threads), of up to 4,096 (256
+    threads, four vectors a thread in registers), wider ones (eight vectors, the rest of a row of 9,000 read
+    twice), and a width that is no multiple of 4 (scalar loads)."""
     T = 19
     x = torch.randn(T, H, device=DEV) * 3
     gamma = (1 + 0.1 * torch.randn(H, device=DEV)).to(gdt)
