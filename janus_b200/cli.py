@@ -112,5 +112,27 @@ def main(argv=None) -> int:
     return 0
 
 
+def run(argv=None) -> int:
+    """`main` for a person at a terminal: what the library refuses (a bad config.json, missing or misshapen
+    tensors, a prompt outside the vocabulary or longer than the cache, a size the kernels do not take) is one
+    line on stderr and exit code 1, not a traceback (JANUS_LOG=debug keeps the traceback)."""
+    from . import log
+    from .cache.pages import CacheFull
+    from .config.base import ConfigError
+    from .engine.step import StepError
+    from .kernels.build import KernelBuildError
+    from .kernels.ops import KernelError
+    from .weights.loader import WeightError
+    from .weights.safetensors_io import SafetensorsError
+    try:
+        return main(argv)
+    except (ConfigError, WeightError, SafetensorsError, StepError, CacheFull, KernelError, KernelBuildError,
+            FileNotFoundError, ValueError) as e:
+        if log.enabled("debug"):
+            raise
+        print(f"Error: {e}", file=sys.stderr)
+        return 1
+
+
 if __name__ == "__main__":
-    sys.exit(main())
+    sys.exit(run())

@@ -159,6 +159,12 @@ def test_command_line(tmp_path):
     assert got["finish_reasons"] == ["length"] * 3
     bad = subprocess.run(cmd[:3] + ["1,x,3"], capture_output=True, text=True, timeout=120)
     assert bad.returncode != 0 and "token ids" in (bad.stderr + bad.stdout)
+    # what the library refuses is one line and exit code 1, not a traceback: a token outside the vocabulary,
+    # a folder that is not there
+    for args in ([cmd[2], "1,99999,3"], [str(tmp_path / "nowhere"), "1,2"]):
+        refused = subprocess.run(cmd[:2] + args, capture_output=True, text=True, timeout=120)
+        assert refused.returncode == 1 and refused.stderr.strip().splitlines()[-1].startswith("Error: ")
+        assert "Traceback" not in refused.stderr
     # the longer spellings of the same options, prompts given as options and from a file
     listing = tmp_path / "prompts.txt"
     listing.write_text(" ".join(map(str, prompts[2])) + "\n")
