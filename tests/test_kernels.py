@@ -317,6 +317,49 @@ def test_attention_bf16_decode(ops, nh, nkv, hd, window, n_splits):
     close(out, plain_attention_rows(qs, ks, vs, q_lens, window), 1.5e-2)
 
 
+def _last_rows_attention(q, k, v, nq, window):
+    """Plain attention of the last `nq` positions of one sequence (q [n, nh, hd], k, v [n, nkv, hd]) in float64:
+    row i sees keys up to its own position, from `window` keys back."""
+    n, nh, hd = q.shape
+    nkv = k.shape[1]
+    qq = q[n - nq:].double()
+    kk = k.double().repeat_interleave(nh // nkv, 1)
+    vv = v.double().repeat_interleave(nh // nkv, 1)
+    scores = torch.einsum("qhd,khd->hqk", qq, kk) / math.sqrt(hd)
+    pos = torch.arange(n - nq, n)[:, None]
+    key = torch.arange(n)[None, :]
+    seen = (key <= pos) & ((key > pos - window) if window > 0 else torch.ones_like(key, dtype=torch.bool))
+    scores = scores.masked_fill(~seen[None], float("-inf"))
+    return torch.einsum("hqk,khd->qhd", torch.softmax(scores, -1), vv).reshape(nq, nh * hd).float()
+
+
+@pytest.mark.parametrize("window", [0, 50000])
+def test_attention_over_a_context_of_70000_keys(ops, window):
+    """Far beyond the engine tests' lengths: 1,094 pages a sequence, a key near the start that stands out for the
+    last query (a kernel that loses count of its pages or splits is far off), one token decoded (splits chosen by
+    the library and 32 given) and the last 70 tokens of the sequence as a prompt chunk on both prompt kernels;
+    with a window of 50,000 the standing-out key lies outside and must not count."""
+    nh, nkv, hd, n, nq = 4, 1, 128, 70000, 70
+    qs, ks, vs = attention_case(nh, nkv, hd, [n], [nq], torch.bfloat16, seed=6)
+    kc, vc, bt = paged(ks, vs, torch.bfloat16, seed=6)
+    ref = _last_rows_attention(qs[0], ks[0], vs[0], nq, window)
+    scale = 1 / math.sqrt(hd)
+    kv_len = torch.tensor([n], device=DEV, dtype=torch.int32)
+    q1 = qs[0][n - 1:].reshape(1, -1).to(DEV).to(torch.bfloat16)
+    for n_splits in (None, 32):
+        out = torch.full_like(q1, float("nan"))
+        ops.attention_bf16_decode(q1, kc, vc, out, bt, kv_len, nh, nkv, hd, PAGE, window, scale, _WS(), n,
+                                  n_splits=n_splits)
+        close(out, ref[-1:], 1.5e-2)
+    q = qs[0][n - nq:].reshape(nq, -1).to(DEV).to(torch.bfloat16)
+    q_start = torch.tensor([0, nq], device=DEV, dtype=torch.int32)
+    for face in (ops.attention_tc_prefill, ops.attention_bf16_prefill):
+        out = torch.full_like(q, float("nan"))
+        face(q, kc, vc, out, bt, q_start, kv_len, 1, nq, nh, nkv, hd, PAGE, window, scale)
+        ops.check_kernel_status(torch.device(DEV))
+        close(out, ref, 1.5e-2)
+
+
 @pytest.mark.parametrize("nh, nkv, hd, window, rotate", [(4, 2, 16, 0, True), (3, 1, 40, 0, True), (32, 8, 128, 0, True),
                                                          (5, 5, 72, 70, False), (40, 2, 32, 0, True)])
 def test_attention_bf16_decode_with_fused_rotation_and_append(ops, nh, nkv, hd, window, rotate):
