@@ -103,3 +103,45 @@ def test_all_32_layers_in_bfloat16_against_the_32_bit_engine():
     top2 = np.sort(f, axis=1)[:, -2:]
     clear = (top2[:, 1] - top2[:, 0]) > 6 * errs[32] * float(np.sqrt((f.astype(np.float64) ** 2).mean()))
     assert (f.argmax(1)[clear] == b.argmax(1)[clear]).all()
+
+
+def test_a_prompt_of_24000_tokens_in_bfloat16_chunks_against_the_32_bit_engine_in_one_step():
+    """A long sequence through the whole engine: 375 pages, rotation angles at positions far beyond the small
+    tests', the prompt cut into four steps of 6,000 tokens for the bfloat16 engine (prompt attention over a cache
+    that earlier steps left) and run as one step by the 32-bit engine, then three tokens one by one.  The logits
+    at the ends of the chunks, at the prompt's last tokens and at the decoded ones agree within the rounding of
+    two layers."""
+    import janus_b200
+    from janus_b200.engine import StepEntry
+    cfg = dict(architectures=["LlamaForCausalLM"], hidden_size=256, num_hidden_layers=2, num_attention_heads=4,
+               num_key_value_heads=2, head_dim=64, intermediate_size=640, vocab_size=1000,
+               max_position_embeddings=32768, rms_norm_eps=1e-5, rope_theta=500000.0,
+               rope_scaling=dict(rope_type="llama3", factor=8.0, low_freq_factor=1.0, high_freq_factor=4.0,
+                                 original_max_position_embeddings=8192),
+               tie_word_embeddings=True)
+    n, chunk = 24000, 6000
+    ids = random_tokens(n + 3, cfg["vocab_size"], 79)
+    ends = [chunk - 1, 2 * chunk - 1, 3 * chunk - 1, n - 2, n - 1]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        model = janus_b200.load_random(cfg, seed=5, dtype=dtype, max_tokens=n + 64, max_slots=1, std=0.05,
+                                       norm_std=0.02, stored_dtype="bfloat16")
+        s = model.alloc_slot()
+        rows = []
+        if dtype == "float32":
+            rows.append(model.step([StepEntry(s, ids[:n], ends)]).cpu().numpy())
+        else:
+            for c in range(0, n, chunk):
+                want = [e - c for e in ends if c <= e < c + chunk]
+                rows.append(model.step([StepEntry(s, ids[c:c + chunk], want)]).cpu().numpy())
+        for j in range(n, n + 3):
+            rows.append(model.step([StepEntry(s, [ids[j]], [0])]).cpu().numpy())
+        model.check()
+        model.free_slot(s)
+        outs[dtype] = np.concatenate(rows)
+        del model
+        torch.cuda.empty_cache()
+    assert outs["float32"].shape == (len(ends) + 3, cfg["vocab_size"])
+    err = rms_err(outs["bfloat16"], outs["float32"])
+    print(f"24,000 tokens, bfloat16 in chunks against float32 whole: {err:.4f} rms of the logits' rms")
+    assert err < BF16_LAYER_ERR * 2 ** 0.5
