@@ -20,7 +20,7 @@ the bfloat16 model's logits are compared with those of the true 32-bit engine on
 the same weights (`checked`).
 
 Other modes (one JSON line per item, none of them the headline): --kernels,
---prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline.
+--prompt-lengths, --workload 1b|13b, --deterministic, --plan-check, --cpu-baseline, --float32.
 """
 import argparse
 import json
@@ -431,6 +431,32 @@ def run_prompt_lengths(layers, which):
     model.check()
 
 
+def run_float32(layers):
+    """The true 32-bit path (the oracle's, not the serving one) at the 8B layer sizes through Model.generate:
+    8 prompts of 2,048 tokens, then 16 tokens each, and one sequence alone.  One JSON line; nothing here is the
+    headline."""
+    import torch
+
+    import janus_b200
+    cfg = dict(CONFIG_8B, num_hidden_layers=layers)
+    model = janus_b200.load_random(cfg, seed=2, dtype="float32", max_tokens=8 * 2304, max_slots=8, norm_std=0.0,
+                                   stored_dtype="bfloat16")
+    g = torch.Generator().manual_seed(0)
+    prompts = [torch.randint(0, cfg["vocab_size"], (2048,), generator=g).tolist() for _ in range(8)]
+    model.generate(prompts, max_tokens=2, ignore_eos=True)            # first touch of the workspaces
+    _, st8 = model.generate(prompts, max_tokens=16, ignore_eos=True)
+    _, st1 = model.generate(prompts[:1], max_tokens=16, ignore_eos=True)
+    n = model_numbers(cfg, layers)
+    weight_bytes = 4 * (layers * n["layer_params"] + n["head_params"])
+    ms8 = st8.decode_ms / st8.decode_steps
+    print(json.dumps({"impl": "janus_b200", "dtype": "float32", "layers": layers, "layers_of_config": 32,
+                      "decode_b8_tokens_per_s": round(st8.decode_tokens_per_s, 1), "decode_b8_ms_per_step": round(ms8, 2),
+                      "decode_b1_tokens_per_s": round(st1.decode_tokens_per_s, 1),
+                      "prefill_tokens_per_s": round(st8.prefill_tokens_per_s),
+                      "weights_GBps_b8": round(weight_bytes / ms8 / 1e6, 1),
+                      "frac_of_hbm_b8": round(weight_bytes / ms8 / 1e6 / peaks()["hbm_gbs"], 3)}), flush=True)
+
+
 def layer_weight_elems(cfg):
     hd = cfg["head_dim"]
     qkv = (cfg["num_attention_heads"] + 2 * cfg["num_key_value_heads"]) * hd * cfg["hidden_size"]
@@ -760,6 +786,9 @@ def main():
                     help="with --kernels: prompt attention alone at these head sizes, on each kernel that takes them")
     ap.add_argument("--kernel-shape", default="8b", choices=sorted(KERNEL_SHAPES),
                     help="with --kernels: the layer sizes (default: the 8B shape)")
+    ap.add_argument("--float32", action="store_true",
+                    help="time the true 32-bit path at the 8B layer sizes through generate (one JSON line; --layers, "
+                         "default 32)")
     ap.add_argument("--plan-check", action="store_true",
                     help="time the kernel and K-split that `ops.gemm_plan` picks against its alternatives for the "
                          "products of 1B-, 8B- and 13B-sized layers (one JSON line each)")
@@ -783,6 +812,9 @@ def main():
     if args.kernels:
         run_kernels([int(c) for c in args.contexts.split(",")] if args.contexts else None, args.kernel_shape,
                     [int(c) for c in args.head_sizes.split(",")] if args.head_sizes else None)
+        return 0
+    if args.float32:
+        run_float32(args.layers or 32)
         return 0
     if args.plan_check:
         run_plan_check()
