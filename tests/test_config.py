@@ -281,3 +281,24 @@ def test_a_second_gpu_in_one_process_is_refused_by_name():
             ops.bind_device(torch.device("cuda:0"))
     finally:
         ops._bound_device[:] = saved
+
+
+def test_the_reference_s_own_config_cases():
+    """The JSON documents and expected values of the reference's config tests, read from its source as text
+    (crates/janus-engine/src/model/config.rs:452-525): parsing, defaults, validation, head size."""
+    parsed = LlamaConfig.from_dict(json.loads('''{"hidden_size": 4096, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "num_key_value_heads": 32, "vocab_size": 32000, "intermediate_size": 11008,
+        "max_position_embeddings": 2048, "rms_norm_eps": 0.00001}'''))                     # config.rs:453-475
+    assert (parsed.hidden_size, parsed.num_hidden_layers, parsed.num_attention_heads, parsed.vocab_size) == \
+           (4096, 32, 32, 32000)
+    assert parsed.head_dim == 128 and parsed.intermediate_size == 11008
+    defaults = LlamaConfig.from_dict(json.loads('''{"hidden_size": 2048, "num_hidden_layers": 16,
+        "num_attention_heads": 16, "vocab_size": 50000}'''))                                # config.rs:478-495
+    assert defaults.num_key_value_heads == 16 and defaults.intermediate_size == 8192
+    assert defaults.max_position_embeddings == 2048 and defaults.rms_norm_eps == 1e-5
+    with pytest.raises(ConfigError, match="hidden_size"):                                   # config.rs:498-510
+        LlamaConfig.from_dict(json.loads('''{"hidden_size": 0, "num_hidden_layers": 32,
+            "num_attention_heads": 32, "vocab_size": 32000}'''))
+    head = LlamaConfig.from_dict(json.loads('''{"hidden_size": 4096, "num_hidden_layers": 32,
+        "num_attention_heads": 32, "vocab_size": 32000}'''))                                # config.rs:513-525
+    assert head.head_dim == 128

@@ -706,6 +706,27 @@ def test_greedy_lowest_index_wins(ops):
     assert got == [P.argmax_lowest(logits[i].cpu()) for i in range(5)] and got[:3] == [300, V - 1, 0]
 
 
+def test_the_reference_s_own_sampler_cases_on_the_device(ops):
+    """The vectors of the reference's sampler tests (crates/janus-engine/src/model/sampler.rs:871-891, 955-1000)
+    through the sampling kernel: the greedy pick, a NaN among the logits (it never wins), and the batch of two
+    rows with the default repetition penalty of 1.15 over contexts [1, 2] and [5, 6]."""
+    for logits, want in (([0.1, 0.5, 0.3, 0.9, 0.2], 3), ([5.0, 1.0, 3.0], 0), ([-1.0, -5.0, -0.5], 2),
+                         ([0.1, float("nan"), 0.3, 0.2], 2)):
+        assert run_sample(ops, torch.tensor([logits], device=DEV), 0.0) == [want]
+    rows = torch.tensor([[0.1, 0.2, 0.3, 0.9, 0.4, 0.1, 0.2, 0.1, 0.3, 0.2],
+                         [0.2, 0.1, 0.3, 0.2, 0.1, 0.4, 0.3, 0.8, 0.2, 0.1]], device=DEV)
+    counts = torch.zeros(2, 10, dtype=torch.int32, device=DEV)
+    counts[0, 1] = counts[0, 2] = counts[1, 5] = counts[1, 6] = 1
+    assert run_sample(ops, rows, 0.0, penalty=1.15, counts=counts) == [3, 7]
+    # crates/janus-engine/src/compute/ops/tests.rs:403,430 (the pick on the GPU) and :149-152 (the matrix product)
+    assert run_sample(ops, torch.tensor([[-1.0, 0.5, 4.2, 3.9, 2.0]], device=DEV), 0.0) == [2]
+    a = torch.tensor([[1., 2., 3.], [4., 5., 6.]], device=DEV)
+    b = torch.tensor([[7., 9., 11.], [8., 10., 12.]], device=DEV)
+    y = torch.empty(2, 2, device=DEV)
+    ops.gemm_f32(a, b, y)
+    assert y.flatten().tolist() == [58., 64., 139., 154.]
+
+
 @pytest.mark.parametrize("V", [384, 5003, 128256])
 @pytest.mark.parametrize("top_k, top_p", [(0, 1.0), (40, 1.0), (0, 0.8), (50, 0.9)])
 def test_temperature_sampling_follows_the_plain_distribution(ops, V, top_k, top_p):

@@ -94,3 +94,27 @@ def test_forward_prefix_property_and_schedule(tmp_path):
     assert not torch.allclose(twice, full) and not torch.allclose(shared, full)
     out = P.generate(cfg, w, ids[:5], 6)
     assert len(out) == 6 and out[0] == P.argmax_lowest(P.forward(cfg, w, ids[:5])[-1])
+
+
+def test_the_reference_s_own_op_cases():
+    """Vectors of the reference's op tests, read from its source as text
+    (crates/janus-engine/src/compute/ops/tests.rs:149-152 the matrix product with the second operand as [N, K];
+    :403 and :430 the greedy pick on the GPU)."""
+    a = torch.tensor([[1., 2., 3.], [4., 5., 6.]])
+    b = torch.tensor([[7., 9., 11.], [8., 10., 12.]])
+    assert P.linear(a, b).flatten().tolist() == [58., 64., 139., 154.]
+    assert P.argmax_lowest(torch.tensor([-1.0, 0.5, 4.2, 3.9, 2.0])) == 2
+
+
+def test_the_reference_s_own_sampler_cases():
+    """The vectors of the reference's sampler tests, read from its source as text
+    (crates/janus-engine/src/model/sampler.rs:871-891, 955-1000): the greedy pick, a NaN among the logits, and a
+    batch of two rows with its default repetition penalty of 1.15 over the contexts [1, 2] and [5, 6]."""
+    assert P.argmax_lowest(torch.tensor([0.1, 0.5, 0.3, 0.9, 0.2])) == 3
+    assert P.argmax_lowest(torch.tensor([5.0, 1.0, 3.0])) == 0
+    assert P.argmax_lowest(torch.tensor([-1.0, -5.0, -0.5])) == 2
+    assert P.argmax_lowest(torch.tensor([0.1, float("nan"), 0.3, 0.2])) == 2
+    rows = [[0.1, 0.2, 0.3, 0.9, 0.4, 0.1, 0.2, 0.1, 0.3, 0.2], [0.2, 0.1, 0.3, 0.2, 0.1, 0.4, 0.3, 0.8, 0.2, 0.1]]
+    picks = [P.sample(torch.tensor(r), 0.0, 0.0, repetition_penalty=1.15, context=c)
+             for r, c in zip(rows, ([1, 2], [5, 6]))]
+    assert picks == [3, 7]
