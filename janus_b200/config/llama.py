@@ -147,6 +147,13 @@ class LlamaConfig:
     # -- checks ------------------------------------------------------------
     def validate(self) -> None:
         """The reference's checks (config.rs:135-229) with `head_dim` free."""
+        # sizes beyond reason first: what follows from them (a head size of 3125) would name the wrong key
+        if self.hidden_size > 32768:                                     # config.rs:207-212
+            raise ConfigError(f"key 'hidden_size' ({self.hidden_size}) is unreasonably large (>32768)")
+        if self.num_hidden_layers > 256:                                 # config.rs:214-219
+            raise ConfigError(f"key 'num_hidden_layers' ({self.num_hidden_layers}) is unreasonably large (>256)")
+        if self.vocab_size > 1_000_000:                                  # config.rs:221-226
+            raise ConfigError(f"key 'vocab_size' ({self.vocab_size}) is unreasonably large (>1M)")
         if self.num_attention_heads % self.num_key_value_heads != 0:     # config.rs:172-180
             raise ConfigError(
                 f"key 'num_attention_heads' ({self.num_attention_heads}) must be divisible by "
@@ -166,12 +173,6 @@ class LlamaConfig:
             raise ConfigError("key 'attention_bias' is true: attention projections with a bias are not supported")
         if self.mlp_bias:
             raise ConfigError("key 'mlp_bias' is true: feed-forward projections with a bias are not supported")
-        if self.hidden_size > 32768:                                     # config.rs:207-212
-            raise ConfigError(f"key 'hidden_size' ({self.hidden_size}) is unreasonably large (>32768)")
-        if self.num_hidden_layers > 256:                                 # config.rs:214-219
-            raise ConfigError(f"key 'num_hidden_layers' ({self.num_hidden_layers}) is unreasonably large (>256)")
-        if self.vocab_size > 1_000_000:                                  # config.rs:221-226
-            raise ConfigError(f"key 'vocab_size' ({self.vocab_size}) is unreasonably large (>1M)")
         for t in self.eos_token_id:
             if not 0 <= t < self.vocab_size:
                 raise ConfigError(f"key 'eos_token_id': {t} is outside the vocabulary ({self.vocab_size})")

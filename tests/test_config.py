@@ -302,3 +302,40 @@ def test_the_reference_s_own_config_cases():
     head = LlamaConfig.from_dict(json.loads('''{"hidden_size": 4096, "num_hidden_layers": 32,
         "num_attention_heads": 32, "vocab_size": 32000}'''))                                # config.rs:513-525
     assert head.head_dim == 128
+
+
+def test_the_reference_s_own_error_handling_cases():
+    """The JSON documents of the reference's error-handling tests, read from its source as text
+    (crates/janus-engine/tests/error_handling.rs:9-177): each is refused or accepted as there, and a refusal
+    names the keys that the reference's message names."""
+    def refused(text, *words, resolve=False):
+        cfg = json.loads(text)
+        with pytest.raises((ConfigError, KeyError, ValueError)) as e:
+            if resolve:
+                resolve_architecture(cfg)
+            else:
+                LlamaConfig.from_dict(cfg)
+        for w in words:
+            assert w in str(e.value), (w, str(e.value))
+
+    refused('{"hidden_size": 0, "num_hidden_layers": 32, "num_attention_heads": 32, "vocab_size": 32000}',
+            "hidden_size")                                                                  # :9-26
+    refused('{"hidden_size": 4097, "num_hidden_layers": 32, "num_attention_heads": 32, "vocab_size": 32000}',
+            "hidden_size", "divisible", "num_attention_heads")                              # :29-47
+    refused('{"hidden_size": 4096, "num_hidden_layers": 32, "num_attention_heads": 32, "num_key_value_heads": 5,'
+            ' "vocab_size": 32000}', "num_attention_heads", "num_key_value_heads", "divisible")   # :50-69
+    refused('{"architectures": ["GPT2LMHeadModel"], "hidden_size": 768, "num_hidden_layers": 12,'
+            ' "num_attention_heads": 12, "vocab_size": 50257}', "GPT2LMHeadModel", "LlamaForCausalLM",
+            resolve=True)                                                                   # :72-91
+    refused('{"hidden_size": 100000, "num_hidden_layers": 32, "num_attention_heads": 32, "vocab_size": 32000}',
+            "unreasonably large")                                                           # :94-110
+    refused('{"num_hidden_layers": 32, "num_attention_heads": 32, "vocab_size": 32000}', "hidden_size")   # :164-177
+    llama = json.loads('{"architectures": ["LlamaForCausalLM"], "hidden_size": 4096, "num_hidden_layers": 32,'
+                       ' "num_attention_heads": 32, "num_key_value_heads": 32, "vocab_size": 32000,'
+                       ' "intermediate_size": 11008, "max_position_embeddings": 2048, "rms_norm_eps": 0.00001}')
+    assert resolve_architecture(llama).config_class.from_dict(llama).num_hidden_layers == 32      # :113-132
+    tiny = LlamaConfig.from_dict(json.loads(
+        '{"architectures": ["LlamaForCausalLM"], "hidden_size": 2048, "num_hidden_layers": 22,'
+        ' "num_attention_heads": 32, "num_key_value_heads": 4, "vocab_size": 32000, "intermediate_size": 5632,'
+        ' "max_position_embeddings": 2048}'))                                               # :135-161
+    assert (tiny.num_attention_heads, tiny.num_key_value_heads) == (32, 4)
