@@ -102,7 +102,8 @@ def test_a_one_layer_model_decodes_many_steps_right():
     import os
     import janus_b200
     from janus_b200.engine import StepEntry
-    assert os.environ.get("JANUS_PDL", "1") != "0"
+    if os.environ.get("JANUS_PDL", "1") == "0":
+        pytest.skip("this test is about programmatic dependent launch, which JANUS_PDL=0 turns off")
     cfg = dict(TINY["A"], num_hidden_layers=1)
     import tempfile
     with tempfile.TemporaryDirectory() as tmp:
