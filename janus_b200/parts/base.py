@@ -183,7 +183,11 @@ class Part:
 
 
 class Norm(Part):
-    def forward(self, x: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None) -> None:
+    def forward(self, x: torch.Tensor, out: torch.Tensor, row_index: Optional[torch.Tensor] = None,
+                clear: Optional[torch.Tensor] = None) -> None:
+        """out[r] = norm(x[row_index[r]] or x[r]) for the rows of `out` (x float32, out the engine dtype).
+        `clear`: a float32 scratch tensor of the part that runs next, to be set to zero on the way (an
+        arrangement passes it when that part asks for it)."""
         raise NotImplementedError
 
 

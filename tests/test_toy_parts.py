@@ -286,3 +286,91 @@ def test_an_arrangement_is_told_which_part_it_lacks():
         DecoderModel(replace(base, layers=(LayerSpec(mixer=l0.mixer, mixer_norm=l0.mixer_norm,
                                                      feed_forward=l0.feed_forward), base.layers[1])),
                      torch.float32, torch.device(DEV))
+
+
+# ---------------------------------------------------------------- another norm
+class ToyCenteredNorm:
+    """A toy norm with two weights: y = (x - mean) / sqrt(var + eps) * gamma + beta, written with device
+    operations of the tensor library (no kernel of this package)."""
+
+    def __init__(self, width, eps, dtype, device):
+        self.width, self.eps, self.dtype, self.device = width, eps, dtype, device
+
+    def weight_shapes(self):
+        return {"gamma": ((self.width,), "ones"), "beta": ((self.width,), "normal")}
+
+    def load(self, gamma, beta):
+        self.gamma, self.beta = gamma.to(self.device).float(), beta.to(self.device).float()
+
+    def forward(self, x, out, row_index=None, clear=None):
+        if clear is not None:
+            clear.zero_()
+        rows = x[:out.shape[0]] if row_index is None else x.index_select(0, row_index.long())
+        mean = rows.mean(-1, keepdim=True)
+        var = ((rows - mean) ** 2).mean(-1, keepdim=True)
+        out.copy_((rows - mean) / torch.sqrt(var + self.eps) * self.gamma + self.beta)
+
+
+def plain_centered(x, gamma, beta, eps):
+    mean = x.mean(-1, keepdim=True)
+    return (x - mean) / torch.sqrt(((x - mean) ** 2).mean(-1, keepdim=True) + eps) * gamma + beta
+
+
+def plain_with_toy_norms(cfg, w, ids):
+    """Layer 0 as the architecture has it; layer 1 and the model's last norm with the toy norm."""
+    eps = 1e-3
+    pos = torch.arange(len(ids))
+    x = P.embed(w["model.embed_tokens.weight"], torch.tensor(ids))
+    x, _ = P.decoder_block(x, pos, cfg, w, 0)
+    a, _ = P.attention_block(plain_centered(x, w["toy.n1.gamma"], w["toy.n1.beta"], eps), pos, cfg, w, 1)
+    x = x + a
+    n = plain_centered(x, w["toy.n2.gamma"], w["toy.n2.beta"], eps)
+    x = x + P.swiglu_ffn(n, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"],
+                         w["model.layers.1.mlp.down_proj.weight"])
+    return P.linear(plain_centered(x, w["toy.n3.gamma"], w["toy.n3.beta"], eps), P.lm_head_weight(cfg, w))
+
+
+@pytest.mark.parametrize("use_graphs", [False, True], ids=["no-graphs", "graphs"])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_toy_norm_with_two_weights_in_a_layer_and_before_the_head(dtype, use_graphs):
+    """Another norm is a registry entry: a toy norm with a weight and a bias, defined here, norms both branches
+    of layer 1 (where it also clears the mixer's scratch when asked) and the rows that go to the head (picked
+    by `row_index`); layer 0 keeps the architecture's norm; the library's files stay as they are."""
+    from janus_b200.config import LlamaConfig
+    from janus_b200.engine import DecoderModel, Engine, EngineOptions, StepEntry
+    from janus_b200.models.llama import llama_spec
+    from janus_b200.parts import PartSpec, register_part
+    from janus_b200.weights import RandomCheckpoint
+
+    register_part("norm", "toy_centered", ToyCenteredNorm)
+    cfg = TINY["A"]
+    base = llama_spec(LlamaConfig.from_dict(cfg))
+
+    def toy(tag):
+        return PartSpec("toy_centered", dict(width=cfg["hidden_size"], eps=1e-3),
+                        weights=dict(gamma=f"toy.{tag}.gamma", beta=f"toy.{tag}.beta"))
+
+    layer1 = replace(base.layers[1], mixer_norm=toy("n1"), feed_forward_norm=toy("n2"))
+    spec = replace(base, layers=(base.layers[0], layer1), final_norm=toy("n3"))
+    model = DecoderModel(spec, getattr(torch, dtype), torch.device(DEV))
+    names = [s.name for s in model.weight_specs()]
+    assert "toy.n3.beta" in names and "model.norm.weight" not in names
+    assert not any("layers.1.input_layernorm" in n or "layers.1.post_attention_layernorm" in n for n in names)
+    ck = RandomCheckpoint(model.weight_specs(), seed=14, dtype=dtype, norm_std=0.05)
+    model.load(ck)
+    w = {n: ck.tensor(n).float() for n in ck.names()}
+    eng = Engine(model, EngineOptions(max_tokens=512, max_slots=2, use_graphs=use_graphs))
+    seqs = [random_tokens(n, cfg["vocab_size"], 90 + n) for n in (75, 20)]
+    ref = [plain_with_toy_norms(cfg, w, ids) for ids in seqs]
+    tol = tol_for(dtype)
+    s0, s1 = eng.alloc_slot(), eng.alloc_slot()
+    a = eng.step([StepEntry(s0, seqs[0][:40], [0, 17, 39]), StepEntry(s1, seqs[1][:9], [8])]).cpu()
+    assert rel_err(a[:3], ref[0][[0, 17, 39]]) < tol and rel_err(a[3:], ref[1][8:9]) < tol
+    for j in range(30):                                  # past position 64; the shorter sequence ends on the way
+        entries = [StepEntry(s0, [seqs[0][40 + j]], [0])]
+        if 9 + j < len(seqs[1]):
+            entries.append(StepEntry(s1, [seqs[1][9 + j]], [0]))
+        b = eng.step(entries).cpu()
+        assert rel_err(b[0:1], ref[0][40 + j:41 + j]) < tol, f"position {40 + j}"
+        if len(entries) == 2:
+            assert rel_err(b[1:2], ref[1][9 + j:10 + j]) < tol
