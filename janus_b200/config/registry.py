@@ -8,6 +8,8 @@ is accepted.
 """
 from __future__ import annotations
 
+import importlib
+import os
 from dataclasses import dataclass
 from typing import Any, Callable, Dict, List
 
@@ -37,8 +39,13 @@ def registered_architectures() -> List[str]:
 
 
 def _load_builtin() -> None:
-    # Importing the package of models registers the built-in architectures.
+    # Importing the package of models registers the built-in architectures; modules named in JANUS_PLUGINS
+    # (comma-separated, importable names) are imported after it, so that the command line and the replay
+    # program also serve architectures and parts that such a module registers.
     from .. import models  # noqa: F401
+    for name in os.environ.get("JANUS_PLUGINS", "").split(","):
+        if name.strip():
+            importlib.import_module(name.strip())
 
 
 def architecture_name(config_dict: Dict[str, Any]) -> str:

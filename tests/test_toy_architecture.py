@@ -166,3 +166,37 @@ def test_a_toy_architecture_from_folder_to_tokens(tmp_path, dtype):
     with pytest.raises(ConfigError, match="groups"):
         ToyConfig.from_dict(dict(TOY, groups=4))
     model.engine.cache.check()
+
+
+def test_the_replay_program_serves_an_architecture_that_a_plugin_module_registers(tmp_path):
+    """`JANUS_PLUGINS` names modules to import before an architecture is looked up: `bin/trace_run`, a process
+    of its own, replays the toy architecture's folder (a prompt, then tokens one by one) with this file as the
+    plugin, and its logits match the plain parts."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    import numpy as np
+    from helpers import ROOT
+    from janus_b200.weights import write_random_model
+    register()
+    d = write_random_model(TOY, str(tmp_path / "toy"), seed=22, dtype="float32", norm_std=0.02)
+    (tmp_path / "toy_plugin.py").write_text("import test_toy_architecture\ntest_toy_architecture.register()\n")
+    cfg, w = read_folder(d)
+    c = ToyConfig.from_dict(cfg)
+    ids = random_tokens(60, c.vocab, 3)
+    steps = [dict(step=0, entries=[dict(id="a", tokens=ids[:50], want=[0, 49])], end=[])]
+    steps += [dict(step=j + 1, entries=[dict(id="a", tokens=[ids[50 + j]], want=[0])], end=["a"] if j == 9 else [])
+              for j in range(10)]
+    env = dict(os.environ, JANUS_PLUGINS="toy_plugin",
+               PYTHONPATH=os.pathsep.join([str(tmp_path), os.path.join(ROOT, "tests"), os.environ.get("PYTHONPATH", "")]))
+    out = tmp_path / "out"
+    res = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", d, "--dtype", "float32",
+                          "--out", str(out), "--max-tokens", "128"],
+                         input="".join(json.dumps(s) + "\n" for s in steps), capture_output=True, text=True,
+                         timeout=600, env=env)
+    assert res.returncode == 0, res.stderr[-2000:]
+    ref = plain_toy(c, w, ids).numpy()
+    got = np.concatenate([np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, c.vocab) for s in steps])
+    assert rel_err(torch.from_numpy(got), torch.from_numpy(ref[[0] + list(range(49, 60))])) < tol_for("float32")
