@@ -51,16 +51,18 @@ class _EngineBackend:
 
     def prefill(self, slots, prompts, requests) -> List[int]:
         steps = plan_prompt_steps([len(p) for p in prompts], self.engine.options.max_step_tokens)
-        rows = [None] * len(prompts)     # the logits at each prompt's last token, from the step that held it
+        rows = None      # the logits at each prompt's last token, copied from the step that held it
         for pieces in steps:
             logits = self.engine.step([StepEntry(slots[i], prompts[i][a:b], (b - a - 1,) if b == len(prompts[i]) else ())
                                        for i, a, b in pieces])
             if len(steps) == 1:
                 return self._sample(logits, slots, requests, [0] * len(slots))
+            if rows is None:
+                rows = torch.empty((len(prompts), logits.shape[1]), dtype=logits.dtype, device=logits.device)
             done = [i for i, _, b in pieces if b == len(prompts[i])]
             for row, i in enumerate(done):
-                rows[i] = logits[row].clone()    # the next step writes its logits to the same place
-        return self._sample(torch.stack(rows), slots, requests, [0] * len(slots))
+                rows[i].copy_(logits[row])       # a device copy; the sampler reads all prompts' rows at once
+        return self._sample(rows, slots, requests, [0] * len(slots))
 
     def decode(self, slots, last_tokens, requests, steps) -> List[int]:
         ids = self.engine.decode_sample(slots, last_tokens, self.sampler, requests, steps)
